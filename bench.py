@@ -1,0 +1,383 @@
+"""Benchmark of the splat hot path: gaussian x pixel evaluations per second, forward +
+backward, on the batched training shape (B=16, N=8192, 256x256, C=3, fp32) per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl reference]
+
+For N > 1 launch under torchrun (one rank per GPU); the batch is sharded, every rank
+renders its own B=16 block (weak scaling), there is no data-path collective.
+
+One JSON line is printed by rank 0.  ``value`` is measured with inputs resident on the
+device; ``e2e`` is the same metric through the public API from pinned host buffers with
+host<->device copies inside the timed region.  ``--impl reference`` times the CPU
+restatement of the reference's chunked torch path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "gaussian_pixel_evals_per_s_fwd_bwd"
+UNIT = "evals/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg3"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------
+# clocks during the timed region
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi (SM clock, power, throttle reasons) of one GPU every 200 ms."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.thread = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], None, [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ts, line in self.rows:
+            if t0 is not None and not (t0 <= ts <= t1 + 0.25):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (restatement of the reference's chunked torch path)
+# ---------------------------------------------------------------------------
+def cpu_step_fn(cfg, n_sample, threads):
+    """Returns (step callable, evals per step, description).  The sample keeps the full
+    batch and the full image and takes the first n_sample gaussians (a multiple of the
+    reference's chunk of 32): the reference's loop runs N/32 identical iterations over
+    [B,32,H,W] blocks, so the sample has the working set and the evals/s of the whole
+    workload."""
+    import torch
+
+    from igs_b200 import workloads
+    from oracle import chunked_port as cp
+
+    torch.set_num_threads(threads)
+    d = workloads.draw(cfg, N=n_sample, device="cpu")
+
+    def step():
+        out, grads = cp.render_fwd_bwd(d["positions"], d["colors"], d["scales"], d["rotations"], d["alphas"], d["x"],
+                                       d["y"], lambda o: 2 * (o - d["target"]) / o.numel())
+        return grads
+
+    return (step, cfg.B * n_sample * cfg.H * cfg.W,
+            f"full batch B={cfg.B}, first {n_sample} of {cfg.N} gaussians, full {cfg.H}x{cfg.W} image")
+
+
+def calibrate_cpu_sample(cfg, threads, target_s):
+    """Gaussians per CPU step so that one step takes about target_s seconds."""
+    step, ev, _ = cpu_step_fn(cfg, 32, threads)
+    step()
+    t0 = time.perf_counter()
+    step()
+    dt = max(time.perf_counter() - t0, 1e-4)
+    n = int(32 * target_s / dt) // 32 * 32
+    return max(32, min(cfg.N, n))
+
+
+def run_cpu_baseline(cfg, seconds):
+    threads = os.cpu_count() or 1
+    n = calibrate_cpu_sample(cfg, threads, max(seconds / 4.0, 0.5))
+    step, ev, sample = cpu_step_fn(cfg, n, threads)
+    step()  # warm-up
+    times = []
+    t_end = time.perf_counter() + seconds * 0.6
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 10):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    res = {"value": ev / med, "unit": UNIT, "cores": threads, "kind": "port",
+           "sample": f"{sample}; median of {len(times)} steps of {med:.2f} s; torch restatement of the reference's "
+                     "chunked path (oracle/chunked_port.py)"}
+    # the fused C oracle on the same sample, for context (a different cost structure)
+    try:
+        import numpy as np
+
+        from igs_b200 import workloads
+        from oracle import splat_oracle as so
+
+        d = {k: v.numpy() for k, v in workloads.draw(cfg, N=n, device="cpu").items()}
+        t0 = time.perf_counter()
+        so.render_with_grads(d["positions"], d["colors"], d["scales"], d["rotations"], d["alphas"], d["x"][:, 0],
+                             d["y"][:, 0], lambda o: 2 * (o - d["target"]) / o.size, dtype=np.float32)
+        res["c_oracle_value"] = ev / (time.perf_counter() - t0)
+        res["c_oracle_threads"] = so.num_threads()
+    except Exception as exc:  # noqa: BLE001 - context only
+        res["c_oracle_value"] = None
+        res["c_oracle_error"] = str(exc)[:200]
+    return res
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU path (its torch restatement) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from igs_b200 import workloads
+
+    cfg = workloads.CONFIGS[args.workload]
+    threads = os.cpu_count() or 1
+    # size each step to ~1.5 s so that steps + warm-ups stay within a few minutes
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    n = calibrate_cpu_sample(cfg, threads, min(1.5, budget))
+    step, ev, sample = cpu_step_fn(cfg, n, threads)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = ev * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"each step: {sample}; torch restatement of the reference's chunked path "
+                                   "(oracle/chunked_port.py; the reference is Python and does not travel)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus):
+    return {"workload": f"{cfg.name}: B={cfg.B} per GPU, N={cfg.N}, {cfg.H}x{cfg.W}, C={cfg.C}, fp32, "
+                        f"MSE loss, fwd+bwd", "B_per_gpu": cfg.B, "global_batch": cfg.B * n_gpus, "N": cfg.N,
+            "H": cfg.H, "W": cfg.W, "C": cfg.C, "parallelism": f"batch-sharded x{n_gpus}, no collective",
+            "l2": "256 MiB buffer written between timed steps"}
+
+
+# ---------------------------------------------------------------------------
+# B200 arm
+# ---------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from igs_b200 import _lib, workloads
+    from igs_b200.gs2d import gaussian_splatting_2d
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: igs_b200 has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    cfg = workloads.CONFIGS[args.workload]
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    # every rank draws its own block of the global batch (different seed per rank)
+    cfg_r = workloads.SplatConfig(**{**cfg.__dict__, "seed": cfg.seed + 1000 * rank})
+    host = {k: v.pin_memory() for k, v in workloads.draw(cfg_r, device="cpu").items()}
+    names = ("positions", "colors", "scales", "rotations", "alphas")
+    on_dev = {k: v.to(dev) for k, v in host.items()}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    grads_host = {k: torch.empty_like(host[k]).pin_memory() for k in names}
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def step_resident():
+        leaves = [on_dev[k].detach().requires_grad_() for k in names]
+        out = gaussian_splatting_2d(*leaves, on_dev["x"], on_dev["y"])
+        loss = torch.nn.functional.mse_loss(out, on_dev["target"])
+        loss.backward()
+        return loss, leaves
+
+    def step_e2e():
+        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        leaves = [d[k].requires_grad_() for k in names]
+        out = gaussian_splatting_2d(*leaves, d["x"], d["y"])
+        loss = torch.nn.functional.mse_loss(out, d["target"])
+        loss.backward()
+        for k, t in zip(names, leaves):
+            grads_host[k].copy_(t.grad, non_blocking=True)
+        loss_host.copy_(loss.detach(), non_blocking=True)
+
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = sum(v.numel() * v.element_size() for v in grads_host.values()) + 4
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """n steps, each bracketed by CUDA events on the current stream, L2 flushed in
+        between (outside the events); returns the per-step device times in ms."""
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        barrier()
+        for a, b in evs:
+            flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        barrier()
+        return [a.elapsed_time(b) for a, b in evs]
+
+    for _ in range(warmup):
+        step_resident()
+    probes = _lib.probe_rates(dev) if rank == 0 else None
+    barrier()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    _lib.profile_reset()
+    _lib.profile_enable(True)
+    n0 = _lib.launch_count()
+    t_wall0 = time.perf_counter()
+    times = timed(step_resident, steps)
+    t_wall1 = time.perf_counter()
+    launches = _lib.launch_count() - n0
+    _lib.profile_enable(False)
+    prof = _lib.profile_read()
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    for _ in range(2):
+        step_e2e()
+    e2e_times = timed(step_e2e, steps)
+
+    total_ms = torch.tensor([sum(times), sum(e2e_times)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = total_ms.tolist()
+    ev_rank = workloads.evals(cfg)
+    value = ev_rank * world * steps / (total_ms[0] * 1e-3)
+    e2e_value = ev_rank * world * steps / (total_ms[1] * 1e-3)
+
+    if rank == 0:
+        C = cfg.C
+        sm = (clocks or {}).get("sm_mhz")
+        n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        fp32_peak = probes["fp32_scalar_lane_instr_per_s"]
+        # canonical FMA-pipe instruction counts per gaussian x pixel (fwd 9+C, bwd 18+2C)
+        instr = {"forward": 9 + C, "backward": 18 + 2 * C}
+
+        def kernel_roof(name):
+            ms, n = prof[name]
+            if n == 0:
+                return None
+            per_launch_s = ms / n * 1e-3
+            ach = ev_rank * instr[name] / per_launch_s
+            return {"bound": "fp32_fma_pipe", "kernel": f"splat_{name}_kernel", "achieved": ach / 1e12,
+                    "peak": fp32_peak / 1e12, "unit": "T lane-instr/s", "frac": ach / fp32_peak,
+                    "launch_ms": ms / n, "launches": n,
+                    "algorithmic_instr_per_eval": instr[name],
+                    "peak_source": "measured live: dependent-chain FFMA kernel (igs_probe_fp32_rate)",
+                    "traffic": None}
+
+        roof = kernel_roof("backward")
+        roof_f = kernel_roof("forward")
+        step_ach = ev_rank * (27 + 3 * C) / (statistics.mean(times) * 1e-3)
+        hbm_bytes = (2 * cfg.B * cfg.N * (6 + C) * 4 + 2 * cfg.B * cfg.H * cfg.W * 4 + cfg.B * (C + 1) * cfg.H * cfg.W * 4
+                     + cfg.B * (2 * C + 3) * cfg.H * cfg.W * 4 + cfg.B * cfg.N * (6 + C) * 4)
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except OSError:
+            pass
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": total_ms[0] / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": total_ms[1] / steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": roof,
+            "roofline_forward": roof_f,
+            "roofline_step": {"bound": "fp32_fma_pipe", "achieved": step_ach / 1e12, "peak": fp32_peak / 1e12,
+                              "unit": "T lane-instr/s", "frac": step_ach / fp32_peak,
+                              "algorithmic_instr_per_eval": 27 + 3 * C,
+                              "nominal_peak": n_sm * 128 * (sm or 0) * 1e6 / 1e12 if sm else None},
+            "probes": probes,
+            "hbm": {"algorithmic_bytes_per_step": hbm_bytes,
+                    "achieved_gbs": hbm_bytes / (statistics.mean(times) * 1e-3) / 1e9,
+                    "peak_gbs": peaks.get("hbm_gbs"), "note": "not the bound: the path is FP32/MUFU issue-bound"},
+            "kernel_ms_per_step": {k: v[0] / steps for k, v in prof.items() if v[1]},
+            "plan": _lib.describe_plan(cfg.B, cfg.N, cfg.H, cfg.W, cfg.C, dev),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = run_cpu_baseline(cfg, args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

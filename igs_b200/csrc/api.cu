@@ -1,0 +1,612 @@
+// extern "C" entry points, launch plans and workspace carving.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "backward.cuh"
+#include "forward.cuh"
+#include "pack.cuh"
+#include "plan.cuh"
+
+namespace igs {
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// ---- optional per-kernel timing (igs_profile_*) ----
+static std::atomic<int> g_profile_on{0};
+static std::mutex g_profile_mu;
+struct EventPair {
+    int id;
+    cudaEvent_t start, stop;
+};
+static std::vector<EventPair> g_pending;
+static double g_total_ms[K_COUNT];
+static long long g_timed_launches[K_COUNT];
+
+KernelTimer::KernelTimer(int id_, cudaStream_t s) : id(id_), stream(s) {
+    if (!g_profile_on.load(std::memory_order_relaxed)) return;
+    if (cudaEventCreate(&start) != cudaSuccess || cudaEventCreate(&stop) != cudaSuccess) {
+        cudaGetLastError();
+        start = stop = nullptr;
+        return;
+    }
+    cudaEventRecord(start, stream);
+}
+KernelTimer::~KernelTimer() {
+    if (!start || !stop) return;
+    cudaEventRecord(stop, stream);
+    std::lock_guard<std::mutex> lock(g_profile_mu);
+    g_pending.push_back({id, start, stop});
+}
+
+// waits for every pending pair and folds it into the totals
+static cudaError_t profile_drain() {
+    std::lock_guard<std::mutex> lock(g_profile_mu);
+    cudaError_t first = cudaSuccess;
+    for (const EventPair& p : g_pending) {
+        cudaError_t e = cudaEventSynchronize(p.stop);
+        float ms = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, p.start, p.stop);
+        if (e == cudaSuccess) {
+            g_total_ms[p.id] += ms;
+            g_timed_launches[p.id] += 1;
+        } else if (first == cudaSuccess) {
+            first = e;
+        }
+        cudaEventDestroy(p.start);
+        cudaEventDestroy(p.stop);
+    }
+    g_pending.clear();
+    return first;
+}
+
+int sm_count(int device) {
+    static int cached[64];
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 148;
+    }
+    if (device >= 0 && device < 64) cached[device] = n;
+    return n;
+}
+
+int make_chunks(int C, Chunks* out) {
+    if (C < 1 || C > 16 * MAX_CHUNKS) return IGS_ERR_LIMIT;
+    out->n = 0;
+    int c = 0;
+    while (c < C) {
+        const int cr = (C - c) >= 16 ? 16 : (C - c);
+        const int k = out->n++;
+        out->c0[k] = c;
+        out->cr[k] = cr;
+        out->ct[k] = chunk_template(cr);
+        c += cr;
+    }
+    return IGS_OK;
+}
+
+// Picks the count (1..max_parts) of equal parts along the streamed axis that wastes the
+// fewest CTA slots in the last wave; ties go to the smaller count.
+static int pick_parts(long long base_ctas, long long slots, long long axis_len, long long min_len, int max_parts) {
+    int best = 1;
+    double best_eff = -1.0;
+    for (int s = 1; s <= max_parts; ++s) {
+        if (s > 1 && axis_len / s < min_len) break;
+        const long long ctas = base_ctas * s;
+        const long long waves = (ctas + slots - 1) / slots;
+        const double eff = (double)ctas / (double)(waves * slots);
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            best = s;
+        }
+    }
+    return best;
+}
+
+int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
+    if (B < 0 || N < 0 || H < 0 || W < 0) return IGS_ERR_ARG;
+    if (B > 65535) return IGS_ERR_LIMIT;
+    int rc = make_chunks(C, &p->ch);
+    if (rc) return rc;
+    const long long HW = (long long)H * W;
+    const int ct = p->ch.ct[0];
+    p->threads = forward_threads(ct);
+    p->px_per_thread = forward_px_per_thread(ct);
+    p->tile_px = p->threads * p->px_per_thread;
+    const long long tiles = (HW + p->tile_px - 1) / p->tile_px;
+    if (tiles > 0x7fffffffLL) return IGS_ERR_LIMIT;
+    p->tiles = (int)tiles;
+    p->chunk_g = forward_chunk_g(ct);
+    p->stages = 2;
+    const long long slots = (long long)sm_count(device) * forward_ctas_per_sm(ct, device);
+    const long long base = tiles * (B > 0 ? B : 1);
+    int ns = pick_parts(base > 0 ? base : 1, slots, N, 2LL * p->chunk_g, 64);
+    if (ns > 65535) ns = 65535;
+    p->n_split = ns;
+    // splits start on a stage boundary so that every bulk copy is a whole number of records
+    long long per = (N + ns - 1) / ns;
+    per = (per + p->chunk_g - 1) / p->chunk_g * p->chunk_g;
+    if (per <= 0) per = p->chunk_g;
+    p->per_split = (int)per;
+    p->n_split = (int)((N + per - 1) / per);
+    if (p->n_split < 1) p->n_split = 1;
+
+    size_t off = STATUS_BYTES;
+    const long long M = (long long)B * N;
+    for (int k = 0; k < p->ch.n; ++k) {
+        p->off_frec[k] = off;
+        off = align_up(off + (size_t)M * fwd_rec_floats(p->ch.ct[k]) * sizeof(float), 256);
+    }
+    p->off_partial = off;
+    off = align_up(off + (size_t)p->n_split * B * (C + 1) * HW * sizeof(float), 256);
+    p->bytes = off;
+    return IGS_OK;
+}
+
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
+    if (B < 0 || N < 0 || H < 0 || W < 0) return IGS_ERR_ARG;
+    if (B > 65535) return IGS_ERR_LIMIT;
+    int rc = make_chunks(C, &p->ch);
+    if (rc) return rc;
+    const long long HW = (long long)H * W;
+    const int ct = p->ch.ct[0];
+    p->threads = backward_threads(ct);
+    p->chunk_pairs = backward_chunk_pairs(ct);
+    p->stages = 2;
+    p->npairs = (HW + 1) / 2;
+    const long long groups = ((long long)N + p->threads - 1) / p->threads;
+    const long long slots = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
+    const long long base = groups * (B > 0 ? B : 1);
+    int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);
+    long long per = (p->npairs + ns - 1) / ns;
+    per = (per + p->chunk_pairs - 1) / p->chunk_pairs * p->chunk_pairs;
+    if (per <= 0) per = p->chunk_pairs;
+    p->pairs_per_slab = per;
+    p->n_slab = (int)((p->npairs + per - 1) / per);
+    if (p->n_slab < 1) p->n_slab = 1;
+    p->planes = N_MOMENTS * p->ch.n + C;
+
+    size_t off = STATUS_BYTES;
+    const long long M = (long long)B * N;
+    p->off_geo = off;
+    off = align_up(off + (size_t)M * GEO_FLOATS * sizeof(float), 256);
+    for (int k = 0; k < p->ch.n; ++k) {
+        p->off_prec[k] = off;
+        off = align_up(off + (size_t)B * p->npairs * bwd_rec_floats(p->ch.ct[k]) * sizeof(float), 256);
+    }
+    p->off_part = off;
+    off = align_up(off + (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float), 256);
+    p->off_xy = off;
+    p->bytes = off;
+    return IGS_OK;
+}
+
+static int check_device(int device) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return IGS_ERR_DEVICE;
+    }
+    return IGS_OK;
+}
+
+struct Strides {
+    long long b, h, w;
+};
+static Strides get_strides(const int64_t* s, int H, int W) {
+    if (!s) return {(long long)H * W, (long long)W, 1};
+    return {(long long)s[0], (long long)s[1], (long long)s[2]};
+}
+
+static int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2,
+                        const float* alpha, const float* colors, const float* x, const int64_t* xs, const float* y,
+                        const int64_t* ys, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
+                        float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
+    const long long HW = (long long)H * W;
+    if (B == 0 || HW == 0) return IGS_OK;
+    if (!x || !y) return IGS_ERR_ARG;
+    if (N > 0 && (!pos || !s0 || !s1 || !alpha || !colors || (kind == SHAPE_COV_INV && !s2))) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    if (N == 0) {
+        // no gaussians: every sum is zero (the reference's loop body never runs)
+        cudaError_t e;
+        if (normalize) {
+            e = cudaMemsetAsync(out, 0, (size_t)B * C * HW * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(wsum, 0, (size_t)B * HW * sizeof(float), st);
+        } else {
+            e = cudaMemsetAsync(out, 0, (size_t)B * (C + 1) * HW * sizeof(float), st);
+        }
+        return (int)e;
+    }
+
+    FwdPlan p;
+    rc = plan_forward(B, N, H, W, C, device, &p);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+
+    PackArgs pa;
+    std::memset(&pa, 0, sizeof(pa));
+    pa.pos = pos;
+    pa.shape0 = s0;
+    pa.shape1 = s1;
+    pa.shape2 = s2;
+    pa.alpha = alpha;
+    pa.colors = colors;
+    pa.geo = nullptr;
+    for (int k = 0; k < p.ch.n; ++k) pa.frec[k] = reinterpret_cast<float*>(ws + p.off_frec[k]);
+    pa.ch = p.ch;
+    pa.M = (long long)B * N;
+    pa.C = C;
+    pa.eps = eps;
+    pa.kind = kind;
+    e = launch_pack(pa, st);
+    if (e != cudaSuccess) return (int)e;
+
+    const bool in_kernel = normalize && p.n_split == 1;
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    for (int k = 0; k < p.ch.n; ++k) {
+        FwdArgs fa;
+        std::memset(&fa, 0, sizeof(fa));
+        fa.frec = pa.frec[k];
+        fa.x = x;
+        fa.y = y;
+        fa.xs_b = sx.b; fa.xs_h = sx.h; fa.xs_w = sx.w;
+        fa.ys_b = sy.b; fa.ys_h = sy.h; fa.ys_w = sy.w;
+        fa.out = out;
+        fa.wsum = wsum;
+        // single split without normalisation: the "partial" array IS the caller's sums buffer
+        fa.partial = (!normalize && p.n_split == 1) ? out : reinterpret_cast<float*>(ws + p.off_partial);
+        fa.status = reinterpret_cast<int*>(ws);
+        fa.B = B; fa.N = N; fa.H = H; fa.W = W; fa.C = C;
+        fa.c0 = p.ch.c0[k];
+        fa.cr = p.ch.cr[k];
+        fa.per_split = p.per_split;
+        fa.in_kernel_normalize = in_kernel ? 1 : 0;
+        fa.write_s = (k == 0) ? 1 : 0;
+        fa.eps = eps;
+        e = launch_forward_chunk(p.ch.ct[k], fa, p, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (p.n_split > 1) {
+        ReduceArgs ra;
+        ra.partial = reinterpret_cast<const float*>(ws + p.off_partial);
+        ra.out = out;
+        ra.wsum = wsum;
+        ra.HW = HW;
+        ra.B = B; ra.C = C; ra.n_split = p.n_split; ra.normalize = normalize ? 1 : 0;
+        ra.eps = eps;
+        e = launch_reduce_normalize(ra, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return IGS_OK;
+}
+
+static int backward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2,
+                         const float* alpha, const float* colors, const float* x, const int64_t* xs, const float* y,
+                         const int64_t* ys, const float* wsum, const float* out, const float* gout, int B, int N,
+                         int H, int W, int C, float eps, int mode, float* d_pos, float* d_s0, float* d_s1,
+                         float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, void* workspace,
+                         size_t workspace_bytes, int device, void* stream) {
+    if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
+    if ((d_x == nullptr) != (d_y == nullptr)) return IGS_ERR_ARG;
+    const long long HW = (long long)H * W;
+    if (B == 0) return IGS_OK;
+    if (HW > 0 && (!x || !y || !wsum || !gout || (mode == IGS_GRAD_EXACT && !out))) return IGS_ERR_ARG;
+    if (N > 0 && (!pos || !s0 || !s1 || !alpha || !colors || !d_pos || !d_s0 || !d_s1 || !d_alpha || !d_colors ||
+                  (kind == SHAPE_COV_INV && (!s2 || !d_s2))))
+        return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+
+    if (N == 0 || HW == 0) {
+        // nothing to sum over: every gradient is zero
+        const size_t M = (size_t)B * N;
+        e = cudaSuccess;
+        if (M) {
+            e = cudaMemsetAsync(d_pos, 0, M * 2 * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_s0, 0, M * (kind == SHAPE_SCALE_ROT ? 2 : 1) * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_s1, 0, M * sizeof(float), st);
+            if (e == cudaSuccess && kind == SHAPE_COV_INV) e = cudaMemsetAsync(d_s2, 0, M * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_alpha, 0, M * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_colors, 0, M * C * sizeof(float), st);
+        }
+        if (e == cudaSuccess && d_x && HW) {
+            e = cudaMemsetAsync(d_x, 0, (size_t)B * HW * sizeof(float), st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_y, 0, (size_t)B * HW * sizeof(float), st);
+        }
+        return (int)e;
+    }
+
+    BwdPlan p;
+    rc = plan_backward(B, N, H, W, C, device, &p);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    e = cudaMemsetAsync(ws, 0, sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+
+    PackArgs pa;
+    std::memset(&pa, 0, sizeof(pa));
+    pa.pos = pos;
+    pa.shape0 = s0;
+    pa.shape1 = s1;
+    pa.shape2 = s2;
+    pa.alpha = alpha;
+    pa.colors = colors;
+    pa.geo = reinterpret_cast<float*>(ws + p.off_geo);
+    pa.ch = p.ch;
+    pa.M = (long long)B * N;
+    pa.C = C;
+    pa.eps = eps;
+    pa.kind = kind;
+    e = launch_pack(pa, st);
+    if (e != cudaSuccess) return (int)e;
+
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    PixelTermArgs ta;
+    std::memset(&ta, 0, sizeof(ta));
+    ta.x = x;
+    ta.y = y;
+    ta.xs_b = sx.b; ta.xs_h = sx.h; ta.xs_w = sx.w;
+    ta.ys_b = sy.b; ta.ys_h = sy.h; ta.ys_w = sy.w;
+    ta.wsum = wsum;
+    ta.out = out;
+    ta.gout = gout;
+    for (int k = 0; k < p.ch.n; ++k) ta.prec[k] = reinterpret_cast<float*>(ws + p.off_prec[k]);
+    ta.ch = p.ch;
+    ta.npairs = p.npairs;
+    ta.B = B; ta.H = H; ta.W = W; ta.C = C;
+    ta.mode = mode;
+    ta.eps = eps;
+    e = launch_pixel_terms(ta, st);
+    if (e != cudaSuccess) return (int)e;
+
+    for (int k = 0; k < p.ch.n; ++k) {
+        BwdArgs ba;
+        std::memset(&ba, 0, sizeof(ba));
+        ba.geo = pa.geo;
+        ba.colors = colors;
+        ba.prec = ta.prec[k];
+        ba.part = reinterpret_cast<float*>(ws + p.off_part);
+        ba.status = reinterpret_cast<int*>(ws);
+        ba.npairs = p.npairs;
+        ba.pairs_per_slab = p.pairs_per_slab;
+        ba.B = B; ba.N = N; ba.C = C;
+        ba.c0 = p.ch.c0[k];
+        ba.cr = p.ch.cr[k];
+        ba.planes = p.planes;
+        ba.moment_plane0 = N_MOMENTS * k;
+        ba.color_plane0 = N_MOMENTS * p.ch.n;
+        e = launch_backward_chunk(p.ch.ct[k], ba, p, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+
+    FinalizeArgs fa;
+    std::memset(&fa, 0, sizeof(fa));
+    fa.part = reinterpret_cast<const float*>(ws + p.off_part);
+    fa.pos = pos;
+    fa.shape0 = s0;
+    fa.shape1 = s1;
+    fa.shape2 = s2;
+    fa.alpha = alpha;
+    fa.d_pos = d_pos;
+    fa.d_shape0 = d_s0;
+    fa.d_shape1 = d_s1;
+    fa.d_shape2 = d_s2;
+    fa.d_alpha = d_alpha;
+    fa.d_colors = d_colors;
+    fa.B = B; fa.N = N; fa.C = C;
+    fa.n_slab = p.n_slab;
+    fa.planes = p.planes;
+    fa.n_chunks = p.ch.n;
+    fa.kind = kind;
+    fa.eps = eps;
+    e = launch_finalize(fa, st);
+    if (e != cudaSuccess) return (int)e;
+
+    if (d_x) {
+        CoordGradArgs ca;
+        std::memset(&ca, 0, sizeof(ca));
+        ca.geo = pa.geo;
+        ca.colors = colors;
+        ca.x = x;
+        ca.y = y;
+        ca.xs_b = sx.b; ca.xs_h = sx.h; ca.xs_w = sx.w;
+        ca.ys_b = sy.b; ca.ys_h = sy.h; ca.ys_w = sy.w;
+        ca.wsum = wsum;
+        ca.out = out;
+        ca.gout = gout;
+        ca.d_x = d_x;
+        ca.d_y = d_y;
+        ca.B = B; ca.N = N; ca.H = H; ca.W = W; ca.C = C;
+        ca.mode = mode;
+        ca.eps = eps;
+        e = launch_coord_grad(ca, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return IGS_OK;
+}
+
+// normalisation split off for the gaussian-sharded multi-GPU path: same kernel as the
+// split reduction, with the all-reduced sums as a single "split"
+static int normalize_impl(const float* sums, int B, int H, int W, int C, float eps, float* out, float* wsum,
+                          int device, void* stream) {
+    if (B < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    const long long HW = (long long)H * W;
+    if (B == 0 || HW == 0) return IGS_OK;
+    if (!sums || !out || !wsum) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    ReduceArgs ra;
+    ra.partial = sums;
+    ra.out = out;
+    ra.wsum = wsum;
+    ra.HW = HW;
+    ra.B = B; ra.C = C; ra.n_split = 1; ra.normalize = 1;
+    ra.eps = eps;
+    return (int)launch_reduce_normalize(ra, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace igs
+
+using namespace igs;
+
+extern "C" {
+
+int igs_version(void) { return 100; }
+
+const char* igs_strerror(int code) {
+    switch (code) {
+        case IGS_OK: return "ok";
+        case IGS_ERR_ARG: return "invalid argument (null pointer, negative size or unsupported value)";
+        case IGS_ERR_WORKSPACE: return "workspace missing or smaller than igs_workspace_bytes reports";
+        case IGS_ERR_LIMIT: return "size beyond a supported limit (B <= 65535, C <= 256)";
+        case IGS_ERR_DEVICE: return "CUDA device cannot be selected";
+        case IGS_ERR_STATUS: return "a kernel gave up on a bounded wait (status word non-zero)";
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown igs_b200 error";
+}
+
+long long igs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int igs_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* forward_bytes, size_t* backward_bytes) {
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    FwdPlan fp;
+    BwdPlan bp;
+    rc = plan_forward(B, N, H, W, C, device, &fp);
+    if (rc) return rc;
+    rc = plan_backward(B, N, H, W, C, device, &bp);
+    if (rc) return rc;
+    if (forward_bytes) *forward_bytes = fp.bytes;
+    if (backward_bytes) *backward_bytes = bp.bytes;
+    return IGS_OK;
+}
+
+int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_tile_pixels, int* fwd_splits,
+                      int* bwd_threads, int* bwd_slabs) {
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    FwdPlan fp;
+    BwdPlan bp;
+    rc = plan_forward(B, N, H, W, C, device, &fp);
+    if (rc) return rc;
+    rc = plan_backward(B, N, H, W, C, device, &bp);
+    if (rc) return rc;
+    if (fwd_tile_pixels) *fwd_tile_pixels = fp.tile_px;
+    if (fwd_splits) *fwd_splits = fp.n_split;
+    if (bwd_threads) *bwd_threads = bp.threads;
+    if (bwd_slabs) *bwd_slabs = bp.n_slab;
+    return IGS_OK;
+}
+
+int igs_forward_sr(const float* positions, const float* scales, const float* rotations, const float* alphas,
+                   const float* colors, const float* x, const int64_t* x_strides, const float* y,
+                   const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
+                   float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    return forward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
+                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream);
+}
+
+int igs_forward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01, const float* cov_inv_11,
+                    const float* alphas, const float* colors, const float* x, const int64_t* x_strides, const float* y,
+                    const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
+                    float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    return forward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
+                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream);
+}
+
+int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, float* out, float* wsum, int device,
+                  void* stream) {
+    return normalize_impl(sums, B, H, W, C, eps, out, wsum, device, stream);
+}
+
+int igs_backward_sr(const float* positions, const float* scales, const float* rotations, const float* alphas,
+                    const float* colors, const float* x, const int64_t* x_strides, const float* y,
+                    const int64_t* y_strides, const float* wsum, const float* out, const float* gout, int B, int N,
+                    int H, int W, int C, float eps, int grad_mode, float* d_positions, float* d_scales,
+                    float* d_rotations, float* d_alphas, float* d_colors, float* d_x, float* d_y, void* workspace,
+                    size_t workspace_bytes, int device, void* stream) {
+    return backward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
+                         y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_scales, d_rotations,
+                         nullptr, d_alphas, d_colors, d_x, d_y, workspace, workspace_bytes, device, stream);
+}
+
+int igs_backward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01,
+                     const float* cov_inv_11, const float* alphas, const float* colors, const float* x,
+                     const int64_t* x_strides, const float* y, const int64_t* y_strides, const float* wsum,
+                     const float* out, const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
+                     float* d_positions, float* d_cov_inv_00, float* d_cov_inv_01, float* d_cov_inv_11,
+                     float* d_alphas, float* d_colors, float* d_x, float* d_y, void* workspace, size_t workspace_bytes,
+                     int device, void* stream) {
+    return backward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
+                         y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_cov_inv_00,
+                         d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, workspace, workspace_bytes, device,
+                         stream);
+}
+
+int igs_profile_enable(int on) {
+    g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+    return IGS_OK;
+}
+
+int igs_profile_reset(void) {
+    cudaError_t e = profile_drain();
+    std::lock_guard<std::mutex> lock(g_profile_mu);
+    for (int k = 0; k < K_COUNT; ++k) {
+        g_total_ms[k] = 0.0;
+        g_timed_launches[k] = 0;
+    }
+    return (int)e;
+}
+
+int igs_profile_read(int kernel_id, double* total_ms, long long* launches) {
+    if (kernel_id < 0 || kernel_id >= K_COUNT) return IGS_ERR_ARG;
+    cudaError_t e = profile_drain();
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lock(g_profile_mu);
+    if (total_ms) *total_ms = g_total_ms[kernel_id];
+    if (launches) *launches = g_timed_launches[kernel_id];
+    return IGS_OK;
+}
+
+int igs_read_status(const void* workspace, int device, void* stream, int* host_status) {
+    if (!workspace || !host_status) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(host_status, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    return *host_status ? IGS_ERR_STATUS : IGS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,461 @@
+// Backward splat kernels (sm_100a).
+//
+// The weights are recomputed, never cached.  The roles of the forward kernel are
+// swapped: one THREAD owns one gaussian (parameters and all of its gradient sums live
+// in registers), one CTA owns a group of gaussians and a slab of pixels, and the
+// per-pixel upstream terms stream through shared memory as pair records
+//   {x0,x1, y0,y1, gS0,gS1, gn_c0,gn_c1 ...}
+// filled by 1-D bulk (TMA) copies.  Every lane reads the same record (broadcast), so
+// the reduction over pixels needs no shuffles and no atomics: it is a register
+// accumulation, folded per stage into a second-level accumulator, and one partial per
+// (slab, gaussian) that finalize_kernel adds in slab order.
+//
+// Per gaussian x pixel, with h = G*e and G = gS + sum_c gn_c*colour_c:
+//   M0 += h; Mx += h*dx; My += h*dy; Mxx += h*dx*dx; Mxy += h*dx*dy; Myy += h*dy*dy;
+//   E_c += gn_c*e
+// 22 FMA-pipe instructions and one MUFU at C = 3, all f32x2 over the two pixels of a
+// pair.  finalize_kernel turns the sums into the reference's gradients:
+//   d_alpha = M0                    d_colour_c = alpha*E_c
+//   d_c00 = -alpha/2*Mxx   d_c11 = -alpha/2*Myy   d_c01 = -alpha*Mxy
+//   d_px = alpha*(c00*Mx + c01*My)  d_py = alpha*(c11*My + c01*Mx)
+// and, for the scale/rotation entry, chains d_c** through the closed-form inverse.
+#include "backward.cuh"
+
+namespace igs {
+
+// ---------------------------------------------------------------------------
+// per-pixel upstream terms
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pixel_terms_kernel(PixelTermArgs a) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*npairs
+    if (i >= (long long)a.B * a.npairs) return;
+    const long long b = i / a.npairs, pair = i - b * a.npairs;
+    const long long HW = (long long)a.H * a.W;
+    float xv[2], yv[2], inv_ok[2], Sp[2], gS[2] = {0.f, 0.f};
+    long long pp[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        long long p = pair * 2 + k;
+        inv_ok[k] = 1.f;
+        if (p >= HW) {  // odd pixel count: repeat the last pixel with zero upstream terms
+            p = HW - 1;
+            inv_ok[k] = 0.f;
+        }
+        pp[k] = p;
+        const long long h = p / a.W, w = p - h * a.W;
+        xv[k] = a.x[b * a.xs_b + h * a.xs_h + w * a.xs_w];
+        yv[k] = a.y[b * a.ys_b + h * a.ys_h + w * a.ys_w];
+        Sp[k] = a.wsum[b * HW + p] + a.eps;
+    }
+    // gS, summed over ALL channels (first chunk carries it)
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        float acc = 0.f;
+        for (int c = 0; c < a.C; ++c) {
+            const float g = a.gout[(b * a.C + c) * HW + pp[k]];
+            if (a.mode == IGS_GRAD_REFERENCE)
+                acc += g * g;
+            else
+                acc += (g / Sp[k]) * a.out[(b * a.C + c) * HW + pp[k]];
+        }
+        gS[k] = (a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp[k] * Sp[k]) : -acc;
+        gS[k] *= inv_ok[k];
+    }
+    for (int q = 0; q < a.ch.n; ++q) {
+        const int ct = a.ch.ct[q], cr = a.ch.cr[q], c0 = a.ch.c0[q];
+        const int rs = bwd_rec_floats(ct);
+        float* r = a.prec[q] + i * rs;
+        r[0] = xv[0];
+        r[1] = xv[1];
+        r[2] = yv[0];
+        r[3] = yv[1];
+        r[4] = q == 0 ? gS[0] : 0.f;
+        r[5] = q == 0 ? gS[1] : 0.f;
+        for (int c = 0; c < rs / 2 - 3; ++c) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                float v = 0.f;
+                if (c < cr) v = inv_ok[k] * (a.gout[(b * a.C + c0 + c) * HW + pp[k]] / Sp[k]);
+                r[6 + 2 * c + k] = v;
+            }
+        }
+    }
+}
+
+cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s) {
+    const long long n = (long long)a.B * a.npairs;
+    if (n <= 0) return cudaSuccess;
+    {
+        KernelTimer timer(K_PIXEL_TERMS, s);
+        pixel_terms_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// main backward kernel
+// ---------------------------------------------------------------------------
+template <int CT>
+struct BwdCfg {
+    static constexpr int THREADS = 128;
+    static constexpr int CHUNK_PAIRS = CT <= 4 ? 256 : 128;
+    static constexpr int STAGES = 2;
+    static constexpr int MIN_CTAS = CT <= 4 ? 5 : (CT <= 8 ? 4 : 3);
+    static constexpr bool TWO_LEVEL = CT <= 4;
+    static constexpr int RS = bwd_rec_floats(CT);
+    static constexpr int NACC = N_MOMENTS + CT;
+    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_PAIRS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
+};
+
+template <int CT>
+__global__ void __launch_bounds__(BwdCfg<CT>::THREADS, BwdCfg<CT>::MIN_CTAS) splat_backward_kernel(BwdArgs a) {
+    using Cfg = BwdCfg<CT>;
+    constexpr int T = Cfg::THREADS, PC = Cfg::CHUNK_PAIRS, NS = Cfg::STAGES, RS = Cfg::RS, NACC = Cfg::NACC;
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* stage_base = reinterpret_cast<float*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NS * PC * RS * sizeof(float));
+    int* s_failed = reinterpret_cast<int*>(bars + NS);
+
+    const int tid = threadIdx.x;
+    const int b = blockIdx.z, slab = blockIdx.y;
+    const int n = blockIdx.x * T + tid;
+    const bool valid = n < a.N;
+    const int nn = valid ? n : a.N - 1;
+
+    // ---- this thread's gaussian ----
+    const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
+    const float4 g0 = gp[0], g1 = gp[1];
+    const f2 px = pk(g0.x, g0.x), py = pk(g0.y, g0.y);
+    const f2 A = pk(g0.z, g0.z), B2 = pk(g0.w, g0.w), Cq = pk(g1.x, g1.x);
+    f2 col[CT];
+#pragma unroll
+    for (int c = 0; c < CT; ++c) {
+        const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
+        col[c] = pk(v, v);
+    }
+
+    f2 tot[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) tot[k] = 0ull;
+
+    // ---- pixel slab, streamed in stages ----
+    const long long pair_begin = (long long)slab * a.pairs_per_slab;
+    const long long pair_end = min(a.npairs, pair_begin + a.pairs_per_slab);
+    const int n_total = (int)max(0ll, pair_end - pair_begin);
+    const int n_chunks = (n_total + PC - 1) / PC;
+    const float* src = a.prec + ((long long)b * a.npairs + pair_begin) * RS;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+        *s_failed = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto issue = [&](int chunk) {
+        const int st = chunk % NS;
+        const int cnt = min(PC, n_total - chunk * PC);
+        const uint32_t bytes = (uint32_t)cnt * RS * sizeof(float);
+        mbar_expect_tx(&bars[st], bytes);
+        bulk_g2s(stage_base + (size_t)st * PC * RS, src + (long long)chunk * PC * RS, bytes, &bars[st]);
+    };
+    if (tid == 0) {
+        for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
+    }
+
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        const int st = chunk % NS;
+        const uint32_t parity = (chunk / NS) & 1;
+        if (!mbar_wait_bounded(&bars[st], parity)) *s_failed = 1;
+        __syncthreads();
+        if (*s_failed) {
+            if (tid == 0) {
+                for (int c = chunk + 1; c < n_chunks && c < chunk + NS; ++c)
+                    mbar_wait_bounded(&bars[c % NS], (c / NS) & 1);
+                atomicOr(a.status, STATUS_WAIT_TIMEOUT);
+            }
+            return;
+        }
+        const int cnt = min(PC, n_total - chunk * PC);
+        const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * PC * RS);
+
+        f2 acc[NACC];
+        if (Cfg::TWO_LEVEL) {
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) acc[k] = 0ull;
+        } else {
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) acc[k] = tot[k];
+        }
+#pragma unroll 2
+        for (int i = 0; i < cnt; ++i) {
+            const ulonglong2* r = rec + (size_t)i * (RS / 4);
+            const ulonglong2 r0 = r[0];  // {x0,x1},{y0,y1}
+            f2 gterm[CT + 2];            // gS, gn_0 .. gn_{CT-1} (+ pad)
+#pragma unroll
+            for (int c = 0; c < (CT + 2) / 2; ++c) {
+                const ulonglong2 rc = r[1 + c];
+                gterm[2 * c] = rc.x;
+                gterm[2 * c + 1] = rc.y;
+            }
+            const f2 dx = sub2(r0.x, px);
+            const f2 dy = sub2(r0.y, py);
+            const f2 t = fma2(A, dx, mul2(B2, dy));
+            const f2 v = mul2(mul2(Cq, dy), dy);
+            const f2 e = ex2_2(fma2(dx, t, v));
+            f2 G = gterm[0];
+#pragma unroll
+            for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[c], G);
+            const f2 h = mul2(G, e);
+            acc[0] = add2(acc[0], h);
+            const f2 hx = mul2(h, dx), hy = mul2(h, dy);
+            acc[1] = add2(acc[1], hx);
+            acc[2] = add2(acc[2], hy);
+            acc[3] = fma2(hx, dx, acc[3]);
+            acc[4] = fma2(hx, dy, acc[4]);
+            acc[5] = fma2(hy, dy, acc[5]);
+#pragma unroll
+            for (int c = 0; c < CT; ++c) acc[N_MOMENTS + c] = fma2(gterm[1 + c], e, acc[N_MOMENTS + c]);
+        }
+        if (Cfg::TWO_LEVEL) {
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) tot[k] = add2(tot[k], acc[k]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) tot[k] = acc[k];
+        }
+        __syncthreads();
+        if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+    }
+
+    if (!valid) return;
+    float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n;
+#pragma unroll
+    for (int k = 0; k < N_MOMENTS; ++k) {
+        float lo, hi;
+        upk(tot[k], lo, hi);
+        dst[(long long)(a.moment_plane0 + k) * a.N] = lo + hi;
+    }
+#pragma unroll
+    for (int c = 0; c < CT; ++c) {
+        if (c < a.cr) {
+            float lo, hi;
+            upk(tot[N_MOMENTS + c], lo, hi);
+            dst[(long long)(a.color_plane0 + a.c0 + c) * a.N] = lo + hi;
+        }
+    }
+}
+
+template <int CT>
+static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    using Cfg = BwdCfg<CT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(splat_backward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((a.N + Cfg::THREADS - 1) / Cfg::THREADS), (unsigned)p.n_slab, (unsigned)a.B);
+    {
+        KernelTimer timer(K_BACKWARD, s);
+        splat_backward_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    switch (ct) {
+        case 1: return launch_one<1>(a, p, s);
+        case 2: return launch_one<2>(a, p, s);
+        case 3: return launch_one<3>(a, p, s);
+        case 4: return launch_one<4>(a, p, s);
+        case 8: return launch_one<8>(a, p, s);
+        case 16: return launch_one<16>(a, p, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int CT>
+static int occ(int device) {
+    using Cfg = BwdCfg<CT>;
+    static int cached[64];
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
+    cudaFuncSetAttribute(splat_backward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_backward_kernel<CT>, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+        n <= 0) {
+        cudaGetLastError();
+        n = Cfg::MIN_CTAS;
+    }
+    if (device >= 0 && device < 64) cached[device] = n;
+    return n;
+}
+
+int backward_ctas_per_sm(int ct, int device) {
+    switch (ct) {
+        case 1: return occ<1>(device);
+        case 2: return occ<2>(device);
+        case 3: return occ<3>(device);
+        case 4: return occ<4>(device);
+        case 8: return occ<8>(device);
+        default: return occ<16>(device);
+    }
+}
+int backward_threads(int) { return BwdCfg<3>::THREADS; }
+int backward_chunk_pairs(int ct) { return ct <= 4 ? BwdCfg<3>::CHUNK_PAIRS : BwdCfg<16>::CHUNK_PAIRS; }
+
+// ---------------------------------------------------------------------------
+// per-gaussian epilogue: slab partials -> gradients
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*N
+    if (i >= (long long)a.B * a.N) return;
+    const long long b = i / a.N, n = i - b * a.N;
+    float M[N_MOMENTS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const long long plane = a.N;
+    for (int s = 0; s < a.n_slab; ++s) {
+        const float* src = a.part + ((long long)s * a.B + b) * a.planes * plane + n;
+        for (int q = 0; q < a.n_chunks; ++q)
+#pragma unroll
+            for (int k = 0; k < N_MOMENTS; ++k) M[k] += src[(long long)(q * N_MOMENTS + k) * plane];
+    }
+    const float al = a.alpha[i];
+    for (int c = 0; c < a.C; ++c) {
+        float e = 0.f;
+        for (int s = 0; s < a.n_slab; ++s)
+            e += a.part[(((long long)s * a.B + b) * a.planes + a.n_chunks * N_MOMENTS + c) * plane + n];
+        a.d_colors[i * a.C + c] = al * e;
+    }
+    float c00, c01, c11;
+    CovInv ci;
+    float sx = 0.f, sy = 0.f;
+    if (a.kind == SHAPE_SCALE_ROT) {
+        sx = a.shape0[2 * i];
+        sy = a.shape0[2 * i + 1];
+        ci = cov_inv_from_scale_rot(sx, sy, a.shape1[i], a.eps);
+        c00 = ci.c00;
+        c01 = ci.c01;
+        c11 = ci.c11;
+    } else {
+        c00 = a.shape0[i];
+        c01 = a.shape1[i];
+        c11 = a.shape2[i];
+    }
+    a.d_alpha[i] = M[0];
+    a.d_pos[2 * i] = al * (c00 * M[1] + c01 * M[2]);
+    a.d_pos[2 * i + 1] = al * (c11 * M[2] + c01 * M[1]);
+    const float g00 = -0.5f * al * M[3], g01 = -al * M[4], g11 = -0.5f * al * M[5];
+    if (a.kind == SHAPE_COV_INV) {
+        a.d_shape0[i] = g00;
+        a.d_shape1[i] = g01;
+        a.d_shape2[i] = g11;
+    } else {
+        // c00 = d/det, c01 = -b/det, c11 = a/det with det = a*d - b^2
+        const float id = 1.0f / ci.det, id2 = id * id;
+        const float A_ = ci.a, B_ = ci.b, D_ = ci.d;
+        const float ga = g00 * (-D_ * D_ * id2) + g01 * (B_ * D_ * id2) + g11 * (id - A_ * D_ * id2);
+        const float gd = g00 * (id - A_ * D_ * id2) + g01 * (A_ * B_ * id2) + g11 * (-A_ * A_ * id2);
+        const float gb = g00 * (2.f * B_ * D_ * id2) + g01 * (-id - 2.f * B_ * B_ * id2) + g11 * (2.f * A_ * B_ * id2);
+        const float cs = ci.cs, sn = ci.sn;
+        a.d_shape0[2 * i] = 2.f * sx * (ga * cs * cs + gb * cs * sn + gd * sn * sn);
+        a.d_shape0[2 * i + 1] = 2.f * sy * (ga * sn * sn - gb * cs * sn + gd * cs * cs);
+        a.d_shape1[i] = -2.f * B_ * ga + (cs * cs - sn * sn) * (sx * sx - sy * sy) * gb + 2.f * B_ * gd;
+    }
+}
+
+cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s) {
+    const long long n = (long long)a.B * a.N;
+    if (n <= 0) return cudaSuccess;
+    {
+        KernelTimer timer(K_FINALIZE, s);
+        finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// coordinate gradients d_x, d_y (pixel-owner pass; only on request)
+//   d_x = sum_n cf*(2 c00 dx + 2 c01 dy) = -sum_n alpha*h*(c00 dx + c01 dy), likewise d_y
+// with the coefficients recovered from the pre-scaled geometry record.
+// ---------------------------------------------------------------------------
+constexpr int CG_THREADS = 128;
+constexpr int CG_CHUNK = 128;
+constexpr int CG_CMAX = 16;
+
+__global__ void __launch_bounds__(CG_THREADS) coord_grad_kernel(CoordGradArgs a) {
+    __shared__ float s_geo[CG_CHUNK][GEO_FLOATS];
+    __shared__ float s_col[CG_CHUNK][CG_CMAX];
+    const long long HW = (long long)a.H * a.W;
+    const int b = blockIdx.y;
+    const long long p = (long long)blockIdx.x * CG_THREADS + threadIdx.x;
+    const bool valid = p < HW;
+    const long long pc = valid ? p : HW - 1;
+    const long long h_ = pc / a.W, w_ = pc - h_ * a.W;
+    const float xv = a.x[b * a.xs_b + h_ * a.xs_h + w_ * a.xs_w];
+    const float yv = a.y[b * a.ys_b + h_ * a.ys_h + w_ * a.ys_w];
+    const float Sp = a.wsum[b * HW + pc] + a.eps;
+    float gS = 0.f;
+    for (int c = 0; c < a.C; ++c) {
+        const float g = a.gout[((long long)b * a.C + c) * HW + pc];
+        gS += (a.mode == IGS_GRAD_REFERENCE) ? g * g : (g / Sp) * a.out[((long long)b * a.C + c) * HW + pc];
+    }
+    gS = (a.mode == IGS_GRAD_REFERENCE) ? -gS / (Sp * Sp) : -gS;
+    float gxa = 0.f, gya = 0.f;
+    const float inv_k = 1.0f / EXP2_SCALE;
+    for (int c0 = 0; c0 < max(a.C, 1); c0 += CG_CMAX) {
+        const int cr = min(CG_CMAX, a.C - c0);
+        float gn[CG_CMAX];
+#pragma unroll
+        for (int c = 0; c < CG_CMAX; ++c)
+            gn[c] = (c < cr) ? a.gout[((long long)b * a.C + c0 + c) * HW + pc] / Sp : 0.f;
+        const float gS_pass = (c0 == 0) ? gS : 0.f;
+        for (int n0 = 0; n0 < a.N; n0 += CG_CHUNK) {
+            const int cnt = min(CG_CHUNK, a.N - n0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < cnt * GEO_FLOATS; i += CG_THREADS)
+                s_geo[i / GEO_FLOATS][i % GEO_FLOATS] = a.geo[((long long)b * a.N + n0) * GEO_FLOATS + i];
+            for (int i = threadIdx.x; i < cnt * CG_CMAX; i += CG_THREADS) {
+                const int g = i / CG_CMAX, c = i % CG_CMAX;
+                s_col[g][c] = (c < cr) ? a.colors[((long long)b * a.N + n0 + g) * a.C + c0 + c] : 0.f;
+            }
+            __syncthreads();
+            for (int g = 0; g < cnt; ++g) {
+                const float dx = xv - s_geo[g][0], dy = yv - s_geo[g][1];
+                const float A = s_geo[g][2], B2 = s_geo[g][3], Cq = s_geo[g][4], al = s_geo[g][5];
+                const float e = ex2f(dx * (A * dx + B2 * dy) + (Cq * dy) * dy);
+                float G = gS_pass;
+#pragma unroll
+                for (int c = 0; c < CG_CMAX; ++c) G = fmaf(gn[c], s_col[g][c], G);
+                const float hw = -(G * e) * al;
+                // c00 = A/k, c01 = B2/(2k), c11 = Cq/k
+                gxa = fmaf(hw, (A * dx + 0.5f * B2 * dy) * inv_k, gxa);
+                gya = fmaf(hw, (Cq * dy + 0.5f * B2 * dx) * inv_k, gya);
+            }
+        }
+    }
+    if (valid) {
+        a.d_x[b * HW + p] = gxa;
+        a.d_y[b * HW + p] = gya;
+    }
+}
+
+cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s) {
+    const long long HW = (long long)a.H * a.W;
+    if (HW <= 0 || a.B <= 0) return cudaSuccess;
+    dim3 grid((unsigned)((HW + CG_THREADS - 1) / CG_THREADS), (unsigned)a.B);
+    {
+        KernelTimer timer(K_COORD_GRAD, s);
+        coord_grad_kernel<<<grid, CG_THREADS, 0, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace igs

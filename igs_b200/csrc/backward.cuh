@@ -1,0 +1,79 @@
+// Argument blocks and launchers of the backward kernels.
+#pragma once
+
+#include "pack.cuh"
+#include "plan.cuh"
+
+namespace igs {
+
+// per-pixel upstream terms -> pair records, all channel chunks in one pass
+struct PixelTermArgs {
+    const float* x;
+    const float* y;
+    long long xs_b, xs_h, xs_w, ys_b, ys_h, ys_w;
+    const float* wsum;  // [B, HW]
+    const float* out;   // [B, C, HW]  (exact mode only)
+    const float* gout;  // [B, C, HW]
+    float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]
+    Chunks ch;
+    long long npairs;
+    int B, H, W, C;
+    int mode;
+    float eps;
+};
+
+struct BwdArgs {
+    const float* geo;     // [B, N, 8]
+    const float* colors;  // [B, N, C]
+    const float* prec;    // records of this chunk
+    float* part;          // [n_slab, B, planes, N]
+    int* status;
+    long long npairs, pairs_per_slab;
+    int B, N, C;
+    int c0, cr;
+    int planes;
+    int moment_plane0;  // first of this chunk's 6 moment planes
+    int color_plane0;   // first colour plane (+ c0 + c)
+};
+
+struct FinalizeArgs {
+    const float* part;  // [n_slab, B, planes, N]
+    const float* pos;
+    const float* shape0;  // scales | cov_inv_00
+    const float* shape1;  // rotations | cov_inv_01
+    const float* shape2;  // - | cov_inv_11
+    const float* alpha;
+    float* d_pos;     // [B,N,2]
+    float* d_shape0;  // d_scales [B,N,2] | d_cov_inv_00 [B,N]
+    float* d_shape1;  // d_rotations [B,N] | d_cov_inv_01
+    float* d_shape2;  // - | d_cov_inv_11
+    float* d_alpha;   // [B,N]
+    float* d_colors;  // [B,N,C]
+    int B, N, C, n_slab, planes, n_chunks;
+    int kind;
+    float eps;
+};
+
+// coordinate gradients (pixel-owner pass, only when the caller asks for d_x / d_y)
+struct CoordGradArgs {
+    const float* geo;
+    const float* colors;
+    const float* x;
+    const float* y;
+    long long xs_b, xs_h, xs_w, ys_b, ys_h, ys_w;
+    const float* wsum;
+    const float* out;
+    const float* gout;
+    float* d_x;  // [B, HW]
+    float* d_y;
+    int B, N, H, W, C;
+    int mode;
+    float eps;
+};
+
+cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s);
+cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
+cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
+
+}  // namespace igs

@@ -1,0 +1,278 @@
+// Forward splat kernel (sm_100a).
+//
+// One CTA owns a tile of pixels of one batch element and one range ("split") of
+// gaussians.  Each thread keeps PX pixels in registers as PX/2 packed pairs:
+// coordinates, the weight sum and CT colour numerators, all fp32.  Gaussian records
+// stream through shared memory in stages filled by 1-D bulk (TMA) copies that
+// complete on an mbarrier; every lane reads the same record, so the shared-memory
+// reads are broadcasts and the arithmetic is f32x2 throughout:
+//   dx = x - px, dy = y - py
+//   q  = dx*(A*dx + B2*dy) + (Cq*dy)*dy            (pre-scaled by -0.5*log2 e)
+//   e  = ex2(q);  S += e*alpha;  num_c += e*(alpha*colour_c)
+// i.e. 11 FMA-pipe instructions and one MUFU per gaussian x pixel at C = 3.
+// Epilogue: with a single split the CTA divides by (S + eps) itself, otherwise it
+// stores un-normalised partial sums that reduce_normalize_kernel adds in split order
+// (deterministic; no atomics anywhere).
+#include "forward.cuh"
+
+namespace igs {
+
+template <int CT>
+struct FwdCfg {
+    static constexpr int THREADS = 128;
+    static constexpr int PX = CT <= 4 ? 8 : (CT <= 8 ? 4 : 4);
+    static constexpr int CHUNK_G = 128;  // gaussians per stage
+    static constexpr int STAGES = 2;
+    static constexpr int MIN_CTAS = CT <= 4 ? 4 : (CT <= 8 ? 4 : 3);
+    static constexpr int RS = fwd_rec_floats(CT);
+    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
+};
+
+template <int CT>
+__global__ void __launch_bounds__(FwdCfg<CT>::THREADS, FwdCfg<CT>::MIN_CTAS) splat_forward_kernel(FwdArgs a) {
+    using Cfg = FwdCfg<CT>;
+    constexpr int T = Cfg::THREADS, NP = Cfg::PX / 2, G = Cfg::CHUNK_G, NS = Cfg::STAGES, RS = Cfg::RS;
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* stage_base = reinterpret_cast<float*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NS * G * RS * sizeof(float));
+    int* s_failed = reinterpret_cast<int*>(bars + NS);
+
+    const int tid = threadIdx.x;
+    const int b = blockIdx.z, split = blockIdx.y;
+    const long long HW = (long long)a.H * a.W;
+    const long long tile_base = (long long)blockIdx.x * (T * Cfg::PX);
+
+    // ---- pixel coordinates (arbitrary strides; read once) ----
+    f2 xx[NP], yy[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const long long p0 = tile_base + (long long)(j * T + tid) * 2;
+        float xv[2], yv[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long p = p0 + k;
+            if (p < HW) {
+                const long long h = p / a.W, w = p - h * a.W;
+                xv[k] = a.x[b * a.xs_b + h * a.xs_h + w * a.xs_w];
+                yv[k] = a.y[b * a.ys_b + h * a.ys_h + w * a.ys_w];
+            } else {
+                xv[k] = 0.f;
+                yv[k] = 0.f;
+            }
+        }
+        xx[j] = pk(xv[0], xv[1]);
+        yy[j] = pk(yv[0], yv[1]);
+    }
+
+    f2 S[NP], acc[NP][CT];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        S[j] = 0ull;
+#pragma unroll
+        for (int c = 0; c < CT; ++c) acc[j][c] = 0ull;
+    }
+
+    // ---- gaussian range of this split, streamed in stages ----
+    const int n_begin = split * a.per_split;
+    const int n_end = min(a.N, n_begin + a.per_split);
+    const int n_total = max(0, n_end - n_begin);
+    const int n_chunks = (n_total + G - 1) / G;
+    const float* src = a.frec + ((long long)b * a.N + n_begin) * RS;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+        *s_failed = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto issue = [&](int chunk) {
+        const int st = chunk % NS;
+        const int cnt = min(G, n_total - chunk * G);
+        const uint32_t bytes = (uint32_t)cnt * RS * sizeof(float);
+        mbar_expect_tx(&bars[st], bytes);
+        bulk_g2s(stage_base + (size_t)st * G * RS, src + (long long)chunk * G * RS, bytes, &bars[st]);
+    };
+    if (tid == 0) {
+        for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
+    }
+
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        const int st = chunk % NS;
+        const uint32_t parity = (chunk / NS) & 1;
+        if (!mbar_wait_bounded(&bars[st], parity)) *s_failed = 1;
+        __syncthreads();
+        if (*s_failed) {
+            // give copies still in flight a bounded chance to land before the CTA
+            // (and its shared memory) goes away, then report and leave
+            if (tid == 0) {
+                for (int c = chunk + 1; c < n_chunks && c < chunk + NS; ++c)
+                    mbar_wait_bounded(&bars[c % NS], (c / NS) & 1);
+                atomicOr(a.status, STATUS_WAIT_TIMEOUT);
+            }
+            return;
+        }
+        const int cnt = min(G, n_total - chunk * G);
+        const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * G * RS);
+#pragma unroll 2
+        for (int g = 0; g < cnt; ++g) {
+            const ulonglong2* r = rec + (size_t)g * (RS / 4);
+            const ulonglong2 r0 = r[0];  // {px,px},{py,py}
+            const ulonglong2 r1 = r[1];  // {A,A},{B2,B2}
+            const ulonglong2 r2 = r[2];  // {Cq,Cq},{al,al}
+            f2 col[CT + 1];
+#pragma unroll
+            for (int c = 0; c < (CT + 1) / 2; ++c) {
+                const ulonglong2 rc = r[3 + c];
+                col[2 * c] = rc.x;
+                col[2 * c + 1] = rc.y;
+            }
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                const f2 dx = sub2(xx[j], r0.x);
+                const f2 dy = sub2(yy[j], r0.y);
+                const f2 t = fma2(r1.x, dx, mul2(r1.y, dy));
+                const f2 v = mul2(mul2(r2.x, dy), dy);
+                const f2 e = ex2_2(fma2(dx, t, v));
+                S[j] = fma2(e, r2.y, S[j]);
+#pragma unroll
+                for (int c = 0; c < CT; ++c) acc[j][c] = fma2(e, col[c], acc[j][c]);
+            }
+        }
+        __syncthreads();  // every lane is done with this stage
+        if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+    }
+
+    // ---- epilogue ----
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const long long p0 = tile_base + (long long)(j * T + tid) * 2;
+        float s0, s1;
+        upk(S[j], s0, s1);
+        const float sv[2] = {s0, s1};
+        float num[CT][2];
+#pragma unroll
+        for (int c = 0; c < CT; ++c) upk(acc[j][c], num[c][0], num[c][1]);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long p = p0 + k;
+            if (p >= HW) continue;
+            if (a.in_kernel_normalize) {
+                const float den = sv[k] + a.eps;
+#pragma unroll
+                for (int c = 0; c < CT; ++c)
+                    if (c < a.cr) a.out[((long long)b * a.C + a.c0 + c) * HW + p] = num[c][k] / den;
+                if (a.write_s) a.wsum[(long long)b * HW + p] = sv[k];
+            } else {
+                float* dst = a.partial + ((long long)split * a.B + b) * (a.C + 1) * HW;
+#pragma unroll
+                for (int c = 0; c < CT; ++c)
+                    if (c < a.cr) dst[(long long)(a.c0 + c) * HW + p] = num[c][k];
+                if (a.write_s) dst[(long long)a.C * HW + p] = sv[k];
+            }
+        }
+    }
+}
+
+// Adds the per-split partial sums in split order and either divides (normalize) or
+// hands back the raw sums [B, C+1, HW].
+__global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
+    const long long HW = a.HW;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*HW
+    if (i >= (long long)a.B * HW) return;
+    const long long b = i / HW, p = i - b * HW;
+    const long long plane = (long long)(a.C + 1) * HW;
+    float s = 0.f;
+    for (int k = 0; k < a.n_split; ++k) s += a.partial[((long long)k * a.B + b) * plane + (long long)a.C * HW + p];
+    if (a.normalize) {
+        a.wsum[b * HW + p] = s;
+    } else {
+        a.out[b * plane + (long long)a.C * HW + p] = s;
+    }
+    const float den = s + a.eps;
+    for (int c = 0; c < a.C; ++c) {
+        float v = 0.f;
+        for (int k = 0; k < a.n_split; ++k) v += a.partial[((long long)k * a.B + b) * plane + (long long)c * HW + p];
+        if (a.normalize)
+            a.out[(b * a.C + c) * HW + p] = v / den;
+        else
+            a.out[b * plane + (long long)c * HW + p] = v;
+    }
+}
+
+template <int CT>
+static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+    using Cfg = FwdCfg<CT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)p.tiles, (unsigned)p.n_split, (unsigned)a.B);
+    {
+        KernelTimer timer(K_FORWARD, s);
+        splat_forward_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_forward_chunk(int ct, const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+    switch (ct) {
+        case 1: return launch_one<1>(a, p, s);
+        case 2: return launch_one<2>(a, p, s);
+        case 3: return launch_one<3>(a, p, s);
+        case 4: return launch_one<4>(a, p, s);
+        case 8: return launch_one<8>(a, p, s);
+        case 16: return launch_one<16>(a, p, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s) {
+    const long long n = (long long)a.B * a.HW;
+    if (n <= 0) return cudaSuccess;
+    {
+        KernelTimer timer(K_REDUCE, s);
+        reduce_normalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <int CT>
+static int occ(int device) {
+    using Cfg = FwdCfg<CT>;
+    static int cached[64];
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
+    cudaFuncSetAttribute(splat_forward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT>, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+        n <= 0) {
+        cudaGetLastError();
+        n = Cfg::MIN_CTAS;
+    }
+    if (device >= 0 && device < 64) cached[device] = n;
+    return n;
+}
+
+int forward_ctas_per_sm(int ct, int device) {
+    switch (ct) {
+        case 1: return occ<1>(device);
+        case 2: return occ<2>(device);
+        case 3: return occ<3>(device);
+        case 4: return occ<4>(device);
+        case 8: return occ<8>(device);
+        default: return occ<16>(device);
+    }
+}
+int forward_px_per_thread(int ct) { return ct <= 4 ? FwdCfg<3>::PX : (ct <= 8 ? FwdCfg<8>::PX : FwdCfg<16>::PX); }
+int forward_threads(int) { return FwdCfg<3>::THREADS; }
+int forward_chunk_g(int) { return FwdCfg<3>::CHUNK_G; }
+
+}  // namespace igs

@@ -1,0 +1,37 @@
+// Argument blocks and launchers of the forward kernels.
+#pragma once
+
+#include "plan.cuh"
+
+namespace igs {
+
+struct FwdArgs {
+    const float* frec;  // forward records of this channel chunk, [B, N, fwd_rec_floats(ct)]
+    const float* x;
+    const float* y;
+    long long xs_b, xs_h, xs_w, ys_b, ys_h, ys_w;  // element strides of x and y
+    float* out;      // [B, C, HW]      (in_kernel_normalize)
+    float* wsum;     // [B, HW]         (in_kernel_normalize && write_s)
+    float* partial;  // [n_split, B, C+1, HW] otherwise
+    int* status;
+    int B, N, H, W, C;
+    int c0, cr;  // first channel and real channel count of this chunk
+    int per_split;
+    int in_kernel_normalize;
+    int write_s;
+    float eps;
+};
+
+struct ReduceArgs {
+    const float* partial;  // [n_split, B, C+1, HW]
+    float* out;            // normalize: [B, C, HW]; else [B, C+1, HW]
+    float* wsum;           // normalize: [B, HW]
+    long long HW;
+    int B, C, n_split, normalize;
+    float eps;
+};
+
+cudaError_t launch_forward_chunk(int ct, const FwdArgs& a, const FwdPlan& p, cudaStream_t s);
+cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s);
+
+}  // namespace igs

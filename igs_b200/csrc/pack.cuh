@@ -1,0 +1,50 @@
+// Per-gaussian prologue: raw parameters -> kernel records.
+#pragma once
+
+#include "plan.cuh"
+
+namespace igs {
+
+enum ShapeKind { SHAPE_SCALE_ROT = 0, SHAPE_COV_INV = 1 };
+
+struct PackArgs {
+    const float* pos;     // [M,2]
+    const float* shape0;  // scales [M,2]  | cov_inv_00 [M]
+    const float* shape1;  // rotations [M] | cov_inv_01 [M]
+    const float* shape2;  // unused        | cov_inv_11 [M]
+    const float* alpha;   // [M]
+    const float* colors;  // [M,C]
+    float* geo;           // [M,8] or nullptr
+    float* frec[MAX_CHUNKS];  // per channel chunk, [M, fwd_rec_floats(ct)] or nullptr
+    Chunks ch;
+    long long M;
+    int C;
+    float eps;
+    int kind;
+};
+
+cudaError_t launch_pack(const PackArgs& a, cudaStream_t s);
+
+// scales, rotation -> inverse-covariance entries (closed form of R S (R S)^T + eps I
+// inverted); shared by the prologue and by the gradient epilogue.
+struct CovInv {
+    float c00, c01, c11;
+    float a, b, d, det, cs, sn;
+};
+
+__device__ __forceinline__ CovInv cov_inv_from_scale_rot(float sx, float sy, float theta, float eps) {
+    CovInv r;
+    sincosf(theta, &r.sn, &r.cs);
+    const float p = sx * sx, q = sy * sy;
+    r.a = r.cs * r.cs * p + r.sn * r.sn * q + eps;
+    r.b = r.cs * r.sn * (p - q);
+    r.d = r.sn * r.sn * p + r.cs * r.cs * q + eps;
+    // det(R diag(p,q) R^T + eps I) = (p+eps)(q+eps): rotation invariant, no cancellation
+    r.det = (p + eps) * (q + eps);
+    r.c00 = r.d / r.det;
+    r.c01 = -r.b / r.det;
+    r.c11 = r.a / r.det;
+    return r;
+}
+
+}  // namespace igs

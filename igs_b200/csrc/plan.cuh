@@ -1,0 +1,64 @@
+// Launch plans: how a call of shape (B, N, H, W, C) is cut into channel chunks,
+// pixel tiles x gaussian splits (forward) and gaussian groups x pixel slabs
+// (backward), and where each scratch array sits in the caller's workspace.
+#pragma once
+
+#include "common.cuh"
+
+namespace igs {
+
+constexpr int MAX_CHUNKS = 16;   // channel chunks of up to 16 -> C <= 256
+constexpr int STATUS_BYTES = 256;
+
+struct Chunks {
+    int n;
+    int c0[MAX_CHUNKS];  // first channel of the chunk
+    int cr[MAX_CHUNKS];  // real channels in the chunk
+    int ct[MAX_CHUNKS];  // kernel instantiation used (>= cr)
+};
+
+struct FwdPlan {
+    Chunks ch;
+    int threads;        // threads per CTA
+    int px_per_thread;  // pixels each thread owns (even)
+    int tile_px;        // threads * px_per_thread
+    int tiles;          // CTAs along the pixel axis, per batch element
+    int n_split;        // CTAs along the gaussian axis
+    int per_split;      // gaussians per split
+    int chunk_g;        // gaussians per shared-memory stage
+    int stages;
+    size_t off_frec[MAX_CHUNKS];
+    size_t off_partial;  // [n_split][B][C+1][HW] when n_split > 1 or not normalising in-kernel
+    size_t bytes;
+};
+
+struct BwdPlan {
+    Chunks ch;
+    int threads;           // gaussians per CTA (one per thread)
+    int n_slab;            // CTAs along the pixel axis
+    long long npairs;      // pixel pairs per batch element
+    long long pairs_per_slab;
+    int chunk_pairs;       // pixel pairs per shared-memory stage
+    int stages;
+    int planes;            // moment planes per (slab, batch): 6 per chunk + C
+    size_t off_geo;
+    size_t off_prec[MAX_CHUNKS];
+    size_t off_part;       // [n_slab][B][planes][N]
+    size_t off_xy;         // scratch of the coordinate-gradient kernel (none today)
+    size_t bytes;
+};
+
+int make_chunks(int C, Chunks* out);
+int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p);
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p);
+
+// occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
+int forward_ctas_per_sm(int ct, int device);
+int backward_ctas_per_sm(int ct, int device);
+int forward_px_per_thread(int ct);
+int forward_threads(int ct);
+int forward_chunk_g(int ct);
+int backward_threads(int ct);
+int backward_chunk_pairs(int ct);
+
+}  // namespace igs

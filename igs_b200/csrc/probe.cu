@@ -1,0 +1,132 @@
+// Micro-benchmarks that give the roofline its denominators on the GPU at hand:
+// the issue rate of the FP32 FMA pipe (scalar FFMA and packed f32x2 FMA) and of the
+// MUFU ex2 unit, each from a kernel that does nothing else.
+#include "common.cuh"
+
+namespace igs {
+
+constexpr int PROBE_THREADS = 256;
+constexpr int PROBE_CHAINS = 8;
+constexpr int PROBE_ITERS = 4096;
+
+__global__ void __launch_bounds__(PROBE_THREADS) probe_ffma_kernel(float* sink, float m, float c) {
+    float v[PROBE_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = (float)(threadIdx.x + k);
+    for (int it = 0; it < PROBE_ITERS; ++it) {
+#pragma unroll
+        for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = fmaf(v[k], m, c);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) s += v[k];
+    if (sink && s == 123.456f) sink[0] = s;
+}
+
+__global__ void __launch_bounds__(PROBE_THREADS) probe_ffma2_kernel(float* sink, float m, float c) {
+    f2 v[PROBE_CHAINS];
+    const f2 mm = pk(m, m), cc = pk(c, c);
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = pk((float)(threadIdx.x + k), (float)k);
+    for (int it = 0; it < PROBE_ITERS; ++it) {
+#pragma unroll
+        for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = fma2(v[k], mm, cc);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) {
+        float lo, hi;
+        upk(v[k], lo, hi);
+        s += lo + hi;
+    }
+    if (sink && s == 123.456f) sink[0] = s;
+}
+
+__global__ void __launch_bounds__(PROBE_THREADS) probe_ex2_kernel(float* sink, float c) {
+    float v[PROBE_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = -(float)(threadIdx.x + k) * 1e-3f;
+    for (int it = 0; it < PROBE_ITERS; ++it) {
+#pragma unroll
+        for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = ex2f(v[k]) - c;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) s += v[k];
+    if (sink && s == 123.456f) sink[0] = s;
+}
+
+// Runs `launch` a few times and returns the best per-launch time in seconds (<0 on error).
+template <typename F>
+static double best_time(F launch, cudaError_t* err) {
+    cudaEvent_t e0, e1;
+    *err = cudaEventCreate(&e0);
+    if (*err != cudaSuccess) return -1.0;
+    *err = cudaEventCreate(&e1);
+    if (*err != cudaSuccess) {
+        cudaEventDestroy(e0);
+        return -1.0;
+    }
+    double best = 1e30;
+    for (int rep = 0; rep < 6; ++rep) {
+        cudaEventRecord(e0, 0);
+        launch();
+        cudaEventRecord(e1, 0);
+        *err = cudaEventSynchronize(e1);
+        if (*err != cudaSuccess) break;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep >= 2 && ms * 1e-3 < best) best = ms * 1e-3;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (*err == cudaSuccess) *err = cudaGetLastError();
+    return best;
+}
+
+}  // namespace igs
+
+using namespace igs;
+
+extern "C" {
+
+int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s) {
+    if (!lane_instr_per_s) return IGS_ERR_ARG;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    const int blocks = sm_count(device) * 16;
+    cudaError_t err;
+    const double t = best_time(
+        [&] {
+            if (packed)
+                probe_ffma2_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
+            else
+                probe_ffma_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
+            count_launch();
+        },
+        &err);
+    if (err != cudaSuccess) return (int)err;
+    const double lanes = (double)blocks * PROBE_THREADS * PROBE_CHAINS * (double)PROBE_ITERS * (packed ? 2.0 : 1.0);
+    *lane_instr_per_s = lanes / t;
+    return IGS_OK;
+}
+
+int igs_probe_ex2_rate(int device, double* results_per_s) {
+    if (!results_per_s) return IGS_ERR_ARG;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    const int blocks = sm_count(device) * 16;
+    cudaError_t err;
+    const double t = best_time(
+        [&] {
+            probe_ex2_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.5f);
+            count_launch();
+        },
+        &err);
+    if (err != cudaSuccess) return (int)err;
+    // each iteration also issues one FADD per chain; the MUFU unit (16/clk/SM) is the slower pipe
+    *results_per_s = (double)blocks * PROBE_THREADS * PROBE_CHAINS * (double)PROBE_ITERS / t;
+    return IGS_OK;
+}
+
+}  // extern "C"

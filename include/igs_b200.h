@@ -1,0 +1,171 @@
+/*
+ * igs_b200 -- C ABI of the sm_100a (B200) implementation of IGS's differentiable,
+ * weight-normalised 2D gaussian splatting (forward and backward).
+ *
+ * The reference (KohakuBlueleaf/IGS) has no FFI of its own: its inner op is a
+ * torch.autograd.Function written in Python.  The entry points below are what a
+ * binding for that op would call; each cites the reference code it replaces
+ * (paths relative to the reference tree).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on `device` unless stated otherwise; all
+ *     tensors are fp32 and contiguous except x / y, which carry element strides;
+ *   - `stream` is a cudaStream_t passed as void*; nothing synchronises the stream
+ *     except igs_read_status and igs_probe_*;
+ *   - the library never allocates: scratch comes in through `workspace`, whose
+ *     size igs_workspace_bytes reports; the first 256 bytes of a workspace hold a
+ *     status word the kernels set if one of their bounded waits gives up;
+ *   - return value: 0 = ok, negative = IGS_ERR_* argument error, positive = a
+ *     cudaError_t from launching.  No entry point throws or aborts.
+ *   - entry points may be called from any host thread (autograd runs backward on
+ *     its own thread); they select `device` themselves and restore the previous one.
+ *
+ * Layouts (the reference's):  positions [B,N,2], scales [B,N,2], rotations [B,N],
+ * alphas [B,N], colors [B,N,C], cov_inv_xx [B,N], x / y logical [B,H,W] with strides
+ * (batch, row, column) in elements, out / gout [B,C,H,W], wsum [B,H,W].
+ */
+#ifndef IGS_B200_H
+#define IGS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IGS_OK 0
+#define IGS_ERR_ARG (-1)        /* null pointer, negative size, unsupported value */
+#define IGS_ERR_WORKSPACE (-2)  /* workspace missing or smaller than igs_workspace_bytes */
+#define IGS_ERR_LIMIT (-3)      /* size beyond a documented limit */
+#define IGS_ERR_DEVICE (-4)     /* device cannot be selected or is not sm_100 */
+#define IGS_ERR_STATUS (-5)     /* a kernel reported a timed-out wait (igs_read_status) */
+
+/* gradient of the per-pixel normalisation term, see igs_backward_* */
+#define IGS_GRAD_REFERENCE 0  /* gS = -sum_c g_c^2 / S^2, src/igs/gs2d.py:370 (and :176) */
+#define IGS_GRAD_EXACT 1      /* gS = -sum_c (g_c/S) out_c, autograd of src/igs/gs2d.py:24-44 */
+
+int igs_version(void);
+const char* igs_strerror(int code);
+
+/* Number of kernels this library has launched in this process so far. */
+long long igs_launch_count(void);
+
+/*
+ * Scratch sizes for one forward / one backward call of the given shape on `device`.
+ * Either output pointer may be NULL.
+ */
+int igs_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* forward_bytes,
+                        size_t* backward_bytes);
+
+/*
+ * Forward from scales and rotations.  Replaces GaussianSplatting2D.render with
+ * fused=True (src/igs/gs2d.py:524-596): scales, rotations -> inverse covariance
+ * (:549-580), then the fused splat (:275-337).
+ *   normalize != 0: out [B,C,H,W] = numerator / (weight_sum + eps), wsum [B,H,W] =
+ *                   weight_sum without eps (what the reference saves, :334);
+ *   normalize == 0: out receives the UN-normalised sums [B,C+1,H,W] (C numerator
+ *                   planes, then the weight-sum plane), wsum is ignored.  Used when
+ *                   gaussians are sharded across GPUs and the sums are all-reduced
+ *                   before igs_normalize.
+ */
+int igs_forward_sr(const float* positions, const float* scales, const float* rotations,
+                   const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
+                   const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C,
+                   float eps, int normalize, float* out, float* wsum, void* workspace,
+                   size_t workspace_bytes, int device, void* stream);
+
+/*
+ * Forward from inverse-covariance entries.  Replaces
+ * GaussianSplatting2DChunkedKernel.forward / GaussianSplatting2DKernel.forward
+ * (src/igs/gs2d.py:275-337, :68-144), the entry the reference's benchmark calls
+ * directly (scripts/profiling.py:97-100).  cov_inv may be indefinite.
+ */
+int igs_forward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01,
+                    const float* cov_inv_11, const float* alphas, const float* colors, const float* x,
+                    const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
+                    int H, int W, int C, float eps, int normalize, float* out, float* wsum,
+                    void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
+ * sums [B,C+1,H,W] -> out [B,C,H,W], wsum [B,H,W].  The division of
+ * src/igs/gs2d.py:323, split off so that an all-reduce can run in between.
+ */
+int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, float* out, float* wsum,
+                  int device, void* stream);
+
+/*
+ * Backward to scales and rotations.  Replaces
+ * GaussianSplatting2DChunkedKernel.backward (src/igs/gs2d.py:339-465) followed by
+ * autograd through the covariance construction (:549-580).
+ *   wsum: as written by the forward; out: the forward image, read only when
+ *   grad_mode == IGS_GRAD_EXACT (may be NULL otherwise); gout [B,C,H,W] is NOT
+ *   modified (the reference divides it in place, :371).
+ *   d_x, d_y [B,H,W] contiguous, both NULL to skip (src/igs/gs2d.py:433-434).
+ */
+int igs_backward_sr(const float* positions, const float* scales, const float* rotations,
+                    const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
+                    const float* y, const int64_t* y_strides, const float* wsum, const float* out,
+                    const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
+                    float* d_positions, float* d_scales, float* d_rotations, float* d_alphas,
+                    float* d_colors, float* d_x, float* d_y, void* workspace, size_t workspace_bytes,
+                    int device, void* stream);
+
+/*
+ * Backward to inverse-covariance entries.  Replaces
+ * GaussianSplatting2DChunkedKernel.backward (src/igs/gs2d.py:339-465); returns the
+ * same eight gradients (:455-465).
+ */
+int igs_backward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01,
+                     const float* cov_inv_11, const float* alphas, const float* colors, const float* x,
+                     const int64_t* x_strides, const float* y, const int64_t* y_strides,
+                     const float* wsum, const float* out, const float* gout, int B, int N, int H, int W,
+                     int C, float eps, int grad_mode, float* d_positions, float* d_cov_inv_00,
+                     float* d_cov_inv_01, float* d_cov_inv_11, float* d_alphas, float* d_colors,
+                     float* d_x, float* d_y, void* workspace, size_t workspace_bytes, int device,
+                     void* stream);
+
+/*
+ * Synchronises `stream`, copies the workspace's status word to *host_status
+ * (HOST pointer) and returns IGS_ERR_STATUS if it is non-zero.
+ */
+int igs_read_status(const void* workspace, int device, void* stream, int* host_status);
+
+/*
+ * Launch geometry the library would use (for reports): pixels per forward CTA,
+ * gaussian splits, backward threads per CTA and pixel slabs.  Any pointer may be NULL.
+ */
+int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_tile_pixels,
+                      int* fwd_splits, int* bwd_threads, int* bwd_slabs);
+
+/*
+ * Per-kernel device timing for reports.  While enabled, every kernel launch of the
+ * library is bracketed by CUDA events recorded on the launch's own stream;
+ * igs_profile_read waits for the recorded events and returns the accumulated device
+ * time and launch count of one kernel since the last igs_profile_reset.  The devices
+ * that recorded events must still be alive when reading.  Off by default.
+ */
+#define IGS_KERNEL_PACK 0         /* per-gaussian prologue */
+#define IGS_KERNEL_FORWARD 1      /* forward splat */
+#define IGS_KERNEL_REDUCE 2       /* split reduction / normalisation */
+#define IGS_KERNEL_PIXEL_TERMS 3  /* per-pixel upstream terms */
+#define IGS_KERNEL_BACKWARD 4     /* backward splat */
+#define IGS_KERNEL_FINALIZE 5     /* per-gaussian gradient epilogue */
+#define IGS_KERNEL_COORD_GRAD 6   /* d_x, d_y */
+#define IGS_KERNEL_COUNT 7
+int igs_profile_enable(int on);
+int igs_profile_reset(void);
+int igs_profile_read(int kernel_id, double* total_ms, long long* launches);
+
+/*
+ * Micro-benchmarks used as roofline denominators; each synchronises and writes a
+ * rate to a HOST double: fp32 lane-instructions per second of the FMA pipe
+ * (packed = with f32x2 instructions) and MUFU ex2 results per second.
+ */
+int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s);
+int igs_probe_ex2_rate(int device, double* results_per_s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IGS_B200_H */

@@ -1,0 +1,68 @@
+"""The C-ABI library loads without a GPU and exports every function the header declares
+(no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tests._util import ROOT
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "igs_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(igs_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = _declared()
+    for must in ("igs_forward_sr", "igs_forward_cov", "igs_backward_sr", "igs_backward_cov", "igs_normalize",
+                 "igs_workspace_bytes", "igs_strerror", "igs_version", "igs_launch_count", "igs_read_status"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from igs_b200 import _lib, build
+
+    build.build()
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in _declared():
+        assert hasattr(lib, name), f"{name} declared in include/igs_b200.h but not exported"
+    # and the Python binding declares a signature for each of them
+    assert sorted(_lib.SIGNATURES) == _declared()
+
+
+def test_error_strings_and_argument_errors_without_gpu():
+    from igs_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.igs_version() >= 100
+    assert b"workspace" in lib.igs_strerror(-2)
+    assert b"ok" == lib.igs_strerror(0)
+    # argument validation happens before any CUDA call
+    assert lib.igs_profile_read(99, None, None) == -1
+    assert lib.igs_forward_sr(None, None, None, None, None, None, None, None, None, 1, 1, 4, 4, 0, 1e-6, 1,
+                              None, None, None, 0, 0, None) == -1
+
+
+def test_product_package_never_imports_the_oracle():
+    """The oracle is test infrastructure; nothing under igs_b200/ may reach it."""
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "igs_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src, f"{f} mentions the oracle"
+
+
+def test_cpu_tensors_are_rejected_not_emulated():
+    import torch
+
+    from igs_b200.gs2d import GaussianSplatting2DKernel, gaussian_splatting_2d
+
+    z = torch.zeros
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        gaussian_splatting_2d(z(1, 2, 2), z(1, 2, 3), z(1, 2, 2) + 1, z(1, 2), z(1, 2), z(1, 1, 3, 3), z(1, 1, 3, 3))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        GaussianSplatting2DKernel.apply(z(1, 1, 3, 3), z(1, 1, 3, 3), z(1, 2, 2), z(1, 2, 1, 1), z(1, 2, 1, 1),
+                                        z(1, 2, 1, 1), z(1, 2), z(1, 2, 3))

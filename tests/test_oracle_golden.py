@@ -82,3 +82,19 @@ def test_empty_inputs():
     out, wsum = so.forward(x, y, np.zeros((1, 0, 2)), np.zeros((1, 0)), np.zeros((1, 0)), np.zeros((1, 0)),
                            np.zeros((1, 0)), np.zeros((1, 0, 3)), 1e-6, np.float32)
     assert out.shape == (1, 3, 4, 6) and not out.any() and not wsum.any()
+
+
+@pytest.mark.parametrize("name", ["render_small_c3", "render_narrow_c3", "render_c17", "render_n1"])
+def test_chunked_torch_port_matches_reference(name):
+    """The torch restatement that is timed as the CPU baseline gives the reference's numbers."""
+    import torch
+
+    from oracle import chunked_port as cp
+
+    g = load_golden(name)
+    t = {k: torch.from_numpy(g[k]) for k in ("positions", "colors", "scales", "rotations", "alphas", "x", "y", "gout")}
+    out, grads = cp.render_fwd_bwd(t["positions"], t["colors"], t["scales"], t["rotations"], t["alphas"], t["x"],
+                                   t["y"], lambda o: t["gout"], float(g["eps"]))
+    assert_close(out.numpy(), g["out"], 1e-5, f"{name} image")
+    for k, v in grads.items():
+        assert_close(v.numpy(), g["g_" + k], 2e-5, f"{name} d_{k}")
