@@ -155,10 +155,12 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
     const long long HW = (long long)H * W;
     const int ct = p->ch.ct[0];
     p->threads = backward_threads(ct);
+    p->gauss_per_thread = backward_gauss_per_thread(ct);
     p->chunk_pairs = backward_chunk_pairs(ct);
     p->stages = 2;
     p->npairs = (HW + 1) / 2;
-    const long long groups = ((long long)N + p->threads - 1) / p->threads;
+    const long long per_cta = (long long)p->threads * p->gauss_per_thread;
+    const long long groups = ((long long)N + per_cta - 1) / per_cta;
     const long long slots = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
     const long long base = groups * (B > 0 ? B : 1);
     int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);

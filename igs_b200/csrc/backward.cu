@@ -21,6 +21,8 @@
 // and, for the scale/rotation entry, chains d_c** through the closed-form inverse.
 #include "backward.cuh"
 
+#include <cstdlib>
+
 namespace igs {
 
 // ---------------------------------------------------------------------------
@@ -96,21 +98,28 @@ cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s) {
 // ---------------------------------------------------------------------------
 // main backward kernel
 // ---------------------------------------------------------------------------
-template <int CT>
+// GPT = gaussians per thread.  A pair record costs one shared-memory read per thread
+// whatever GPT is, and a 16-byte broadcast read occupies the shared-memory return path
+// for four cycles per warp, so with GPT = 1 the 3 reads per pixel pair (C = 3) need
+// more return-path cycles than the 22 f32x2 instructions need FMA-pipe cycles; GPT = 2
+// halves the reads per evaluation and makes the FMA pipe the limiter again.
+template <int CT, int GPT>
 struct BwdCfg {
     static constexpr int THREADS = 128;
+    static constexpr int GAUSS_PER_CTA = THREADS * GPT;
     static constexpr int CHUNK_PAIRS = CT <= 4 ? 256 : 128;
     static constexpr int STAGES = 2;
-    static constexpr int MIN_CTAS = CT <= 4 ? 5 : (CT <= 8 ? 4 : 3);
-    static constexpr bool TWO_LEVEL = CT <= 4;
+    static constexpr int MIN_CTAS = GPT == 2 ? 4 : (CT <= 4 ? 5 : (CT <= 8 ? 4 : 3));
+    static constexpr bool TWO_LEVEL = (CT <= 4 && GPT == 1);
     static constexpr int RS = bwd_rec_floats(CT);
     static constexpr int NACC = N_MOMENTS + CT;
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_PAIRS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
 };
 
-template <int CT>
-__global__ void __launch_bounds__(BwdCfg<CT>::THREADS, BwdCfg<CT>::MIN_CTAS) splat_backward_kernel(BwdArgs a) {
-    using Cfg = BwdCfg<CT>;
+template <int CT, int GPT>
+__global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN_CTAS)
+    splat_backward_kernel(BwdArgs a) {
+    using Cfg = BwdCfg<CT, GPT>;
     constexpr int T = Cfg::THREADS, PC = Cfg::CHUNK_PAIRS, NS = Cfg::STAGES, RS = Cfg::RS, NACC = Cfg::NACC;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -120,25 +129,33 @@ __global__ void __launch_bounds__(BwdCfg<CT>::THREADS, BwdCfg<CT>::MIN_CTAS) spl
 
     const int tid = threadIdx.x;
     const int b = blockIdx.z, slab = blockIdx.y;
-    const int n = blockIdx.x * T + tid;
-    const bool valid = n < a.N;
-    const int nn = valid ? n : a.N - 1;
 
-    // ---- this thread's gaussian ----
-    const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
-    const float4 g0 = gp[0], g1 = gp[1];
-    const f2 px = pk(g0.x, g0.x), py = pk(g0.y, g0.y);
-    const f2 A = pk(g0.z, g0.z), B2 = pk(g0.w, g0.w), Cq = pk(g1.x, g1.x);
-    f2 col[CT];
+    // ---- this thread's gaussians ----
+    int n[GPT];
+    f2 px[GPT], py[GPT], A[GPT], B2[GPT], Cq[GPT], col[GPT][CT];
 #pragma unroll
-    for (int c = 0; c < CT; ++c) {
-        const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
-        col[c] = pk(v, v);
+    for (int g = 0; g < GPT; ++g) {
+        n[g] = blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        const int nn = n[g] < a.N ? n[g] : a.N - 1;
+        const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
+        const float4 g0 = gp[0], g1 = gp[1];
+        px[g] = pk(g0.x, g0.x);
+        py[g] = pk(g0.y, g0.y);
+        A[g] = pk(g0.z, g0.z);
+        B2[g] = pk(g0.w, g0.w);
+        Cq[g] = pk(g1.x, g1.x);
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
+            col[g][c] = pk(v, v);
+        }
     }
 
-    f2 tot[NACC];
+    f2 tot[GPT][NACC];
 #pragma unroll
-    for (int k = 0; k < NACC; ++k) tot[k] = 0ull;
+    for (int g = 0; g < GPT; ++g)
+#pragma unroll
+        for (int k = 0; k < NACC; ++k) tot[g][k] = 0ull;
 
     // ---- pixel slab, streamed in stages ----
     const long long pair_begin = (long long)slab * a.pairs_per_slab;
@@ -181,14 +198,12 @@ __global__ void __launch_bounds__(BwdCfg<CT>::THREADS, BwdCfg<CT>::MIN_CTAS) spl
         const int cnt = min(PC, n_total - chunk * PC);
         const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * PC * RS);
 
-        f2 acc[NACC];
-        if (Cfg::TWO_LEVEL) {
+        f2 acc[GPT][NACC];
 #pragma unroll
-            for (int k = 0; k < NACC; ++k) acc[k] = 0ull;
-        } else {
+        for (int g = 0; g < GPT; ++g)
 #pragma unroll
-            for (int k = 0; k < NACC; ++k) acc[k] = tot[k];
-        }
+            for (int k = 0; k < NACC; ++k) acc[g][k] = Cfg::TWO_LEVEL ? 0ull : tot[g][k];
+
 #pragma unroll 2
         for (int i = 0; i < cnt; ++i) {
             const ulonglong2* r = rec + (size_t)i * (RS / 4);
@@ -200,95 +215,100 @@ __global__ void __launch_bounds__(BwdCfg<CT>::THREADS, BwdCfg<CT>::MIN_CTAS) spl
                 gterm[2 * c] = rc.x;
                 gterm[2 * c + 1] = rc.y;
             }
-            const f2 dx = sub2(r0.x, px);
-            const f2 dy = sub2(r0.y, py);
-            const f2 t = fma2(A, dx, mul2(B2, dy));
-            const f2 v = mul2(mul2(Cq, dy), dy);
-            const f2 e = ex2_2(fma2(dx, t, v));
-            f2 G = gterm[0];
 #pragma unroll
-            for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[c], G);
-            const f2 h = mul2(G, e);
-            acc[0] = add2(acc[0], h);
-            const f2 hx = mul2(h, dx), hy = mul2(h, dy);
-            acc[1] = add2(acc[1], hx);
-            acc[2] = add2(acc[2], hy);
-            acc[3] = fma2(hx, dx, acc[3]);
-            acc[4] = fma2(hx, dy, acc[4]);
-            acc[5] = fma2(hy, dy, acc[5]);
+            for (int g = 0; g < GPT; ++g) {
+                const f2 dx = sub2(r0.x, px[g]);
+                const f2 dy = sub2(r0.y, py[g]);
+                const f2 t = fma2(A[g], dx, mul2(B2[g], dy));
+                const f2 v = mul2(mul2(Cq[g], dy), dy);
+                const f2 e = ex2_2(fma2(dx, t, v));
+                f2 G = gterm[0];
 #pragma unroll
-            for (int c = 0; c < CT; ++c) acc[N_MOMENTS + c] = fma2(gterm[1 + c], e, acc[N_MOMENTS + c]);
+                for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[g][c], G);
+                const f2 h = mul2(G, e);
+                acc[g][0] = add2(acc[g][0], h);
+                const f2 hx = mul2(h, dx), hy = mul2(h, dy);
+                acc[g][1] = add2(acc[g][1], hx);
+                acc[g][2] = add2(acc[g][2], hy);
+                acc[g][3] = fma2(hx, dx, acc[g][3]);
+                acc[g][4] = fma2(hx, dy, acc[g][4]);
+                acc[g][5] = fma2(hy, dy, acc[g][5]);
+#pragma unroll
+                for (int c = 0; c < CT; ++c) acc[g][N_MOMENTS + c] = fma2(gterm[1 + c], e, acc[g][N_MOMENTS + c]);
+            }
         }
-        if (Cfg::TWO_LEVEL) {
 #pragma unroll
-            for (int k = 0; k < NACC; ++k) tot[k] = add2(tot[k], acc[k]);
-        } else {
+        for (int g = 0; g < GPT; ++g)
 #pragma unroll
-            for (int k = 0; k < NACC; ++k) tot[k] = acc[k];
-        }
+            for (int k = 0; k < NACC; ++k) tot[g][k] = Cfg::TWO_LEVEL ? add2(tot[g][k], acc[g][k]) : acc[g][k];
         __syncthreads();
         if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
     }
 
-    if (!valid) return;
-    float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n;
 #pragma unroll
-    for (int k = 0; k < N_MOMENTS; ++k) {
-        float lo, hi;
-        upk(tot[k], lo, hi);
-        dst[(long long)(a.moment_plane0 + k) * a.N] = lo + hi;
-    }
+    for (int g = 0; g < GPT; ++g) {
+        if (n[g] >= a.N) continue;
+        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n[g];
 #pragma unroll
-    for (int c = 0; c < CT; ++c) {
-        if (c < a.cr) {
+        for (int k = 0; k < N_MOMENTS; ++k) {
             float lo, hi;
-            upk(tot[N_MOMENTS + c], lo, hi);
-            dst[(long long)(a.color_plane0 + a.c0 + c) * a.N] = lo + hi;
+            upk(tot[g][k], lo, hi);
+            dst[(long long)(a.moment_plane0 + k) * a.N] = lo + hi;
+        }
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            if (c < a.cr) {
+                float lo, hi;
+                upk(tot[g][N_MOMENTS + c], lo, hi);
+                dst[(long long)(a.color_plane0 + a.c0 + c) * a.N] = lo + hi;
+            }
         }
     }
 }
 
-template <int CT>
+template <int CT, int GPT>
 static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
-    using Cfg = BwdCfg<CT>;
+    using Cfg = BwdCfg<CT, GPT>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(splat_backward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Cfg::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(splat_backward_kernel<CT, GPT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    dim3 grid((unsigned)((a.N + Cfg::THREADS - 1) / Cfg::THREADS), (unsigned)p.n_slab, (unsigned)a.B);
+    dim3 grid((unsigned)((a.N + Cfg::GAUSS_PER_CTA - 1) / Cfg::GAUSS_PER_CTA), (unsigned)p.n_slab, (unsigned)a.B);
     {
         KernelTimer timer(K_BACKWARD, s);
-        splat_backward_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_backward_kernel<CT, GPT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    const bool two = p.gauss_per_thread == 2;
     switch (ct) {
-        case 1: return launch_one<1>(a, p, s);
-        case 2: return launch_one<2>(a, p, s);
-        case 3: return launch_one<3>(a, p, s);
-        case 4: return launch_one<4>(a, p, s);
-        case 8: return launch_one<8>(a, p, s);
-        case 16: return launch_one<16>(a, p, s);
+        case 1: return two ? launch_one<1, 2>(a, p, s) : launch_one<1, 1>(a, p, s);
+        case 2: return two ? launch_one<2, 2>(a, p, s) : launch_one<2, 1>(a, p, s);
+        case 3: return two ? launch_one<3, 2>(a, p, s) : launch_one<3, 1>(a, p, s);
+        case 4: return two ? launch_one<4, 2>(a, p, s) : launch_one<4, 1>(a, p, s);
+        case 8: return launch_one<8, 1>(a, p, s);
+        case 16: return launch_one<16, 1>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
 
-template <int CT>
+template <int CT, int GPT>
 static int occ(int device) {
-    using Cfg = BwdCfg<CT>;
+    using Cfg = BwdCfg<CT, GPT>;
     static int cached[64];
     if (device >= 0 && device < 64 && cached[device]) return cached[device];
-    cudaFuncSetAttribute(splat_backward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    cudaFuncSetAttribute(splat_backward_kernel<CT, GPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_backward_kernel<CT>, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_backward_kernel<CT, GPT>, Cfg::THREADS, Cfg::SMEM) !=
+            cudaSuccess ||
         n <= 0) {
         cudaGetLastError();
         n = Cfg::MIN_CTAS;
@@ -297,18 +317,29 @@ static int occ(int device) {
     return n;
 }
 
+int backward_gauss_per_thread(int ct) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("IGS_B200_BWD_GPT");  // development knob: 1 or 2
+        forced = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+    }
+    if (ct > 4) return 1;
+    return forced ? forced : 2;
+}
+
 int backward_ctas_per_sm(int ct, int device) {
+    const bool two = backward_gauss_per_thread(ct) == 2;
     switch (ct) {
-        case 1: return occ<1>(device);
-        case 2: return occ<2>(device);
-        case 3: return occ<3>(device);
-        case 4: return occ<4>(device);
-        case 8: return occ<8>(device);
-        default: return occ<16>(device);
+        case 1: return two ? occ<1, 2>(device) : occ<1, 1>(device);
+        case 2: return two ? occ<2, 2>(device) : occ<2, 1>(device);
+        case 3: return two ? occ<3, 2>(device) : occ<3, 1>(device);
+        case 4: return two ? occ<4, 2>(device) : occ<4, 1>(device);
+        case 8: return occ<8, 1>(device);
+        default: return occ<16, 1>(device);
     }
 }
-int backward_threads(int) { return BwdCfg<3>::THREADS; }
-int backward_chunk_pairs(int ct) { return ct <= 4 ? BwdCfg<3>::CHUNK_PAIRS : BwdCfg<16>::CHUNK_PAIRS; }
+int backward_threads(int) { return 128; }
+int backward_chunk_pairs(int ct) { return ct <= 4 ? 256 : 128; }
 
 // ---------------------------------------------------------------------------
 // per-gaussian epilogue: slab partials -> gradients

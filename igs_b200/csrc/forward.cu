@@ -15,22 +15,29 @@
 // (deterministic; no atomics anywhere).
 #include "forward.cuh"
 
+#include <cstdlib>
+
 namespace igs {
 
-template <int CT>
+// PX = pixels per thread.  A forward record costs 5 sixteen-byte broadcast reads per
+// thread whatever PX is (20 cycles of the shared-memory return path per warp), against
+// 11 f32x2 instructions per pixel pair; more pixels per thread move the balance from
+// the return path to the FMA pipe at the price of registers (occupancy).
+template <int CT, int PX_>
 struct FwdCfg {
     static constexpr int THREADS = 128;
-    static constexpr int PX = CT <= 4 ? 8 : (CT <= 8 ? 4 : 4);
+    static constexpr int PX = PX_;
     static constexpr int CHUNK_G = 128;  // gaussians per stage
     static constexpr int STAGES = 2;
-    static constexpr int MIN_CTAS = CT <= 4 ? 4 : (CT <= 8 ? 4 : 3);
+    static constexpr int MIN_CTAS = (PX_ * (CT + 3) >= 64) ? 3 : 4;
     static constexpr int RS = fwd_rec_floats(CT);
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
 };
 
-template <int CT>
-__global__ void __launch_bounds__(FwdCfg<CT>::THREADS, FwdCfg<CT>::MIN_CTAS) splat_forward_kernel(FwdArgs a) {
-    using Cfg = FwdCfg<CT>;
+template <int CT, int PX_>
+__global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN_CTAS)
+    splat_forward_kernel(FwdArgs a) {
+    using Cfg = FwdCfg<CT, PX_>;
     constexpr int T = Cfg::THREADS, NP = Cfg::PX / 2, G = Cfg::CHUNK_G, NS = Cfg::STAGES, RS = Cfg::RS;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(FwdCfg<CT>::THREADS, FwdCfg<CT>::MIN_CTAS) spl
         }
         const int cnt = min(G, n_total - chunk * G);
         const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * G * RS);
-#pragma unroll 2
+#pragma unroll(Cfg::PX >= 16 ? 1 : 2)
         for (int g = 0; g < cnt; ++g) {
             const ulonglong2* r = rec + (size_t)g * (RS / 4);
             const ulonglong2 r0 = r[0];  // {px,px},{py,py}
@@ -201,35 +208,47 @@ __global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
     }
 }
 
-template <int CT>
+template <int CT, int PX_>
 static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
-    using Cfg = FwdCfg<CT>;
+    using Cfg = FwdCfg<CT, PX_>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Cfg::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     dim3 grid((unsigned)p.tiles, (unsigned)p.n_split, (unsigned)a.B);
     {
         KernelTimer timer(K_FORWARD, s);
-        splat_forward_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_forward_kernel<CT, PX_><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
 }
 
+int forward_px_per_thread(int ct) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("IGS_B200_FWD_PX");  // development knob: 8 or 16
+        forced = e ? atoi(e) : 0;
+        if (forced != 8 && forced != 16) forced = 0;
+    }
+    if (ct > 4) return 4;
+    return forced ? forced : 8;
+}
+
 cudaError_t launch_forward_chunk(int ct, const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+    const bool wide = p.px_per_thread == 16;
     switch (ct) {
-        case 1: return launch_one<1>(a, p, s);
-        case 2: return launch_one<2>(a, p, s);
-        case 3: return launch_one<3>(a, p, s);
-        case 4: return launch_one<4>(a, p, s);
-        case 8: return launch_one<8>(a, p, s);
-        case 16: return launch_one<16>(a, p, s);
+        case 1: return wide ? launch_one<1, 16>(a, p, s) : launch_one<1, 8>(a, p, s);
+        case 2: return wide ? launch_one<2, 16>(a, p, s) : launch_one<2, 8>(a, p, s);
+        case 3: return wide ? launch_one<3, 16>(a, p, s) : launch_one<3, 8>(a, p, s);
+        case 4: return wide ? launch_one<4, 16>(a, p, s) : launch_one<4, 8>(a, p, s);
+        case 8: return launch_one<8, 4>(a, p, s);
+        case 16: return launch_one<16, 4>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -245,14 +264,15 @@ cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-template <int CT>
+template <int CT, int PX_>
 static int occ(int device) {
-    using Cfg = FwdCfg<CT>;
+    using Cfg = FwdCfg<CT, PX_>;
     static int cached[64];
     if (device >= 0 && device < 64 && cached[device]) return cached[device];
-    cudaFuncSetAttribute(splat_forward_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    cudaFuncSetAttribute(splat_forward_kernel<CT, PX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT>, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT, PX_>, Cfg::THREADS, Cfg::SMEM) !=
+            cudaSuccess ||
         n <= 0) {
         cudaGetLastError();
         n = Cfg::MIN_CTAS;
@@ -262,17 +282,17 @@ static int occ(int device) {
 }
 
 int forward_ctas_per_sm(int ct, int device) {
+    const bool wide = forward_px_per_thread(ct) == 16;
     switch (ct) {
-        case 1: return occ<1>(device);
-        case 2: return occ<2>(device);
-        case 3: return occ<3>(device);
-        case 4: return occ<4>(device);
-        case 8: return occ<8>(device);
-        default: return occ<16>(device);
+        case 1: return wide ? occ<1, 16>(device) : occ<1, 8>(device);
+        case 2: return wide ? occ<2, 16>(device) : occ<2, 8>(device);
+        case 3: return wide ? occ<3, 16>(device) : occ<3, 8>(device);
+        case 4: return wide ? occ<4, 16>(device) : occ<4, 8>(device);
+        case 8: return occ<8, 4>(device);
+        default: return occ<16, 4>(device);
     }
 }
-int forward_px_per_thread(int ct) { return ct <= 4 ? FwdCfg<3>::PX : (ct <= 8 ? FwdCfg<8>::PX : FwdCfg<16>::PX); }
-int forward_threads(int) { return FwdCfg<3>::THREADS; }
-int forward_chunk_g(int) { return FwdCfg<3>::CHUNK_G; }
+int forward_threads(int) { return 128; }
+int forward_chunk_g(int) { return 128; }
 
 }  // namespace igs

@@ -34,7 +34,8 @@ struct FwdPlan {
 
 struct BwdPlan {
     Chunks ch;
-    int threads;           // gaussians per CTA (one per thread)
+    int threads;           // threads per CTA
+    int gauss_per_thread;  // gaussians each thread owns (1 or 2)
     int n_slab;            // CTAs along the pixel axis
     long long npairs;      // pixel pairs per batch element
     long long pairs_per_slab;
@@ -59,6 +60,7 @@ int forward_px_per_thread(int ct);
 int forward_threads(int ct);
 int forward_chunk_g(int ct);
 int backward_threads(int ct);
+int backward_gauss_per_thread(int ct);
 int backward_chunk_pairs(int ct);
 
 }  // namespace igs

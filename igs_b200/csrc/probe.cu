@@ -13,6 +13,7 @@ __global__ void __launch_bounds__(PROBE_THREADS) probe_ffma_kernel(float* sink, 
     float v[PROBE_CHAINS];
 #pragma unroll
     for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = (float)(threadIdx.x + k);
+#pragma unroll 16
     for (int it = 0; it < PROBE_ITERS; ++it) {
 #pragma unroll
         for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = fmaf(v[k], m, c);
@@ -28,6 +29,7 @@ __global__ void __launch_bounds__(PROBE_THREADS) probe_ffma2_kernel(float* sink,
     const f2 mm = pk(m, m), cc = pk(c, c);
 #pragma unroll
     for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = pk((float)(threadIdx.x + k), (float)k);
+#pragma unroll 16
     for (int it = 0; it < PROBE_ITERS; ++it) {
 #pragma unroll
         for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = fma2(v[k], mm, cc);
@@ -46,6 +48,7 @@ __global__ void __launch_bounds__(PROBE_THREADS) probe_ex2_kernel(float* sink, f
     float v[PROBE_CHAINS];
 #pragma unroll
     for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = -(float)(threadIdx.x + k) * 1e-3f;
+#pragma unroll 16
     for (int it = 0; it < PROBE_ITERS; ++it) {
 #pragma unroll
         for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = ex2f(v[k]) - c;

@@ -35,6 +35,8 @@ CONFIGS = {
     "cfg0": SplatConfig("cfg0", 1, 2048, 256, 256, 3, 0.25, 0.75, seed=0, loss="sse"),
     # headline: batched training shape
     "cfg2": SplatConfig("cfg2", 16, 8192, 256, 256, 3, 0.25, 0.75, seed=2),
+    # the headline shape cut down (B=4, N=4096) for profiler captures that must stay short
+    "cfg2_small": SplatConfig("cfg2_small", 4, 4096, 256, 256, 3, 0.25, 0.75, seed=2),
     # single-image fit, sharded over gaussian ranges when run on several GPUs
     "cfg3": SplatConfig("cfg3", 1, 16384, 512, 512, 3, 0.05, 0.30, seed=3),
     # large feature-map render
