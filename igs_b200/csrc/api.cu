@@ -204,10 +204,10 @@ static Strides get_strides(const int64_t* s, int H, int W) {
     return {(long long)s[0], (long long)s[1], (long long)s[2]};
 }
 
-static int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2,
-                        const float* alpha, const float* colors, const float* x, const int64_t* xs, const float* y,
-                        const int64_t* ys, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
-                        float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
+                 const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
+                 int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
+                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
@@ -233,8 +233,12 @@ static int forward_impl(int kind, const float* pos, const float* s0, const float
     }
 
     FwdPlan p;
-    rc = plan_forward(B, N, H, W, C, device, &p);
-    if (rc) return rc;
+    if (use_plan) {
+        p = *use_plan;
+    } else {
+        rc = plan_forward(B, N, H, W, C, device, &p);
+        if (rc) return rc;
+    }
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(int), st);
@@ -483,7 +487,7 @@ const char* igs_strerror(int code) {
         case IGS_OK: return "ok";
         case IGS_ERR_ARG: return "invalid argument (null pointer, negative size or unsupported value)";
         case IGS_ERR_WORKSPACE: return "workspace missing or smaller than igs_workspace_bytes reports";
-        case IGS_ERR_LIMIT: return "size beyond a supported limit (B <= 65535, C <= 256)";
+        case IGS_ERR_LIMIT: return "size beyond a supported limit (B <= 65535, C <= 256, or the fixed scratch of a *_static entry point)";
         case IGS_ERR_DEVICE: return "CUDA device cannot be selected";
         case IGS_ERR_STATUS: return "a kernel gave up on a bounded wait (status word non-zero)";
     }

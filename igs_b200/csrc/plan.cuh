@@ -53,6 +53,13 @@ int make_chunks(int C, Chunks* out);
 int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p);
 int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p);
 
+// Body of igs_forward_sr / igs_forward_cov (kind = ShapeKind).  use_plan, when given,
+// replaces the plan the call would compute itself.
+int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
+                 const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
+                 int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
+                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr);
+
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);
 int backward_ctas_per_sm(int ct, int device);

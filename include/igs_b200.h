@@ -88,6 +88,30 @@ int igs_forward_cov(const float* positions, const float* cov_inv_00, const float
                     void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
+ * igs_forward_sr without a workspace argument, for hosts that cannot allocate device
+ * memory (a plug-in inside another application's memory budget, a loop that must stay
+ * off the driver's allocator).  No counterpart in the reference: it is an addition of
+ * this library.  Same arguments, results and return codes as igs_forward_sr; the
+ * scratch is a fixed array of IGS_STATIC_SCRATCH_BYTES inside the library's device
+ * image (held on every GPU that loads the library until the process exits).
+ *   - returns IGS_ERR_LIMIT when the shape needs more scratch than that: with C <= 4
+ *     the records take 80 bytes per gaussian (B*N*80 <= 8 MiB, about 100k gaussians);
+ *     gaussian splits are dropped first if their partial sums would not fit;
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine (per-kernel
+ *     profiling, igs_profile_enable, must stay off: it creates events);
+ *   - all calls on a device share the one array: calls whose kernels could overlap on
+ *     the GPU must be ordered on one stream by the caller;
+ *   - the first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make it at start-up, before any stream capture begins.
+ */
+#define IGS_STATIC_SCRATCH_BYTES (8u << 20)
+int igs_forward_sr_static(const float* positions, const float* scales, const float* rotations,
+                          const float* alphas, const float* colors, const float* x,
+                          const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
+                          int H, int W, int C, float eps, int normalize, float* out, float* wsum, int device,
+                          void* stream);
+
+/*
  * sums [B,C+1,H,W] -> out [B,C,H,W], wsum [B,H,W].  The division of
  * src/igs/gs2d.py:323, split off so that an all-reduce can run in between.
  */
