@@ -26,6 +26,15 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures
+# summarised under profiles/ (workload -> kernel -> bytes)
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    # profiles/splat_kernels_cfg2_dram.md
+    "cfg2": {"forward": 18.93e6 + 8.23e6, "backward": 31.38e6 + 8.05e6},
+    # profiles/splat_kernels_cfg2_small_ncu_full.md
+    "cfg2_small": {"forward": 3.46e6 + 0.01e6, "backward": 7.03e6},
+}
+
 METRIC = "gaussian_pixel_evals_per_s_fwd_bwd"
 UNIT = "evals/s"
 
@@ -33,7 +42,7 @@ UNIT = "evals/s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg2_small", "cfg3"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -46,7 +55,7 @@ def parse_args():
 # clocks during the timed region
 # ---------------------------------------------------------------------------
 class ClockSampler:
-    """Samples nvidia-smi (SM clock, power, throttle reasons) of one GPU every 200 ms."""
+    """Samples nvidia-smi (SM clock, power, throttle reasons) of one GPU every 50 ms."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -59,7 +68,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -314,7 +323,11 @@ def run_b200(args):
         C = cfg.C
         sm = (clocks or {}).get("sm_mhz")
         n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
-        fp32_peak = probes["fp32_scalar_lane_instr_per_s"]
+        # the FMA pipe's measured issue rate: the better of the scalar and the packed probe
+        fp32_peak = max(probes["fp32_scalar_lane_instr_per_s"], probes["fp32_packed_lane_instr_per_s"])
+        mix_ceiling = {"forward": probes["fp32_forward_mix_lane_instr_per_s"],
+                       "backward": probes["fp32_backward_mix_lane_instr_per_s"]}
+        executed = {"forward": 8 + C, "backward": 16 + 2 * C}  # FMA-pipe instructions the kernels issue
         # canonical FMA-pipe instruction counts per gaussian x pixel (fwd 9+C, bwd 18+2C)
         instr = {"forward": 9 + C, "backward": 18 + 2 * C}
 
@@ -328,8 +341,11 @@ def run_b200(args):
                     "peak": fp32_peak / 1e12, "unit": "T lane-instr/s", "frac": ach / fp32_peak,
                     "launch_ms": ms / n, "launches": n,
                     "algorithmic_instr_per_eval": instr[name],
-                    "peak_source": "measured live: dependent-chain FFMA kernel (igs_probe_fp32_rate)",
-                    "traffic": None}
+                    "executed_instr_per_eval": executed[name],
+                    "executed_frac": ev_rank * executed[name] / per_launch_s / fp32_peak,
+                    "mix_ceiling_frac": mix_ceiling[name] / fp32_peak,
+                    "peak_source": "measured live: FFMA-only kernel, best of scalar and f32x2 (igs_probe_fp32_rate)",
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(cfg.name, {}).get(name)}
 
         roof = kernel_roof("backward")
         roof_f = kernel_roof("forward")

@@ -14,7 +14,8 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libigs_b200.so")
+# IGS_B200_LIB: development override, a differently tuned build of the same library
+LIB_PATH = os.environ.get("IGS_B200_LIB") or os.path.join(_HERE, "libigs_b200.so")
 
 GRAD_REFERENCE = 0
 GRAD_EXACT = 1
@@ -45,6 +46,7 @@ SIGNATURES = {
     "igs_describe_plan": (_i, [_i] * 6 + [ctypes.POINTER(_i)] * 4),
     "igs_probe_fp32_rate": (_i, [_i, _i, ctypes.POINTER(ctypes.c_double)]),
     "igs_probe_ex2_rate": (_i, [_i, ctypes.POINTER(ctypes.c_double)]),
+    "igs_probe_mix_rate": (_i, [_i, _i, ctypes.POINTER(ctypes.c_double)]),
 }
 
 
@@ -239,4 +241,8 @@ def probe_rates(device: torch.device):
     d = ctypes.c_double(0)
     check("igs_probe_ex2_rate", lib.igs_probe_ex2_rate(device.index, ctypes.byref(d)))
     vals["ex2_results_per_s"] = d.value
+    for key, bwd in (("fp32_forward_mix_lane_instr_per_s", 0), ("fp32_backward_mix_lane_instr_per_s", 1)):
+        d = ctypes.c_double(0)
+        check("igs_probe_mix_rate", lib.igs_probe_mix_rate(device.index, bwd, ctypes.byref(d)))
+        vals[key] = d.value
     return vals

@@ -109,7 +109,16 @@ struct BwdCfg {
     static constexpr int GAUSS_PER_CTA = THREADS * GPT;
     static constexpr int CHUNK_PAIRS = CT <= 4 ? 256 : 128;
     static constexpr int STAGES = 2;
-    static constexpr int MIN_CTAS = GPT == 2 ? 4 : (CT <= 4 ? 5 : (CT <= 8 ? 4 : 3));
+#ifdef IGS_BWD_MINCTAS
+    static constexpr int MIN_CTAS = IGS_BWD_MINCTAS;
+#else
+    static constexpr int MIN_CTAS = CT <= 4 ? 5 : (CT <= 8 ? 4 : 3);
+#endif
+#ifdef IGS_BWD_UNROLL
+    static constexpr int UNROLL = IGS_BWD_UNROLL;
+#else
+    static constexpr int UNROLL = GPT == 2 ? 4 : 2;
+#endif
     static constexpr bool TWO_LEVEL = (CT <= 4 && GPT == 1);
     static constexpr int RS = bwd_rec_floats(CT);
     static constexpr int NACC = N_MOMENTS + CT;
@@ -204,7 +213,7 @@ __global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN
 #pragma unroll
             for (int k = 0; k < NACC; ++k) acc[g][k] = Cfg::TWO_LEVEL ? 0ull : tot[g][k];
 
-#pragma unroll 2
+#pragma unroll(Cfg::UNROLL)
         for (int i = 0; i < cnt; ++i) {
             const ulonglong2* r = rec + (size_t)i * (RS / 4);
             const ulonglong2 r0 = r[0];  // {x0,x1},{y0,y1}

@@ -29,7 +29,16 @@ struct FwdCfg {
     static constexpr int PX = PX_;
     static constexpr int CHUNK_G = 128;  // gaussians per stage
     static constexpr int STAGES = 2;
+#ifdef IGS_FWD_MINCTAS
+    static constexpr int MIN_CTAS = IGS_FWD_MINCTAS;
+#else
     static constexpr int MIN_CTAS = (PX_ * (CT + 3) >= 64) ? 3 : 4;
+#endif
+#ifdef IGS_FWD_UNROLL
+    static constexpr int UNROLL = IGS_FWD_UNROLL;
+#else
+    static constexpr int UNROLL = PX_ >= 16 ? 1 : (CT <= 3 ? 4 : 2);
+#endif
     static constexpr int RS = fwd_rec_floats(CT);
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
 };
@@ -122,7 +131,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
         }
         const int cnt = min(G, n_total - chunk * G);
         const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * G * RS);
-#pragma unroll(Cfg::PX >= 16 ? 1 : 2)
+#pragma unroll(Cfg::UNROLL)
         for (int g = 0; g < cnt; ++g) {
             const ulonglong2* r = rec + (size_t)g * (RS / 4);
             const ulonglong2 r0 = r[0];  // {px,px},{py,py}

@@ -59,6 +59,35 @@ __global__ void __launch_bounds__(PROBE_THREADS) probe_ex2_kernel(float* sink, f
     if (sink && s == 123.456f) sink[0] = s;
 }
 
+// The kernels' own instruction mix with every dependency removed: NF independent f32x2
+// FMAs and two ex2 (each followed by the FADD that keeps its chain bounded) per
+// iteration, NF = 11 for the forward mix and 22 for the backward mix.  What this
+// reaches is the ceiling of the FMA pipe for that mix on this GPU: MUFU instructions
+// are not free for the FMA pipe's issue port.
+template <int NF>
+__global__ void __launch_bounds__(PROBE_THREADS) probe_mix_kernel(float* sink, float m, float c) {
+    f2 v[NF];
+    float e0 = -1e-3f * threadIdx.x, e1 = -2e-3f * threadIdx.x;
+    const f2 mm = pk(m, m), cc = pk(c, c);
+#pragma unroll
+    for (int k = 0; k < NF; ++k) v[k] = pk((float)(threadIdx.x + k), (float)k);
+#pragma unroll 4
+    for (int it = 0; it < PROBE_ITERS / 2; ++it) {
+#pragma unroll
+        for (int k = 0; k < NF; ++k) v[k] = fma2(v[k], mm, cc);
+        e0 = ex2f(e0) - 1.5f;
+        e1 = ex2f(e1) - 1.5f;
+    }
+    float s = e0 + e1;
+#pragma unroll
+    for (int k = 0; k < NF; ++k) {
+        float lo, hi;
+        upk(v[k], lo, hi);
+        s += lo + hi;
+    }
+    if (sink && s == 123.456f) sink[0] = s;
+}
+
 // Runs `launch` a few times and returns the best per-launch time in seconds (<0 on error).
 template <typename F>
 static double best_time(F launch, cudaError_t* err) {
@@ -111,6 +140,34 @@ int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s) {
     if (err != cudaSuccess) return (int)err;
     const double lanes = (double)blocks * PROBE_THREADS * PROBE_CHAINS * (double)PROBE_ITERS * (packed ? 2.0 : 1.0);
     *lane_instr_per_s = lanes / t;
+    return IGS_OK;
+}
+
+int igs_probe_mix_rate(int device, int backward_mix, double* lane_instr_per_s) {
+    if (!lane_instr_per_s) return IGS_ERR_ARG;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    // 96 KB of (unused) dynamic shared memory per CTA holds residency at 2 CTAs of 256
+    // threads per SM: the splat kernels' own 16 warps per SM
+    const int blocks = sm_count(device) * 8;
+    cudaError_t err = backward_mix ? cudaFuncSetAttribute(probe_mix_kernel<22>,
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)
+                                   : cudaFuncSetAttribute(probe_mix_kernel<11>,
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (err != cudaSuccess) return (int)err;
+    const double t = best_time(
+        [&] {
+            if (backward_mix)
+                probe_mix_kernel<22><<<blocks, PROBE_THREADS, 96 * 1024>>>(nullptr, 0.999f, 0.001f);
+            else
+                probe_mix_kernel<11><<<blocks, PROBE_THREADS, 96 * 1024>>>(nullptr, 0.999f, 0.001f);
+            count_launch();
+        },
+        &err);
+    if (err != cudaSuccess) return (int)err;
+    // FMA-pipe lane-instructions: two per f32x2 FMA plus the two scalar FADDs
+    const double per_iter = (backward_mix ? 44.0 : 22.0) + 2.0;
+    *lane_instr_per_s = (double)blocks * PROBE_THREADS * (PROBE_ITERS / 2) * per_iter / t;
     return IGS_OK;
 }
 

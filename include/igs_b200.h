@@ -188,6 +188,9 @@ int igs_profile_read(int kernel_id, double* total_ms, long long* launches);
  */
 int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s);
 int igs_probe_ex2_rate(int device, double* results_per_s);
+/* FMA-pipe rate reached by the kernels' instruction mix with all dependencies removed
+ * (11 f32x2 FMA : 2 ex2 forward, 22 : 2 backward), at the kernels' occupancy. */
+int igs_probe_mix_rate(int device, int backward_mix, double* lane_instr_per_s);
 
 #ifdef __cplusplus
 }
