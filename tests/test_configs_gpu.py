@@ -1,0 +1,165 @@
+"""The benchmark configurations other than the headline one, at their full sizes (config 4
+on one of its 64 batch elements), each checked against the fp64 oracle on random subsets:
+the image at sampled pixels, the per-gaussian gradients (sums over ALL pixels) for sampled
+gaussians.  The oracle accepts any set of sample points and any subset of gaussians, given
+the device's own per-pixel weight sums, so these checks cost seconds whatever the size.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    return torch.device("cuda", 0)
+
+
+def _np(t):
+    return t.detach().cpu().numpy()
+
+
+def subset_check(d, out, gout, grads, n_pix=192, n_gauss=24, seed=0, eps=1e-6, tol=TOL):
+    """d: dict of device tensors (positions, colors, scales, rotations, alphas, x, y);
+    out, gout: [B,C,H,W]; grads: dict of device gradients shaped like the parameters."""
+    from igs_b200 import _lib
+    from oracle import splat_oracle as so
+
+    B, C, H, W = out.shape
+    N = d["positions"].shape[1]
+    rng = np.random.default_rng(seed)
+    P = {k: _np(d[k]) for k in ("positions", "colors", "scales", "rotations", "alphas")}
+    x, y = _np(d["x"].expand(B, 1, H, W))[:, 0], _np(d["y"].expand(B, 1, H, W))[:, 0]
+
+    # image at sampled pixels: an H=1, W=K "image" for the oracle
+    idx = rng.choice(H * W, size=min(n_pix, H * W), replace=False)
+    xs, ys = x.reshape(B, -1)[:, idx][:, None, :], y.reshape(B, -1)[:, idx][:, None, :]
+    o_out, _ = so.render(P["positions"], P["colors"], P["scales"], P["rotations"], P["alphas"], xs, ys, eps,
+                         dtype=np.float64)
+    got = _np(out).reshape(B, C, -1)[:, :, idx][:, :, None, :]
+    err = np.abs(got - o_out).max() / max(np.abs(_np(out)).max(), 1e-30)
+    assert err <= tol, f"image at sampled pixels: {err:.3e}"
+
+    # gradients of sampled gaussians, from the device's weight sums (ones-colour forward)
+    sel = np.sort(rng.choice(N, size=min(n_gauss, N), replace=False))
+    _, wsum = _lib.forward("sr", d["positions"].contiguous(), d["scales"].contiguous(), d["rotations"].contiguous(),
+                           None, d["alphas"].contiguous(), torch.ones_like(d["colors"]).contiguous(),
+                           d["x"].expand(B, 1, H, W)[:, 0], d["y"].expand(B, 1, H, W)[:, 0], eps)
+    S = {k: v[:, sel] for k, v in P.items()}
+    c00, c01, c11 = so.cov_inv(S["scales"], S["rotations"], eps, np.float64)
+    gr = so.backward(x, y, S["positions"], c00, c01, c11, S["alphas"], S["colors"], _np(wsum), _np(out), _np(gout),
+                     eps, so.MODE_REFERENCE, False, np.float64)
+    gs, grot = so.cov_inv_backward(S["scales"], S["rotations"], gr["c00"], gr["c01"], gr["c11"], eps, np.float64)
+    want = {"positions": gr["positions"], "colors": gr["colors"], "scales": gs, "rotations": grot,
+            "alphas": gr["alphas"]}
+    errs = {}
+    for k, w in want.items():
+        if k not in grads or grads[k] is None:
+            continue
+        full = _np(grads[k])
+        errs[k] = float(np.abs(full[:, sel] - w).max() / max(np.abs(full).max(), 1e-30))
+        assert errs[k] <= tol, f"d_{k} on sampled gaussians: {errs[k]:.3e}"
+    return errs
+
+
+def _render_and_backward(d, loss_fn):
+    from igs_b200.gs2d import gaussian_splatting_2d
+
+    names = ("positions", "colors", "scales", "rotations", "alphas")
+    leaves = {k: d[k].clone().requires_grad_() for k in names}
+    out = gaussian_splatting_2d(*[leaves[k] for k in names], d["x"], d["y"])
+    out.retain_grad()
+    loss = loss_fn(out)
+    loss.backward()
+    return out.detach(), out.grad.detach(), {k: v.grad for k, v in leaves.items()}, float(loss.detach())
+
+
+def test_cfg3_single_image_fit_shape(dev):
+    """B=1, N=16384, 512x512, C=3, scales U[0.05,0.3]: one forward + backward."""
+    from igs_b200 import workloads
+
+    cfg = workloads.CONFIGS["cfg3"]
+    d = workloads.draw(cfg, device=dev)
+    out, gout, grads, _ = _render_and_backward(d, lambda o: torch.nn.functional.mse_loss(o, d["target"]))
+    subset_check(d, out, gout, grads, seed=3)
+
+
+def test_cfg3_adam_steps_reduce_the_loss(dev):
+    """The fit protocol: Adam (lr 1e-2) on the five parameter tensors against a smooth
+    target (sum of 64 random sinusoids per channel, min-max normalised); the loss must go
+    down, and nothing may turn non-finite when scales drift through zero."""
+    from igs_b200 import workloads
+    from igs_b200.gs2d import gaussian_splatting_2d
+
+    cfg = workloads.CONFIGS["cfg3"]
+    d = workloads.draw(cfg, device=dev, with_target=False)
+    gen = torch.Generator().manual_seed(33)
+    a = torch.rand(3, 64, generator=gen)
+    f = torch.rand(3, 64, 2, generator=gen) * 16 - 8
+    ph = torch.rand(3, 64, generator=gen) * 2 * math.pi
+    x, y = d["x"][0, 0].cpu(), d["y"][0, 0].cpu()
+    tgt = (a[:, :, None, None] * torch.sin(math.pi * (f[:, :, 0, None, None] * x + f[:, :, 1, None, None] * y)
+                                           + ph[:, :, None, None])).sum(1)
+    tgt = (tgt - tgt.amin((1, 2), keepdim=True)) / (tgt.amax((1, 2), keepdim=True) - tgt.amin((1, 2), keepdim=True))
+    tgt = tgt[None].to(dev)
+    names = ("positions", "colors", "scales", "rotations", "alphas")
+    params = [d[k].clone().requires_grad_() for k in names]
+    opt = torch.optim.Adam(params, lr=1e-2)
+    losses = []
+    for _ in range(60):
+        opt.zero_grad(set_to_none=True)
+        out = gaussian_splatting_2d(*params, d["x"], d["y"])
+        loss = torch.nn.functional.mse_loss(out, tgt)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert all(math.isfinite(v) for v in losses)
+    assert losses[-1] < 0.5 * losses[0], (losses[0], losses[-1])
+    assert all(bool(torch.isfinite(p).all()) for p in params)
+
+
+def test_cfg4_feature_map_regime_one_batch_element(dev):
+    """C=16 colours ~ N(0,1), N=65536, 512x512, scales U[0.02,0.2] (config 4, one of its 64
+    independent batch elements)."""
+    from igs_b200 import workloads
+
+    cfg = workloads.CONFIGS["cfg4"]
+    d = workloads.draw(cfg, B=1, device=dev)
+    out, gout, grads, _ = _render_and_backward(d, lambda o: torch.nn.functional.mse_loss(o, d["target"]))
+    subset_check(d, out, gout, grads, n_pix=96, n_gauss=8, seed=4)
+
+
+def test_cfg1_module_at_init(dev):
+    """GaussianSplatting2D(32 per feature, 1024) with random-init weights on x ~ N(0,1)
+    [1,128,1024]: N=4096 narrow gaussians (scale ~ e^-4) at 256x256, where about one pixel
+    in a hundred has a weight sum near zero.  The splat inside the module is checked on
+    subsets; the projection in front of it is plain torch."""
+    from igs_b200 import GaussianSplatting2D
+
+    torch.manual_seed(1)
+    m = GaussianSplatting2D(32, 1024).to(dev)
+    feat = torch.randn(1, 128, 1024, device=dev, requires_grad=True)
+    out, gs_feature = m(feat, size=(256, 256))
+    gs_feature.retain_grad()
+    out.retain_grad()
+    tgt = torch.rand(1, 3, 256, 256, device=dev)
+    torch.nn.functional.mse_loss(out, tgt).backward()
+    assert out.shape == (1, 3, 256, 256) and gs_feature.shape == (1, 4096, 9)
+    assert bool(torch.isfinite(m.proj.weight.grad).all()) and bool(torch.isfinite(feat.grad).all())
+
+    pos, log_sc, rot, _, col = gs_feature.detach().split([2, 2, 1, 1, 3], dim=-1)
+    xg, yg = GaussianSplatting2D.xy_grid((256, 256), dev)
+    d = {"positions": pos.contiguous(), "colors": col.contiguous(), "scales": torch.exp(log_sc) + 1e-6,
+         "rotations": rot[..., 0].contiguous(), "alphas": torch.ones(1, 4096, device=dev), "x": xg[None], "y": yg[None]}
+    g = gs_feature.grad
+    sc = d["scales"]
+    grads = {"positions": g[..., 0:2], "colors": g[..., 6:9], "rotations": g[..., 4],
+             # d/d log_scale = d/d scale * exp(log_scale); undo it to compare scale gradients
+             "scales": g[..., 2:4] / (sc - 1e-6)}
+    subset_check(d, out.detach(), out.grad.detach(), grads, n_pix=256, n_gauss=32, seed=1)
