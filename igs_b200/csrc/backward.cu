@@ -103,6 +103,10 @@ cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s) {
 // for four cycles per warp, so with GPT = 1 the 3 reads per pixel pair (C = 3) need
 // more return-path cycles than the 22 f32x2 instructions need FMA-pipe cycles; GPT = 2
 // halves the reads per evaluation and makes the FMA pipe the limiter again.
+#ifndef IGS_BWD_GPT
+#define IGS_BWD_GPT 2
+#endif
+
 template <int CT, int GPT>
 struct BwdCfg {
     static constexpr int THREADS = 128;
@@ -117,7 +121,7 @@ struct BwdCfg {
 #ifdef IGS_BWD_UNROLL
     static constexpr int UNROLL = IGS_BWD_UNROLL;
 #else
-    static constexpr int UNROLL = GPT == 2 ? 4 : 2;
+    static constexpr int UNROLL = GPT >= 2 ? 4 : 2;
 #endif
     static constexpr bool TWO_LEVEL = (CT <= 4 && GPT == 1);
     static constexpr int RS = bwd_rec_floats(CT);
@@ -297,12 +301,12 @@ static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s
 }
 
 cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
-    const bool two = p.gauss_per_thread == 2;
+    const bool two = p.gauss_per_thread >= 2;
     switch (ct) {
-        case 1: return two ? launch_one<1, 2>(a, p, s) : launch_one<1, 1>(a, p, s);
-        case 2: return two ? launch_one<2, 2>(a, p, s) : launch_one<2, 1>(a, p, s);
-        case 3: return two ? launch_one<3, 2>(a, p, s) : launch_one<3, 1>(a, p, s);
-        case 4: return two ? launch_one<4, 2>(a, p, s) : launch_one<4, 1>(a, p, s);
+        case 1: return two ? launch_one<1, IGS_BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);
+        case 2: return two ? launch_one<2, IGS_BWD_GPT>(a, p, s) : launch_one<2, 1>(a, p, s);
+        case 3: return two ? launch_one<3, IGS_BWD_GPT>(a, p, s) : launch_one<3, 1>(a, p, s);
+        case 4: return two ? launch_one<4, IGS_BWD_GPT>(a, p, s) : launch_one<4, 1>(a, p, s);
         case 8: return launch_one<8, 1>(a, p, s);
         case 16: return launch_one<16, 1>(a, p, s);
     }
@@ -330,19 +334,19 @@ int backward_gauss_per_thread(int ct) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("IGS_B200_BWD_GPT");  // development knob: 1 or 2
-        forced = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+        forced = (e && e[0] == '1') ? 1 : 0;
     }
     if (ct > 4) return 1;
-    return forced ? forced : 2;
+    return forced ? forced : IGS_BWD_GPT;
 }
 
 int backward_ctas_per_sm(int ct, int device) {
-    const bool two = backward_gauss_per_thread(ct) == 2;
+    const bool two = backward_gauss_per_thread(ct) >= 2;
     switch (ct) {
-        case 1: return two ? occ<1, 2>(device) : occ<1, 1>(device);
-        case 2: return two ? occ<2, 2>(device) : occ<2, 1>(device);
-        case 3: return two ? occ<3, 2>(device) : occ<3, 1>(device);
-        case 4: return two ? occ<4, 2>(device) : occ<4, 1>(device);
+        case 1: return two ? occ<1, IGS_BWD_GPT>(device) : occ<1, 1>(device);
+        case 2: return two ? occ<2, IGS_BWD_GPT>(device) : occ<2, 1>(device);
+        case 3: return two ? occ<3, IGS_BWD_GPT>(device) : occ<3, 1>(device);
+        case 4: return two ? occ<4, IGS_BWD_GPT>(device) : occ<4, 1>(device);
         case 8: return occ<8, 1>(device);
         default: return occ<16, 1>(device);
     }

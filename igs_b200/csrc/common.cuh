@@ -20,10 +20,13 @@ namespace igs {
 constexpr int GEO_FLOATS = 8;
 constexpr float EXP2_SCALE = -0.72134752044448170368f;  // -0.5 * log2(e)
 
-// Forward record, one per gaussian and channel chunk, every value stored twice so a
-// 16-byte shared-memory load yields two ready f32x2 operands:
-//   {px,px, py,py, A,A, B2,B2, Cq,Cq, al,al, al*c0,al*c0, ...}  padded to 4 floats
-__host__ __device__ constexpr int fwd_rec_floats(int ct) { return (12 + 2 * ct + 3) / 4 * 4; }
+// Forward record, one per gaussian and channel chunk, padded to a multiple of 4 floats:
+//   {px, py, A, B2,  Cq, al, al*c0, al*c1,  al*c2, ...}
+// Each value is stored once and duplicated into an f32x2 operand in registers (a move on
+// the otherwise idle ALU pipe): a record then costs 3 sixteen-byte broadcast reads at
+// C = 3 instead of the 5 a pre-duplicated record needs, and the shared-memory return path
+// (4 cycles per 16-byte warp read) stops co-limiting the kernel.
+__host__ __device__ constexpr int fwd_rec_floats(int ct) { return (6 + ct + 3) / 4 * 4; }
 
 // Backward pixel record, one per PAIR of consecutive pixels and channel chunk:
 //   {x0,x1, y0,y1, gS0,gS1, gn0_0,gn0_1, ...}  padded to 4 floats

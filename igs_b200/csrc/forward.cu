@@ -19,10 +19,11 @@
 
 namespace igs {
 
-// PX = pixels per thread.  A forward record costs 5 sixteen-byte broadcast reads per
-// thread whatever PX is (20 cycles of the shared-memory return path per warp), against
+// PX = pixels per thread.  A forward record costs 3 sixteen-byte broadcast reads per
+// thread whatever PX is (12 cycles of the shared-memory return path per warp), against
 // 11 f32x2 instructions per pixel pair; more pixels per thread move the balance from
-// the return path to the FMA pipe at the price of registers (occupancy).
+// the return path to the FMA pipe at the price of registers (occupancy).  Measured at
+// C = 3: PX = 8 with 4 CTAs/SM and the gaussian loop unrolled 4x is the fastest.
 template <int CT, int PX_>
 struct FwdCfg {
     static constexpr int THREADS = 128;
@@ -130,20 +131,23 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
             return;
         }
         const int cnt = min(G, n_total - chunk * G);
-        const ulonglong2* rec = reinterpret_cast<const ulonglong2*>(stage_base + (size_t)st * G * RS);
+        const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * G * RS);
 #pragma unroll(Cfg::UNROLL)
         for (int g = 0; g < cnt; ++g) {
-            const ulonglong2* r = rec + (size_t)g * (RS / 4);
-            const ulonglong2 r0 = r[0];  // {px,px},{py,py}
-            const ulonglong2 r1 = r[1];  // {A,A},{B2,B2}
-            const ulonglong2 r2 = r[2];  // {Cq,Cq},{al,al}
+            const float4* rf = rec + (size_t)g * (RS / 4);
+            float vals[RS];
+#pragma unroll
+            for (int q = 0; q < RS / 4; ++q) {
+                const float4 t4 = rf[q];
+                vals[4 * q] = t4.x; vals[4 * q + 1] = t4.y; vals[4 * q + 2] = t4.z; vals[4 * q + 3] = t4.w;
+            }
+            ulonglong2 r0, r1, r2;
+            r0.x = pk(vals[0], vals[0]); r0.y = pk(vals[1], vals[1]);
+            r1.x = pk(vals[2], vals[2]); r1.y = pk(vals[3], vals[3]);
+            r2.x = pk(vals[4], vals[4]); r2.y = pk(vals[5], vals[5]);
             f2 col[CT + 1];
 #pragma unroll
-            for (int c = 0; c < (CT + 1) / 2; ++c) {
-                const ulonglong2 rc = r[3 + c];
-                col[2 * c] = rc.x;
-                col[2 * c + 1] = rc.y;
-            }
+            for (int c = 0; c < CT; ++c) col[c] = pk(vals[6 + c], vals[6 + c]);
 #pragma unroll
             for (int j = 0; j < NP; ++j) {
                 const f2 dx = sub2(xx[j], r0.x);

@@ -32,17 +32,10 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
         if (!rec) continue;
         const int ct = a.ch.ct[k], cr = a.ch.cr[k], c0 = a.ch.c0[k];
         const int rs = fwd_rec_floats(ct);
-        float4* r = reinterpret_cast<float4*>(rec + i * rs);
-        r[0] = make_float4(px, px, py, py);
-        r[1] = make_float4(A, A, B2, B2);
-        r[2] = make_float4(Cq, Cq, al, al);
         // colours pre-multiplied by alpha: numerator += e * (alpha * colour)
-        float* cdst = rec + i * rs + 12;
-        for (int c = 0; c < rs / 2 - 6; ++c) {
-            const float v = (c < cr) ? al * a.colors[i * a.C + c0 + c] : 0.f;
-            cdst[2 * c] = v;
-            cdst[2 * c + 1] = v;
-        }
+        float* r = rec + i * rs;
+        r[0] = px; r[1] = py; r[2] = A; r[3] = B2; r[4] = Cq; r[5] = al;
+        for (int c = 0; c < rs - 6; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * a.C + c0 + c] : 0.f;
     }
 }
 

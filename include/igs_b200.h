@@ -95,7 +95,7 @@ int igs_forward_cov(const float* positions, const float* cov_inv_00, const float
  * scratch is a fixed array of IGS_STATIC_SCRATCH_BYTES inside the library's device
  * image (held on every GPU that loads the library until the process exits).
  *   - returns IGS_ERR_LIMIT when the shape needs more scratch than that: with C <= 4
- *     the records take 80 bytes per gaussian (B*N*80 <= 8 MiB, about 100k gaussians);
+ *     the records take 48 bytes per gaussian (B*N*48 <= 8 MiB, about 170k gaussians);
  *     gaussian splits are dropped first if their partial sums would not fit;
  *   - calls no cudaMalloc / cudaFree and no allocating library routine (per-kernel
  *     profiling, igs_profile_enable, must stay off: it creates events);

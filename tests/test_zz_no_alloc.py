@@ -91,8 +91,8 @@ def test_static_scratch_unnormalised_sums_and_limit():
     assert rc_ref == 0 and rc == 0
     assert_close(sums.cpu().numpy(), sums_ref.cpu().numpy(), 1e-5, "un-normalised sums")
 
-    # records alone take 80 bytes per gaussian at C=3: this many cannot fit the array
-    n_big = STATIC_SCRATCH_BYTES // 80 + 4096
+    # records alone take 48 bytes per gaussian at C=3: this many cannot fit the array
+    n_big = STATIC_SCRATCH_BYTES // 48 + 4096
     big = _inputs(1, n_big, 8, 8, 3, 404, dev)
     rc, out, _ = _call(lib, True, big, 1, n_big, 8, 8, 3, dev)
     assert rc == -3, lib.igs_strerror(rc)          # IGS_ERR_LIMIT, nothing launched
