@@ -209,7 +209,7 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     return res
 
 
-KERNEL_NAMES = ("pack", "forward", "reduce_normalize", "pixel_terms", "backward", "finalize", "coord_grad")
+KERNEL_NAMES = ("pack", "forward", "reduce_normalize", "pixel_terms", "backward", "finalize", "coord_grad", "grid_check")
 
 
 def profile_enable(on: bool) -> None:

@@ -1,11 +1,13 @@
 // extern "C" entry points, launch plans and workspace carving.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
 
 #include "backward.cuh"
 #include "forward.cuh"
+#include "grid.cuh"
 #include "pack.cuh"
 #include "plan.cuh"
 
@@ -60,6 +62,16 @@ static cudaError_t profile_drain() {
     }
     g_pending.clear();
     return first;
+}
+
+// IGS_B200_NO_SEPARABLE=1 (development knob) keeps every call on the general kernels.
+static bool separable_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("IGS_B200_NO_SEPARABLE");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v != 0;
 }
 
 int sm_count(int device) {
@@ -120,6 +132,10 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
     const long long tiles = (HW + p->tile_px - 1) / p->tile_px;
     if (tiles > 0x7fffffffLL) return IGS_ERR_LIMIT;
     p->tiles = (int)tiles;
+    // separable tiling (16 x 64 pixel tiles); the split count chosen below serves both
+    p->tiles_x = (W + forward_sep_tile_w() - 1) / forward_sep_tile_w();
+    const long long tiles_sep = (long long)p->tiles_x * ((H + forward_sep_tile_h() - 1) / forward_sep_tile_h());
+    p->tiles_sep = (forward_has_separable(ct) && tiles_sep <= 0x7fffffffLL) ? (int)tiles_sep : 0;
     p->chunk_g = forward_chunk_g(ct);
     p->stages = 2;
     const long long slots = (long long)sm_count(device) * forward_ctas_per_sm(ct, device);
@@ -264,6 +280,19 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
 
     const bool in_kernel = normalize && p.n_split == 1;
     const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    // separable grid (x by column, y by row)?  known from the strides, or checked on the device
+    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    const GridKind grid_kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && p.tiles_sep > 0);
+    if (grid_kind == GRID_CHECK_ON_DEVICE) {
+        GridCheckArgs ga;
+        ga.x = x; ga.y = y;
+        ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;
+        ga.ys_b = sy.b; ga.ys_h = sy.h; ga.ys_w = sy.w;
+        ga.flag = grid_flag;
+        ga.B = B; ga.H = H; ga.W = W;
+        e = launch_grid_check(ga, st);
+        if (e != cudaSuccess) return (int)e;
+    }
     for (int k = 0; k < p.ch.n; ++k) {
         FwdArgs fa;
         std::memset(&fa, 0, sizeof(fa));
@@ -284,8 +313,19 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         fa.in_kernel_normalize = in_kernel ? 1 : 0;
         fa.write_s = (k == 0) ? 1 : 0;
         fa.eps = eps;
-        e = launch_forward_chunk(p.ch.ct[k], fa, p, st);
-        if (e != cudaSuccess) return (int)e;
+        fa.tiles_x = p.tiles_x;
+        const GridKind gk = forward_has_separable(p.ch.ct[k]) ? grid_kind : GRID_GENERAL;
+        fa.grid_flag = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
+        if (gk != GRID_GENERAL) {
+            e = launch_forward_chunk(p.ch.ct[k], true, fa, p, st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (gk != GRID_SEPARABLE) {
+            // a chunk without a separable instantiation runs whatever the flag says
+            if (gk == GRID_GENERAL) fa.grid_flag = nullptr;
+            e = launch_forward_chunk(p.ch.ct[k], false, fa, p, st);
+            if (e != cudaSuccess) return (int)e;
+        }
     }
     if (p.n_split > 1) {
         ReduceArgs ra;

@@ -139,7 +139,7 @@ void count_launch(int n = 1);
 int sm_count(int device);
 
 // Kernel ids for igs_profile_read (include/igs_b200.h lists them as IGS_KERNEL_*).
-enum KernelId { K_PACK = 0, K_FORWARD, K_REDUCE, K_PIXEL_TERMS, K_BACKWARD, K_FINALIZE, K_COORD_GRAD, K_COUNT };
+enum KernelId { K_PACK = 0, K_FORWARD, K_REDUCE, K_PIXEL_TERMS, K_BACKWARD, K_FINALIZE, K_COORD_GRAD, K_GRID_CHECK, K_COUNT };
 
 // When profiling is enabled, brackets one launch with CUDA events on its own stream;
 // otherwise does nothing.

@@ -10,6 +10,18 @@
 //   q  = dx*(A*dx + B2*dy) + (Cq*dy)*dy            (pre-scaled by -0.5*log2 e)
 //   e  = ex2(q);  S += e*alpha;  num_c += e*(alpha*colour_c)
 // i.e. 11 FMA-pipe instructions and one MUFU per gaussian x pixel at C = 3.
+//
+// Two instantiations per channel count:
+//   general (SEP = false): any sample coordinates x[b,h,w], y[b,h,w]; a thread's pixels
+//     are consecutive pairs of the flattened image;
+//   separable (SEP = true): x depends on the column only and y on the row only (what
+//     xy_grid produces).  A thread owns a 2-row x 4-column patch, so dx and A*dx are
+//     computed once per column pair and dy, B2*dy, Cq*dy^2 once per row:
+//     8 instead of 11 FMA-pipe instructions per evaluation.
+// Which one applies is a property of the data; grid_check_kernel (grid.cu) decides it on
+// the device and both instantiations are launched, the one whose mode does not match
+// the flag returning at once (no host synchronisation).
+//
 // Epilogue: with a single split the CTA divides by (S + eps) itself, otherwise it
 // stores un-normalised partial sums that reduce_normalize_kernel adds in split order
 // (deterministic; no atomics anywhere).
@@ -44,11 +56,18 @@ struct FwdCfg {
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
 };
 
-template <int CT, int PX_>
+// Separable tiles: 16 rows x 64 columns per CTA, 2 rows x 4 columns per thread.
+constexpr int SEP_TILE_H = 16, SEP_TILE_W = 64;
+
+template <int CT, int PX_, bool SEP>
 __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN_CTAS)
     splat_forward_kernel(FwdArgs a) {
     using Cfg = FwdCfg<CT, PX_>;
     constexpr int T = Cfg::THREADS, NP = Cfg::PX / 2, G = Cfg::CHUNK_G, NS = Cfg::STAGES, RS = Cfg::RS;
+    static_assert(!SEP || PX_ == 8, "the separable patch is 2 rows x 4 columns");
+
+    // only the instantiation that matches the grid's kind does the work
+    if (a.grid_flag && ((*a.grid_flag != 0) == SEP)) return;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* stage_base = reinterpret_cast<float*>(smem_raw);
@@ -58,28 +77,44 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
     const int tid = threadIdx.x;
     const int b = blockIdx.z, split = blockIdx.y;
     const long long HW = (long long)a.H * a.W;
-    const long long tile_base = (long long)blockIdx.x * (T * Cfg::PX);
 
-    // ---- pixel coordinates (arbitrary strides; read once) ----
-    f2 xx[NP], yy[NP];
+    // ---- this thread's pixels: pair j, lane k -> (row, column) ----
+    // general: consecutive pairs of the flattened image, interleaved over the CTA's threads
+    const long long tile_base = (long long)blockIdx.x * (T * Cfg::PX);
+    // separable: rows h0, h0+1 and columns w0 .. w0+3
+    const int tile_y = SEP ? (int)(blockIdx.x / a.tiles_x) : 0, tile_x = SEP ? (int)(blockIdx.x % a.tiles_x) : 0;
+    const int h0 = tile_y * SEP_TILE_H + (tid >> 4) * 2, w0 = tile_x * SEP_TILE_W + (tid & 15) * 4;
+
+    f2 xx[NP], yy[NP];  // general: per pair.  separable: xx[0..1] = column pairs, yy[0] = {row0,row1}
+    if constexpr (SEP) {
+        float xv[4], yv[2];
 #pragma unroll
-    for (int j = 0; j < NP; ++j) {
-        const long long p0 = tile_base + (long long)(j * T + tid) * 2;
-        float xv[2], yv[2];
+        for (int k = 0; k < 4; ++k) xv[k] = a.x[b * a.xs_b + (long long)min(w0 + k, a.W - 1) * a.xs_w];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const long long p = p0 + k;
-            if (p < HW) {
-                const long long h = p / a.W, w = p - h * a.W;
-                xv[k] = a.x[b * a.xs_b + h * a.xs_h + w * a.xs_w];
-                yv[k] = a.y[b * a.ys_b + h * a.ys_h + w * a.ys_w];
-            } else {
-                xv[k] = 0.f;
-                yv[k] = 0.f;
+        for (int k = 0; k < 2; ++k) yv[k] = a.y[b * a.ys_b + (long long)min(h0 + k, a.H - 1) * a.ys_h];
+        xx[0] = pk(xv[0], xv[1]);
+        xx[1] = pk(xv[2], xv[3]);
+        yy[0] = pk(yv[0], yv[1]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+            const long long p0 = tile_base + (long long)(j * T + tid) * 2;
+            float xv[2], yv[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const long long p = p0 + k;
+                if (p < HW) {
+                    const long long h = p / a.W, w = p - h * a.W;
+                    xv[k] = a.x[b * a.xs_b + h * a.xs_h + w * a.xs_w];
+                    yv[k] = a.y[b * a.ys_b + h * a.ys_h + w * a.ys_w];
+                } else {
+                    xv[k] = 0.f;
+                    yv[k] = 0.f;
+                }
             }
+            xx[j] = pk(xv[0], xv[1]);
+            yy[j] = pk(yv[0], yv[1]);
         }
-        xx[j] = pk(xv[0], xv[1]);
-        yy[j] = pk(yv[0], yv[1]);
     }
 
     f2 S[NP], acc[NP][CT];
@@ -141,23 +176,40 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
                 const float4 t4 = rf[q];
                 vals[4 * q] = t4.x; vals[4 * q + 1] = t4.y; vals[4 * q + 2] = t4.z; vals[4 * q + 3] = t4.w;
             }
-            ulonglong2 r0, r1, r2;
-            r0.x = pk(vals[0], vals[0]); r0.y = pk(vals[1], vals[1]);
-            r1.x = pk(vals[2], vals[2]); r1.y = pk(vals[3], vals[3]);
-            r2.x = pk(vals[4], vals[4]); r2.y = pk(vals[5], vals[5]);
+            const f2 px2 = pk(vals[0], vals[0]), py2 = pk(vals[1], vals[1]);
+            const f2 A2 = pk(vals[2], vals[2]), B22 = pk(vals[3], vals[3]);
+            const f2 Cq2 = pk(vals[4], vals[4]), al2 = pk(vals[5], vals[5]);
             f2 col[CT + 1];
 #pragma unroll
             for (int c = 0; c < CT; ++c) col[c] = pk(vals[6 + c], vals[6 + c]);
+            if constexpr (SEP) {
+                // per column pair: dx, A*dx;  per row (both rows in one f32x2): B2*dy, Cq*dy^2
+                const f2 dxc[2] = {sub2(xx[0], px2), sub2(xx[1], px2)};
+                const f2 adx[2] = {mul2(A2, dxc[0]), mul2(A2, dxc[1])};
+                const f2 dyr = sub2(yy[0], py2);
+                float b0, b1, c0, c1;
+                upk(mul2(B22, dyr), b0, b1);
+                upk(mul2(mul2(Cq2, dyr), dyr), c0, c1);
+                const f2 bd[2] = {pk(b0, b0), pk(b1, b1)}, cd[2] = {pk(c0, c0), pk(c1, c1)};
 #pragma unroll
-            for (int j = 0; j < NP; ++j) {
-                const f2 dx = sub2(xx[j], r0.x);
-                const f2 dy = sub2(yy[j], r0.y);
-                const f2 t = fma2(r1.x, dx, mul2(r1.y, dy));
-                const f2 v = mul2(mul2(r2.x, dy), dy);
-                const f2 e = ex2_2(fma2(dx, t, v));
-                S[j] = fma2(e, r2.y, S[j]);
+                for (int j = 0; j < NP; ++j) {  // j = 2*row + column pair
+                    const f2 e = ex2_2(fma2(dxc[j & 1], add2(adx[j & 1], bd[j >> 1]), cd[j >> 1]));
+                    S[j] = fma2(e, al2, S[j]);
 #pragma unroll
-                for (int c = 0; c < CT; ++c) acc[j][c] = fma2(e, col[c], acc[j][c]);
+                    for (int c = 0; c < CT; ++c) acc[j][c] = fma2(e, col[c], acc[j][c]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    const f2 dx = sub2(xx[j], px2);
+                    const f2 dy = sub2(yy[j], py2);
+                    const f2 t = fma2(A2, dx, mul2(B22, dy));
+                    const f2 v = mul2(mul2(Cq2, dy), dy);
+                    const f2 e = ex2_2(fma2(dx, t, v));
+                    S[j] = fma2(e, al2, S[j]);
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) acc[j][c] = fma2(e, col[c], acc[j][c]);
+                }
             }
         }
         __syncthreads();  // every lane is done with this stage
@@ -167,7 +219,6 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
     // ---- epilogue ----
 #pragma unroll
     for (int j = 0; j < NP; ++j) {
-        const long long p0 = tile_base + (long long)(j * T + tid) * 2;
         float s0, s1;
         upk(S[j], s0, s1);
         const float sv[2] = {s0, s1};
@@ -176,8 +227,15 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
         for (int c = 0; c < CT; ++c) upk(acc[j][c], num[c][0], num[c][1]);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-            const long long p = p0 + k;
-            if (p >= HW) continue;
+            long long p;
+            if constexpr (SEP) {
+                const int h = h0 + (j >> 1), w = w0 + (j & 1) * 2 + k;
+                if (h >= a.H || w >= a.W) continue;
+                p = (long long)h * a.W + w;
+            } else {
+                p = tile_base + (long long)(j * T + tid) * 2 + k;
+                if (p >= HW) continue;
+            }
             if (a.in_kernel_normalize) {
                 const float den = sv[k] + a.eps;
 #pragma unroll
@@ -221,22 +279,22 @@ __global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
     }
 }
 
-template <int CT, int PX_>
+template <int CT, int PX_, bool SEP>
 static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
     using Cfg = FwdCfg<CT, PX_>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_>,
+        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, SEP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    dim3 grid((unsigned)p.tiles, (unsigned)p.n_split, (unsigned)a.B);
+    dim3 grid((unsigned)(SEP ? p.tiles_sep : p.tiles), (unsigned)p.n_split, (unsigned)a.B);
     {
         KernelTimer timer(K_FORWARD, s);
-        splat_forward_kernel<CT, PX_><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_forward_kernel<CT, PX_, SEP><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
@@ -253,15 +311,27 @@ int forward_px_per_thread(int ct) {
     return forced ? forced : 8;
 }
 
-cudaError_t launch_forward_chunk(int ct, const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+// separable instantiations exist where the general one uses 8 pixels per thread
+bool forward_has_separable(int ct) { return ct <= 4; }
+
+cudaError_t launch_forward_chunk(int ct, bool separable, const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+    if (separable) {
+        switch (ct) {
+            case 1: return launch_one<1, 8, true>(a, p, s);
+            case 2: return launch_one<2, 8, true>(a, p, s);
+            case 3: return launch_one<3, 8, true>(a, p, s);
+            case 4: return launch_one<4, 8, true>(a, p, s);
+        }
+        return cudaErrorInvalidValue;
+    }
     const bool wide = p.px_per_thread == 16;
     switch (ct) {
-        case 1: return wide ? launch_one<1, 16>(a, p, s) : launch_one<1, 8>(a, p, s);
-        case 2: return wide ? launch_one<2, 16>(a, p, s) : launch_one<2, 8>(a, p, s);
-        case 3: return wide ? launch_one<3, 16>(a, p, s) : launch_one<3, 8>(a, p, s);
-        case 4: return wide ? launch_one<4, 16>(a, p, s) : launch_one<4, 8>(a, p, s);
-        case 8: return launch_one<8, 4>(a, p, s);
-        case 16: return launch_one<16, 4>(a, p, s);
+        case 1: return wide ? launch_one<1, 16, false>(a, p, s) : launch_one<1, 8, false>(a, p, s);
+        case 2: return wide ? launch_one<2, 16, false>(a, p, s) : launch_one<2, 8, false>(a, p, s);
+        case 3: return wide ? launch_one<3, 16, false>(a, p, s) : launch_one<3, 8, false>(a, p, s);
+        case 4: return wide ? launch_one<4, 16, false>(a, p, s) : launch_one<4, 8, false>(a, p, s);
+        case 8: return launch_one<8, 4, false>(a, p, s);
+        case 16: return launch_one<16, 4, false>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -282,10 +352,11 @@ static int occ(int device) {
     using Cfg = FwdCfg<CT, PX_>;
     static int cached[64];
     if (device >= 0 && device < 64 && cached[device]) return cached[device];
-    cudaFuncSetAttribute(splat_forward_kernel<CT, PX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+    cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Cfg::SMEM);
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT, PX_>, Cfg::THREADS, Cfg::SMEM) !=
-            cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT, PX_, false>, Cfg::THREADS,
+                                                      Cfg::SMEM) != cudaSuccess ||
         n <= 0) {
         cudaGetLastError();
         n = Cfg::MIN_CTAS;
@@ -307,5 +378,7 @@ int forward_ctas_per_sm(int ct, int device) {
 }
 int forward_threads(int) { return 128; }
 int forward_chunk_g(int) { return 128; }
+int forward_sep_tile_h() { return SEP_TILE_H; }
+int forward_sep_tile_w() { return SEP_TILE_W; }
 
 }  // namespace igs

@@ -14,6 +14,8 @@ struct FwdArgs {
     float* wsum;     // [B, HW]         (in_kernel_normalize && write_s)
     float* partial;  // [n_split, B, C+1, HW] otherwise
     int* status;
+    const int* grid_flag;  // device word: 0 = separable grid; nullptr = run unconditionally
+    int tiles_x;           // separable tiling: CTAs per tile row
     int B, N, H, W, C;
     int c0, cr;  // first channel and real channel count of this chunk
     int per_split;
@@ -31,7 +33,7 @@ struct ReduceArgs {
     float eps;
 };
 
-cudaError_t launch_forward_chunk(int ct, const FwdArgs& a, const FwdPlan& p, cudaStream_t s);
+cudaError_t launch_forward_chunk(int ct, bool separable, const FwdArgs& a, const FwdPlan& p, cudaStream_t s);
 cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s);
 
 }  // namespace igs

@@ -22,7 +22,9 @@ struct FwdPlan {
     int threads;        // threads per CTA
     int px_per_thread;  // pixels each thread owns (even)
     int tile_px;        // threads * px_per_thread
-    int tiles;          // CTAs along the pixel axis, per batch element
+    int tiles;          // CTAs along the pixel axis, per batch element (general kernel)
+    int tiles_sep;      // the same for the separable kernel (16 x 64 pixel tiles), 0 = not available
+    int tiles_x;        // separable tiles per tile row
     int n_split;        // CTAs along the gaussian axis
     int per_split;      // gaussians per split
     int chunk_g;        // gaussians per shared-memory stage
@@ -66,6 +68,9 @@ int backward_ctas_per_sm(int ct, int device);
 int forward_px_per_thread(int ct);
 int forward_threads(int ct);
 int forward_chunk_g(int ct);
+bool forward_has_separable(int ct);
+int forward_sep_tile_h();
+int forward_sep_tile_w();
 int backward_threads(int ct);
 int backward_gauss_per_thread(int ct);
 int backward_chunk_pairs(int ct);

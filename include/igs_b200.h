@@ -176,7 +176,8 @@ int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_ti
 #define IGS_KERNEL_BACKWARD 4     /* backward splat */
 #define IGS_KERNEL_FINALIZE 5     /* per-gaussian gradient epilogue */
 #define IGS_KERNEL_COORD_GRAD 6   /* d_x, d_y */
-#define IGS_KERNEL_COUNT 7
+#define IGS_KERNEL_GRID_CHECK 7   /* separable-grid detection */
+#define IGS_KERNEL_COUNT 8
 int igs_profile_enable(int on);
 int igs_profile_reset(void);
 int igs_profile_read(int kernel_id, double* total_ms, long long* launches);
