@@ -349,25 +349,37 @@ def run_b200(args):
         fp32_peak = max(probes["fp32_scalar_lane_instr_per_s"], probes["fp32_packed_lane_instr_per_s"])
         mix_ceiling = {"forward": probes["fp32_forward_mix_lane_instr_per_s"],
                        "backward": probes["fp32_backward_mix_lane_instr_per_s"]}
-        executed = {"forward": 8 + C, "backward": 16 + 2 * C}  # FMA-pipe instructions the kernels issue
-        # canonical FMA-pipe instruction counts per gaussian x pixel (fwd 9+C, bwd 18+2C)
+        # The workloads sample on xy_grid, which the library detects on the device as a
+        # separable grid (x by column, y by row) and serves with kernels that share the
+        # row / column terms: they ISSUE fewer FMA-pipe instructions per evaluation than the
+        # canonical count for arbitrary sample points (fwd 9+C, bwd 18+2C).  `frac` follows
+        # the canonical count, so it can exceed 1; `executed_frac` is the pipe's utilisation.
+        separable = (os.environ.get("IGS_B200_NO_SEPARABLE") != "1" and C <= 4 and cfg.H >= 4 and cfg.W >= 16)
+        if separable:
+            executed = {"forward": 5 + C, "backward": 8 + 2 * C}
+        else:
+            executed = {"forward": 8 + C, "backward": 16 + 2 * C}
         instr = {"forward": 9 + C, "backward": 18 + 2 * C}
+        suffix = "_sep" if separable else ""
 
         def kernel_roof(name):
             ms, n = prof[name]
             if n == 0:
                 return None
-            per_launch_s = ms / n * 1e-3
-            ach = ev_rank * instr[name] / per_launch_s
-            return {"bound": "fp32_fma_pipe", "kernel": f"splat_{name}_kernel", "achieved": ach / 1e12,
+            # device time of this kernel per pass (with the on-device grid check, the
+            # instantiation that does not match returns at once; its launch is included)
+            per_pass_s = ms / steps * 1e-3
+            ach = ev_rank * instr[name] / per_pass_s
+            return {"bound": "fp32_fma_pipe", "kernel": f"splat_{name}{suffix}_kernel", "achieved": ach / 1e12,
                     "peak": fp32_peak / 1e12, "unit": "T lane-instr/s", "frac": ach / fp32_peak,
-                    "launch_ms": ms / n, "launches": n,
+                    "launch_ms": ms / steps, "launches": n,
                     "algorithmic_instr_per_eval": instr[name],
                     "executed_instr_per_eval": executed[name],
-                    "executed_frac": ev_rank * executed[name] / per_launch_s / fp32_peak,
-                    "mix_ceiling_frac": mix_ceiling[name] / fp32_peak,
+                    "executed_frac": ev_rank * executed[name] / per_pass_s / fp32_peak,
+                    "mix_ceiling_frac": None if separable else mix_ceiling[name] / fp32_peak,
+                    "grid": "separable (xy_grid), detected on the device" if separable else "general",
                     "peak_source": "measured live: FFMA-only kernel, best of scalar and f32x2 (igs_probe_fp32_rate)",
-                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(cfg.name, {}).get(name)}
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(cfg.name + suffix, {}).get(name)}
 
         roof = kernel_roof("backward")
         roof_f = kernel_roof("forward")
@@ -394,6 +406,9 @@ def run_b200(args):
             "roofline_step": {"bound": "fp32_fma_pipe", "achieved": step_ach / 1e12, "peak": fp32_peak / 1e12,
                               "unit": "T lane-instr/s", "frac": step_ach / fp32_peak,
                               "algorithmic_instr_per_eval": 27 + 3 * C,
+                              "executed_instr_per_eval": executed["forward"] + executed["backward"],
+                              "executed_frac": step_ach / fp32_peak * (executed["forward"] + executed["backward"])
+                              / (27 + 3 * C),
                               "nominal_peak": n_sm * 128 * (sm or 0) * 1e6 / 1e12 if sm else None},
             "probes": probes,
             "hbm": {"algorithmic_bytes_per_step": hbm_bytes,

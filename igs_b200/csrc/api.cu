@@ -187,6 +187,12 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
     p->n_slab = (int)((p->npairs + per - 1) / per);
     if (p->n_slab < 1) p->n_slab = 1;
     p->planes = N_MOMENTS * p->ch.n + C;
+    // separable variant: same slab count, slabs are ranges of whole row pairs
+    p->nrp = (H + 1) / 2;
+    p->ncb = (W + 3) / 4;
+    p->rp_per_slab = (p->nrp + p->n_slab - 1) / p->n_slab;
+    if (p->rp_per_slab < 1) p->rp_per_slab = 1;
+    p->sep_ok = (p->ch.n == 1 && backward_has_separable(ct)) ? 1 : 0;
 
     size_t off = STATUS_BYTES;
     const long long M = (long long)B * N;
@@ -194,7 +200,12 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
     off = align_up(off + (size_t)M * GEO_FLOATS * sizeof(float), 256);
     for (int k = 0; k < p->ch.n; ++k) {
         p->off_prec[k] = off;
-        off = align_up(off + (size_t)B * p->npairs * bwd_rec_floats(p->ch.ct[k]) * sizeof(float), 256);
+        size_t rec_bytes = (size_t)B * p->npairs * bwd_rec_floats(p->ch.ct[k]) * sizeof(float);
+        if (p->sep_ok) {
+            const size_t sep_bytes = (size_t)B * p->nrp * p->ncb * bwd_sep_rec_floats(p->ch.ct[k]) * sizeof(float);
+            if (sep_bytes > rec_bytes) rec_bytes = sep_bytes;
+        }
+        off = align_up(off + rec_bytes, 256);
     }
     p->off_part = off;
     off = align_up(off + (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float), 256);
@@ -420,11 +431,33 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     for (int k = 0; k < p.ch.n; ++k) ta.prec[k] = reinterpret_cast<float*>(ws + p.off_prec[k]);
     ta.ch = p.ch;
     ta.npairs = p.npairs;
+    ta.nrp = p.nrp;
+    ta.ncb = p.ncb;
+    // separable grid?  (same decision procedure as the forward)
+    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    const GridKind grid_kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && p.sep_ok);
+    if (grid_kind == GRID_CHECK_ON_DEVICE) {
+        GridCheckArgs ga;
+        ga.x = x; ga.y = y;
+        ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;
+        ga.ys_b = sy.b; ga.ys_h = sy.h; ga.ys_w = sy.w;
+        ga.flag = grid_flag;
+        ga.B = B; ga.H = H; ga.W = W;
+        e = launch_grid_check(ga, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    ta.grid_flag = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
     ta.B = B; ta.H = H; ta.W = W; ta.C = C;
     ta.mode = mode;
     ta.eps = eps;
-    e = launch_pixel_terms(ta, st);
-    if (e != cudaSuccess) return (int)e;
+    if (grid_kind != GRID_GENERAL) {
+        e = launch_pixel_terms(ta, true, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (grid_kind != GRID_SEPARABLE) {
+        e = launch_pixel_terms(ta, false, st);
+        if (e != cudaSuccess) return (int)e;
+    }
 
     for (int k = 0; k < p.ch.n; ++k) {
         BwdArgs ba;
@@ -435,6 +468,10 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.part = reinterpret_cast<float*>(ws + p.off_part);
         ba.status = reinterpret_cast<int*>(ws);
         ba.npairs = p.npairs;
+        ba.nrp = p.nrp;
+        ba.ncb = p.ncb;
+        ba.rp_per_slab = p.rp_per_slab;
+        ba.grid_flag = ta.grid_flag;
         ba.pairs_per_slab = p.pairs_per_slab;
         ba.B = B; ba.N = N; ba.C = C;
         ba.c0 = p.ch.c0[k];
@@ -442,8 +479,14 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.planes = p.planes;
         ba.moment_plane0 = N_MOMENTS * k;
         ba.color_plane0 = N_MOMENTS * p.ch.n;
-        e = launch_backward_chunk(p.ch.ct[k], ba, p, st);
-        if (e != cudaSuccess) return (int)e;
+        if (grid_kind != GRID_GENERAL) {
+            e = launch_backward_chunk(p.ch.ct[k], true, ba, p, st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (grid_kind != GRID_SEPARABLE) {
+            e = launch_backward_chunk(p.ch.ct[k], false, ba, p, st);
+            if (e != cudaSuccess) return (int)e;
+        }
     }
 
     FinalizeArgs fa;

@@ -29,6 +29,7 @@ namespace igs {
 // per-pixel upstream terms
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) pixel_terms_kernel(PixelTermArgs a) {
+    if (a.grid_flag && *a.grid_flag == 0) return;  // separable grid: the block-record kernel runs
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*npairs
     if (i >= (long long)a.B * a.npairs) return;
     const long long b = i / a.npairs, pair = i - b * a.npairs;
@@ -84,7 +85,8 @@ __global__ void __launch_bounds__(256) pixel_terms_kernel(PixelTermArgs a) {
     }
 }
 
-cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s) {
+cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStream_t s) {
+    if (separable) return launch_pixel_terms_sep(a, s);
     const long long n = (long long)a.B * a.npairs;
     if (n <= 0) return cudaSuccess;
     {
@@ -134,6 +136,8 @@ __global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN
     splat_backward_kernel(BwdArgs a) {
     using Cfg = BwdCfg<CT, GPT>;
     constexpr int T = Cfg::THREADS, PC = Cfg::CHUNK_PAIRS, NS = Cfg::STAGES, RS = Cfg::RS, NACC = Cfg::NACC;
+
+    if (a.grid_flag && *a.grid_flag == 0) return;  // separable grid: splat_backward_sep_kernel runs
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* stage_base = reinterpret_cast<float*>(smem_raw);
@@ -300,7 +304,8 @@ static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s
     return cudaGetLastError();
 }
 
-cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+cudaError_t launch_backward_chunk(int ct, bool separable, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    if (separable) return launch_backward_sep_chunk(ct, a, p, s);
     const bool two = p.gauss_per_thread >= 2;
     switch (ct) {
         case 1: return two ? launch_one<1, IGS_BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);

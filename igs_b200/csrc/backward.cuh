@@ -14,9 +14,11 @@ struct PixelTermArgs {
     const float* wsum;  // [B, HW]
     const float* out;   // [B, C, HW]  (exact mode only)
     const float* gout;  // [B, C, HW]
-    float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]
+    float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]  or, separable, [B, nrp*ncb, bwd_sep_rec_floats(ct)]
+    const int* grid_flag;     // 0 = separable; nullptr = run unconditionally
     Chunks ch;
     long long npairs;
+    int nrp, ncb;             // separable: row pairs and 4-column blocks per row pair
     int B, H, W, C;
     int mode;
     float eps;
@@ -28,7 +30,9 @@ struct BwdArgs {
     const float* prec;    // records of this chunk
     float* part;          // [n_slab, B, planes, N]
     int* status;
+    const int* grid_flag;  // 0 = separable; nullptr = run unconditionally
     long long npairs, pairs_per_slab;
+    int nrp, ncb, rp_per_slab;  // separable: row pairs, blocks per row pair, row pairs per slab
     int B, N, C;
     int c0, cr;
     int planes;
@@ -71,8 +75,11 @@ struct CoordGradArgs {
     float eps;
 };
 
-cudaError_t launch_pixel_terms(const PixelTermArgs& a, cudaStream_t s);
-cudaError_t launch_backward_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStream_t s);
+cudaError_t launch_backward_chunk(int ct, bool separable, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+bool backward_has_separable(int ct);
+cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
+cudaError_t launch_backward_sep_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
 cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
 

@@ -1,0 +1,343 @@
+// Backward splat kernel for separable grids (x by column, y by row; what xy_grid makes).
+//
+// Same ownership as the general backward kernel (a thread owns gaussians, pixels stream
+// through shared memory by bulk copies) but the pixels arrive as 2-row x 4-column
+// blocks, row pair after row pair, and a slab is a range of whole row pairs.  With
+// h = G*e as before, the six moments factor along a row of constant dy:
+//   M0 = sum_rows hs_r              Mx  = sum_rows hxs_r
+//   My = sum_rows dy_r*hs_r         Mxy = sum_rows dy_r*hxs_r        Myy = sum_rows dy_r^2*hs_r
+//   Mxx = sum h*dx*dx               with  hs_r = sum_cols h,  hxs_r = sum_cols h*dx
+// so per pixel only hs, hxs and Mxx are updated, and the row-level products are formed
+// once per row pair.  The exponent shares its terms the same way as in the separable
+// forward (dx, A*dx per column pair; B2*dy, Cq*dy^2 per row).  Per gaussian x pixel that
+// is 13 FMA-pipe instructions + 1 per pixel of column terms instead of 22, at C = 3:
+//   s = A*dx + B2*dy; q = dx*s + Cq*dy^2              2      G = gS + sum_c gn_c*col_c   3
+//   h = G*e; hs += h; hx = h*dx; hxs += hx; Mxx += hx*dx  5  E_c += gn_c*e               3
+#include "backward.cuh"
+
+namespace igs {
+
+// ---------------------------------------------------------------------------
+// per-pixel upstream terms, block records
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
+    if (a.grid_flag && *a.grid_flag != 0) return;
+    const long long per_b = (long long)a.nrp * a.ncb;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*nrp*ncb
+    if (i >= (long long)a.B * per_b) return;
+    const long long b = i / per_b, blk = i - b * per_b;
+    const int rp = (int)(blk / a.ncb), cbk = (int)(blk - (long long)rp * a.ncb);
+    const long long HW = (long long)a.H * a.W;
+    const int h0 = rp * 2, w0 = cbk * 4;
+
+    float xv[4], yv[2];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) xv[k] = a.x[b * a.xs_b + (long long)min(w0 + k, a.W - 1) * a.xs_w];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) yv[k] = a.y[b * a.ys_b + (long long)min(h0 + k, a.H - 1) * a.ys_h];
+
+    // pixel (r, k): valid flag, flat index, S + eps, gS over ALL channels
+    float ok[2][4], Sp[2][4], gS[2][4];
+    long long pp[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const bool valid = (h0 + r < a.H) && (w0 + k < a.W);
+            ok[r][k] = valid ? 1.f : 0.f;
+            pp[r][k] = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + k, a.W - 1);
+            Sp[r][k] = a.wsum[b * HW + pp[r][k]] + a.eps;
+            float acc = 0.f;
+            for (int c = 0; c < a.C; ++c) {
+                const float g = a.gout[(b * a.C + c) * HW + pp[r][k]];
+                if (a.mode == IGS_GRAD_REFERENCE)
+                    acc += g * g;
+                else
+                    acc += (g / Sp[r][k]) * a.out[(b * a.C + c) * HW + pp[r][k]];
+            }
+            gS[r][k] = ok[r][k] * ((a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp[r][k] * Sp[r][k]) : -acc);
+        }
+
+    for (int q = 0; q < a.ch.n; ++q) {
+        const int ct = a.ch.ct[q], cr = a.ch.cr[q], c0 = a.ch.c0[q];
+        const int pf = bwd_sep_pair_floats(ct);
+        float* rec = a.prec[q] + i * bwd_sep_rec_floats(ct);
+        reinterpret_cast<float4*>(rec)[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
+        reinterpret_cast<float4*>(rec)[1] = make_float4(yv[0], yv[1], 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int cp = 0; cp < 2; ++cp) {
+                float* pr = rec + 8 + (r * 2 + cp) * pf;
+                pr[0] = q == 0 ? gS[r][2 * cp] : 0.f;
+                pr[1] = q == 0 ? gS[r][2 * cp + 1] : 0.f;
+                for (int c = 0; c < pf / 2 - 1; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        float v = 0.f;
+                        if (c < cr) {
+                            const int kk = 2 * cp + k;
+                            v = ok[r][kk] * (a.gout[(b * a.C + c0 + c) * HW + pp[r][kk]] / Sp[r][kk]);
+                        }
+                        pr[2 + 2 * c + k] = v;
+                    }
+                }
+            }
+    }
+}
+
+cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s) {
+    const long long n = (long long)a.B * a.nrp * a.ncb;
+    if (n <= 0) return cudaSuccess;
+    {
+        KernelTimer timer(K_PIXEL_TERMS, s);
+        pixel_terms_sep_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------
+template <int CT>
+struct BwdSepCfg {
+    static constexpr int THREADS = 128;
+    static constexpr int GPT = 2;  // gaussians per thread
+    static constexpr int GAUSS_PER_CTA = THREADS * GPT;
+    static constexpr int CHUNK_BLOCKS = 64;  // 2x4-pixel blocks per shared-memory stage
+    static constexpr int STAGES = 2;
+#ifdef IGS_BWDSEP_MINCTAS
+    static constexpr int MIN_CTAS = IGS_BWDSEP_MINCTAS;
+#else
+    static constexpr int MIN_CTAS = CT <= 3 ? 4 : 3;
+#endif
+    static constexpr int RS = bwd_sep_rec_floats(CT);
+    static constexpr int PF = bwd_sep_pair_floats(CT);
+    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_BLOCKS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
+};
+
+template <int CT>
+__global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTAS) splat_backward_sep_kernel(BwdArgs a) {
+    using Cfg = BwdSepCfg<CT>;
+    constexpr int T = Cfg::THREADS, GPT = Cfg::GPT, PCB = Cfg::CHUNK_BLOCKS, NS = Cfg::STAGES, RS = Cfg::RS, PF = Cfg::PF;
+
+    if (a.grid_flag && *a.grid_flag != 0) return;  // not a separable grid: the general kernel runs
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* stage_base = reinterpret_cast<float*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NS * PCB * RS * sizeof(float));
+    int* s_failed = reinterpret_cast<int*>(bars + NS);
+
+    const int tid = threadIdx.x;
+    const int b = blockIdx.z, slab = blockIdx.y;
+
+    // ---- this thread's gaussians ----
+    int n[GPT];
+    f2 px[GPT], py[GPT], A[GPT], B2[GPT], Cq[GPT], col[GPT][CT];
+#pragma unroll
+    for (int g = 0; g < GPT; ++g) {
+        n[g] = blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        const int nn = n[g] < a.N ? n[g] : a.N - 1;
+        const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
+        const float4 g0 = gp[0], g1 = gp[1];
+        px[g] = pk(g0.x, g0.x);
+        py[g] = pk(g0.y, g0.y);
+        A[g] = pk(g0.z, g0.z);
+        B2[g] = pk(g0.w, g0.w);
+        Cq[g] = pk(g1.x, g1.x);
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
+            col[g][c] = pk(v, v);
+        }
+    }
+
+    // totals: M0, Mx, My, Mxx, Mxy, Myy, E_c;  row-pair state: per row r of the pair
+    f2 M[GPT][N_MOMENTS], E[GPT][CT];
+    f2 dyd[GPT][2], bd[GPT][2], cd[GPT][2], hs[GPT][2], hxs[GPT][2];
+#pragma unroll
+    for (int g = 0; g < GPT; ++g) {
+#pragma unroll
+        for (int k = 0; k < N_MOMENTS; ++k) M[g][k] = 0ull;
+#pragma unroll
+        for (int c = 0; c < CT; ++c) E[g][c] = 0ull;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) dyd[g][r] = bd[g][r] = cd[g][r] = hs[g][r] = hxs[g][r] = 0ull;
+    }
+
+    // ---- this slab's row pairs, as a stream of blocks ----
+    const int rp_begin = min(a.nrp, slab * a.rp_per_slab);
+    const int rp_end = min(a.nrp, rp_begin + a.rp_per_slab);
+    const long long blk_begin = (long long)rp_begin * a.ncb;
+    const int n_total = (rp_end - rp_begin) * a.ncb;
+    const int n_chunks = (n_total + PCB - 1) / PCB;
+    const float* src = a.prec + ((long long)b * a.nrp * a.ncb + blk_begin) * RS;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+        *s_failed = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto issue = [&](int chunk) {
+        const int st = chunk % NS;
+        const int cnt = min(PCB, n_total - chunk * PCB);
+        const uint32_t bytes = (uint32_t)cnt * RS * sizeof(float);
+        mbar_expect_tx(&bars[st], bytes);
+        bulk_g2s(stage_base + (size_t)st * PCB * RS, src + (long long)chunk * PCB * RS, bytes, &bars[st]);
+    };
+    if (tid == 0) {
+        for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
+    }
+
+    int cb = 0;  // block position inside the current row pair (uniform over the CTA)
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        const int st = chunk % NS;
+        const uint32_t parity = (chunk / NS) & 1;
+        if (!mbar_wait_bounded(&bars[st], parity)) *s_failed = 1;
+        __syncthreads();
+        if (*s_failed) {
+            if (tid == 0) {
+                for (int c = chunk + 1; c < n_chunks && c < chunk + NS; ++c)
+                    mbar_wait_bounded(&bars[c % NS], (c / NS) & 1);
+                atomicOr(a.status, STATUS_WAIT_TIMEOUT);
+            }
+            return;
+        }
+        const int cnt = min(PCB, n_total - chunk * PCB);
+        const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * PCB * RS);
+
+#pragma unroll 1
+        for (int i = 0; i < cnt; ++i) {
+            const float4* r = rec + (size_t)i * (RS / 4);
+            const float4 xc = r[0];
+            const f2 xcp[2] = {pk(xc.x, xc.y), pk(xc.z, xc.w)};
+            if (cb == 0) {
+                // new row pair: row terms of the exponent, fresh row sums
+                const float4 yr = r[1];
+                const f2 yy = pk(yr.x, yr.y);
+#pragma unroll
+                for (int g = 0; g < GPT; ++g) {
+                    const f2 dyr = sub2(yy, py[g]);
+                    float d0, d1, b0, b1, c0, c1;
+                    upk(dyr, d0, d1);
+                    upk(mul2(B2[g], dyr), b0, b1);
+                    upk(mul2(mul2(Cq[g], dyr), dyr), c0, c1);
+                    dyd[g][0] = pk(d0, d0); dyd[g][1] = pk(d1, d1);
+                    bd[g][0] = pk(b0, b0);  bd[g][1] = pk(b1, b1);
+                    cd[g][0] = pk(c0, c0);  cd[g][1] = pk(c1, c1);
+                    hs[g][0] = hs[g][1] = hxs[g][0] = hxs[g][1] = 0ull;
+                }
+            }
+            f2 dxc[GPT][2], adx[GPT][2];
+#pragma unroll
+            for (int g = 0; g < GPT; ++g)
+#pragma unroll
+                for (int cp = 0; cp < 2; ++cp) {
+                    dxc[g][cp] = sub2(xcp[cp], px[g]);
+                    adx[g][cp] = mul2(A[g], dxc[g][cp]);
+                }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // j = 2*row + column pair
+                const ulonglong2* pr = reinterpret_cast<const ulonglong2*>(r + 2 + j * (PF / 4));
+                f2 gterm[PF / 2];  // gS, gn_0 .. gn_{CT-1} (+ pad)
+#pragma unroll
+                for (int c = 0; c < PF / 4; ++c) {
+                    const ulonglong2 rc = pr[c];
+                    gterm[2 * c] = rc.x;
+                    gterm[2 * c + 1] = rc.y;
+                }
+                const int row = j >> 1, cp = j & 1;
+#pragma unroll
+                for (int g = 0; g < GPT; ++g) {
+                    const f2 dx = dxc[g][cp];
+                    const f2 e = ex2_2(fma2(dx, add2(adx[g][cp], bd[g][row]), cd[g][row]));
+                    f2 G = gterm[0];
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[g][c], G);
+                    const f2 h = mul2(G, e);
+                    hs[g][row] = add2(hs[g][row], h);
+                    const f2 hx = mul2(h, dx);
+                    hxs[g][row] = add2(hxs[g][row], hx);
+                    M[g][3] = fma2(hx, dx, M[g][3]);
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) E[g][c] = fma2(gterm[1 + c], e, E[g][c]);
+                }
+            }
+            if (++cb == a.ncb) {
+                // row pair complete: fold its row sums into the moments
+                cb = 0;
+#pragma unroll
+                for (int g = 0; g < GPT; ++g)
+#pragma unroll
+                    for (int row = 0; row < 2; ++row) {
+                        M[g][0] = add2(M[g][0], hs[g][row]);
+                        M[g][1] = add2(M[g][1], hxs[g][row]);
+                        M[g][2] = fma2(dyd[g][row], hs[g][row], M[g][2]);
+                        M[g][4] = fma2(dyd[g][row], hxs[g][row], M[g][4]);
+                        M[g][5] = fma2(mul2(dyd[g][row], dyd[g][row]), hs[g][row], M[g][5]);
+                    }
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+    }
+
+#pragma unroll
+    for (int g = 0; g < GPT; ++g) {
+        if (n[g] >= a.N) continue;
+        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n[g];
+#pragma unroll
+        for (int k = 0; k < N_MOMENTS; ++k) {
+            float lo, hi;
+            upk(M[g][k], lo, hi);
+            dst[(long long)(a.moment_plane0 + k) * a.N] = lo + hi;
+        }
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            if (c < a.cr) {
+                float lo, hi;
+                upk(E[g][c], lo, hi);
+                dst[(long long)(a.color_plane0 + a.c0 + c) * a.N] = lo + hi;
+            }
+        }
+    }
+}
+
+template <int CT>
+static cudaError_t launch_sep_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    using Cfg = BwdSepCfg<CT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(splat_backward_sep_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((a.N + Cfg::GAUSS_PER_CTA - 1) / Cfg::GAUSS_PER_CTA), (unsigned)p.n_slab, (unsigned)a.B);
+    {
+        KernelTimer timer(K_BACKWARD, s);
+        splat_backward_sep_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// instantiations exist for single-chunk channel counts up to 4, two gaussians per thread
+bool backward_has_separable(int ct) { return ct <= 4 && backward_gauss_per_thread(ct) == BwdSepCfg<3>::GPT; }
+
+cudaError_t launch_backward_sep_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+    switch (ct) {
+        case 1: return launch_sep_one<1>(a, p, s);
+        case 2: return launch_sep_one<2>(a, p, s);
+        case 3: return launch_sep_one<3>(a, p, s);
+        case 4: return launch_sep_one<4>(a, p, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace igs

@@ -32,6 +32,12 @@ __host__ __device__ constexpr int fwd_rec_floats(int ct) { return (6 + ct + 3) /
 //   {x0,x1, y0,y1, gS0,gS1, gn0_0,gn0_1, ...}  padded to 4 floats
 __host__ __device__ constexpr int bwd_rec_floats(int ct) { return (6 + 2 * ct + 3) / 4 * 4; }
 
+// Backward block record (separable grids), one per 2-row x 4-column block of pixels:
+//   {x0,x1,x2,x3, y0,y1,-,-} then, per pixel pair (row 0 cols 01, row 0 cols 23, row 1 cols
+//   01, row 1 cols 23), {gS0,gS1, gn0_0,gn0_1, ...} padded to 4 floats
+__host__ __device__ constexpr int bwd_sep_pair_floats(int ct) { return (2 + 2 * ct + 3) / 4 * 4; }
+__host__ __device__ constexpr int bwd_sep_rec_floats(int ct) { return 8 + 4 * bwd_sep_pair_floats(ct); }
+
 // Moment planes written by the backward kernel per (slab, gaussian):
 //   M0, Mx, My, Mxx, Mxy, Myy, then one plane per channel of the chunk
 constexpr int N_MOMENTS = 6;

@@ -44,6 +44,9 @@ struct BwdPlan {
     int chunk_pairs;       // pixel pairs per shared-memory stage
     int stages;
     int planes;            // moment planes per (slab, batch): 6 per chunk + C
+    int sep_ok;            // a separable instantiation exists for this shape
+    int nrp, ncb;          // separable: row pairs (2 rows) and blocks (4 columns) per row pair
+    int rp_per_slab;       // separable: row pairs per slab (same n_slab as the general kernel)
     size_t off_geo;
     size_t off_prec[MAX_CHUNKS];
     size_t off_part;       // [n_slab][B][planes][N]

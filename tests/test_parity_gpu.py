@@ -213,6 +213,25 @@ def test_strided_and_broadcast_grids(dev):
     assert torch.equal(a, ref) and torch.equal(b, ref)
 
 
+def test_separable_and_general_kernels_agree(dev):
+    """A materialised xy_grid is detected on the device as separable (x by column, y by row)
+    and takes the kernels that share row / column terms; moving ONE coordinate by one ulp
+    makes the same data non-separable, so the general kernels run.  The two must agree
+    everywhere to rounding, image and gradients."""
+    import numpy as np
+
+    p, gout, x, y = _seeded(2, 500, 40, 52, 3, 0.05, 0.4, seed=41)
+    g = dict(p, x=x[:, None], y=y[:, None], gout=gout, eps=np.float32(1e-6))
+    o_sep, g_sep = _run_render(g, dev)
+    x2 = x.copy()
+    x2[1, 17, 23] = np.nextafter(x2[1, 17, 23], np.float32(10))
+    o_gen, g_gen = _run_render(dict(g, x=x2[:, None]), dev)
+    assert not torch.equal(o_sep, o_gen)  # different code paths (and one pixel moved)
+    assert_close(_np(o_gen), _np(o_sep), 2e-6, "image, general vs separable kernels")
+    for k in g_sep:
+        assert_close(_np(g_gen[k]), _np(g_sep[k]), 2e-5, f"d_{k}, general vs separable kernels")
+
+
 def test_bitwise_repeatable(dev):
     """No atomics anywhere: two runs give identical bits (also a race check)."""
     p, gout, x, y = _seeded(2, 600, 48, 40, 3, 0.05, 0.4, seed=9)
