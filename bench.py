@@ -31,8 +31,11 @@ if ROOT not in sys.path:
 NCU_DRAM_BYTES_PER_LAUNCH = {
     # profiles/splat_kernels_cfg2_dram.md
     "cfg2": {"forward": 18.93e6 + 8.23e6, "backward": 31.38e6 + 8.05e6},
+    "cfg2_sep": {"forward": 6.90e6 + 8.56e6, "backward": 26.76e6 + 7.62e6},
     # profiles/splat_kernels_cfg2_small_ncu_full.md
     "cfg2_small": {"forward": 3.46e6 + 0.01e6, "backward": 7.03e6},
+    # profiles/splat_sep_kernels_cfg2_small_ncu_full.md
+    "cfg2_small_sep": {"forward": 0.98e6 + 0.02e6, "backward": 5.98e6},
 }
 
 METRIC = "gaussian_pixel_evals_per_s_fwd_bwd"
