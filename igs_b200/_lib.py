@@ -8,6 +8,7 @@ scratch allocations the library asks for.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 import threading
 
@@ -106,11 +107,16 @@ def _strides3(t: torch.Tensor):
     return (ctypes.c_int64 * 3)(*t.stride())
 
 
-def workspace_bytes(B, N, H, W, C, device: torch.device):
+@functools.lru_cache(maxsize=256)
+def _workspace_bytes(B, N, H, W, C, index):
     f, b = _sz(0), _sz(0)
-    check("igs_workspace_bytes",
-          load().igs_workspace_bytes(B, N, H, W, C, device.index, ctypes.byref(f), ctypes.byref(b)))
+    check("igs_workspace_bytes", load().igs_workspace_bytes(B, N, H, W, C, index, ctypes.byref(f), ctypes.byref(b)))
     return int(f.value), int(b.value)
+
+
+def workspace_bytes(B, N, H, W, C, device: torch.device):
+    """(forward, backward) scratch bytes; a pure function of the shape and the device."""
+    return _workspace_bytes(int(B), int(N), int(H), int(W), int(C), device.index)
 
 
 def describe_plan(B, N, H, W, C, device: torch.device):
