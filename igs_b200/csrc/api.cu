@@ -209,7 +209,6 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
     }
     p->off_part = off;
     off = align_up(off + (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float), 256);
-    p->off_xy = off;
     p->bytes = off;
     return IGS_OK;
 }

@@ -21,8 +21,6 @@
 // and, for the scale/rotation entry, chains d_c** through the closed-form inverse.
 #include "backward.cuh"
 
-#include <cstdlib>
-
 namespace igs {
 
 // ---------------------------------------------------------------------------
@@ -335,15 +333,8 @@ static int occ(int device) {
     return n;
 }
 
-int backward_gauss_per_thread(int ct) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("IGS_B200_BWD_GPT");  // development knob: 1 or 2
-        forced = (e && e[0] == '1') ? 1 : 0;
-    }
-    if (ct > 4) return 1;
-    return forced ? forced : IGS_BWD_GPT;
-}
+// two gaussians per thread where the registers allow it (up to 4 channels per chunk)
+int backward_gauss_per_thread(int ct) { return ct > 4 ? 1 : IGS_BWD_GPT; }
 
 int backward_ctas_per_sm(int ct, int device) {
     const bool two = backward_gauss_per_thread(ct) >= 2;

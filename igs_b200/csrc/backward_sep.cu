@@ -112,6 +112,11 @@ struct BwdSepCfg {
 #else
     static constexpr int MIN_CTAS = CT <= 3 ? 4 : 3;
 #endif
+#ifdef IGS_BWDSEP_UNROLL
+    static constexpr int UNROLL = IGS_BWDSEP_UNROLL;
+#else
+    static constexpr int UNROLL = 1;
+#endif
     static constexpr int RS = bwd_sep_rec_floats(CT);
     static constexpr int PF = bwd_sep_pair_floats(CT);
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_BLOCKS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
@@ -209,7 +214,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         const int cnt = min(PCB, n_total - chunk * PCB);
         const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * PCB * RS);
 
-#pragma unroll 1
+#pragma unroll(Cfg::UNROLL)
         for (int i = 0; i < cnt; ++i) {
             const float4* r = rec + (size_t)i * (RS / 4);
             const float4 xc = r[0];

@@ -27,8 +27,6 @@
 // (deterministic; no atomics anywhere).
 #include "forward.cuh"
 
-#include <cstdlib>
-
 namespace igs {
 
 // PX = pixels per thread.  A forward record costs 3 sixteen-byte broadcast reads per
@@ -50,7 +48,7 @@ struct FwdCfg {
 #ifdef IGS_FWD_UNROLL
     static constexpr int UNROLL = IGS_FWD_UNROLL;
 #else
-    static constexpr int UNROLL = PX_ >= 16 ? 1 : (CT <= 3 ? 4 : 2);
+    static constexpr int UNROLL = CT <= 3 ? 4 : 2;
 #endif
     static constexpr int RS = fwd_rec_floats(CT);
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
@@ -300,16 +298,7 @@ static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s
     return cudaGetLastError();
 }
 
-int forward_px_per_thread(int ct) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("IGS_B200_FWD_PX");  // development knob: 8 or 16
-        forced = e ? atoi(e) : 0;
-        if (forced != 8 && forced != 16) forced = 0;
-    }
-    if (ct > 4) return 4;
-    return forced ? forced : 8;
-}
+int forward_px_per_thread(int ct) { return ct > 4 ? 4 : 8; }
 
 // separable instantiations exist where the general one uses 8 pixels per thread
 bool forward_has_separable(int ct) { return ct <= 4; }
@@ -324,12 +313,11 @@ cudaError_t launch_forward_chunk(int ct, bool separable, const FwdArgs& a, const
         }
         return cudaErrorInvalidValue;
     }
-    const bool wide = p.px_per_thread == 16;
     switch (ct) {
-        case 1: return wide ? launch_one<1, 16, false>(a, p, s) : launch_one<1, 8, false>(a, p, s);
-        case 2: return wide ? launch_one<2, 16, false>(a, p, s) : launch_one<2, 8, false>(a, p, s);
-        case 3: return wide ? launch_one<3, 16, false>(a, p, s) : launch_one<3, 8, false>(a, p, s);
-        case 4: return wide ? launch_one<4, 16, false>(a, p, s) : launch_one<4, 8, false>(a, p, s);
+        case 1: return launch_one<1, 8, false>(a, p, s);
+        case 2: return launch_one<2, 8, false>(a, p, s);
+        case 3: return launch_one<3, 8, false>(a, p, s);
+        case 4: return launch_one<4, 8, false>(a, p, s);
         case 8: return launch_one<8, 4, false>(a, p, s);
         case 16: return launch_one<16, 4, false>(a, p, s);
     }
@@ -366,12 +354,11 @@ static int occ(int device) {
 }
 
 int forward_ctas_per_sm(int ct, int device) {
-    const bool wide = forward_px_per_thread(ct) == 16;
     switch (ct) {
-        case 1: return wide ? occ<1, 16>(device) : occ<1, 8>(device);
-        case 2: return wide ? occ<2, 16>(device) : occ<2, 8>(device);
-        case 3: return wide ? occ<3, 16>(device) : occ<3, 8>(device);
-        case 4: return wide ? occ<4, 16>(device) : occ<4, 8>(device);
+        case 1: return occ<1, 8>(device);
+        case 2: return occ<2, 8>(device);
+        case 3: return occ<3, 8>(device);
+        case 4: return occ<4, 8>(device);
         case 8: return occ<8, 4>(device);
         default: return occ<16, 4>(device);
     }

@@ -50,7 +50,6 @@ struct BwdPlan {
     size_t off_geo;
     size_t off_prec[MAX_CHUNKS];
     size_t off_part;       // [n_slab][B][planes][N]
-    size_t off_xy;         // scratch of the coordinate-gradient kernel (none today)
     size_t bytes;
 };
 
