@@ -68,7 +68,7 @@ class ImageFitter(nn.Module):
         key = (int(size[0]), int(size[1]), str(self.position.device))
         if key not in self._grids:
             x_grid, y_grid = GaussianSplatting2D.xy_grid(size, self.position.device)
-            self._grids[key] = (x_grid[None].contiguous(), y_grid[None].contiguous())
+            self._grids[key] = (x_grid[None], y_grid[None])  # stride-0 views: known separable
         return self._grids[key]
 
     def forward(self, size):

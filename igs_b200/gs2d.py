@@ -24,6 +24,7 @@ reference); ``set_grad_mode("exact")`` switches to the true derivative
 from __future__ import annotations
 
 import contextlib
+import functools
 
 import torch
 import torch.nn as nn
@@ -258,17 +259,16 @@ class GaussianSplatting2D(nn.Module):
     @staticmethod
     def xy_grid(size=None, device=None):
         """Pixel-centre coordinates (reference :503-522): endpoints inclusive, the longer
-        side spans more than [-1,1] so that x_range * y_range = 1.  Returns two
-        expanded [1,H,W] views."""
+        side spans more than [-1,1] so that x_range * y_range = 1.  Returns two [1,H,W]
+        tensors that are expanded (stride-0) views of one row / one column ON the target
+        device: same values as the reference's, no H*W copy, and the splat kernels can see
+        from the strides alone that the grid is separable."""
         h, w = size
         aspect = h / w
         h_range = aspect ** 0.5
         w_range = 1 / aspect ** 0.5
-        xs = torch.linspace(-w_range, w_range, w)
-        ys = torch.linspace(-h_range, h_range, h)
-        x_grid = xs.view(1, 1, w).expand(1, h, w).to(device)
-        y_grid = ys.view(1, h, 1).expand(1, h, w).to(device)
-        return x_grid, y_grid
+        xs, ys = _grid_axes(int(h), int(w), float(w_range), float(h_range), str(torch.device(device or "cpu")))
+        return xs.view(1, 1, w).expand(1, h, w), ys.view(1, h, 1).expand(1, h, w)
 
     @staticmethod
     def render(positions, colors, scales, rotations, alphas, x_grid, y_grid, eps=1e-6, fused=True):
@@ -311,6 +311,16 @@ class GaussianSplatting2D(nn.Module):
         rotations = rotations[..., 0]
         output = self.render(positions, colors, scales, rotations, alphas, x_grid, y_grid, eps, fused)
         return output, gs_feature
+
+
+@functools.lru_cache(maxsize=64)
+def _grid_axes(h, w, w_range, h_range, device):
+    """The W column and H row coordinates on ``device``; computed on the host like the
+    reference does (same bits) and kept, so that repeated calls -- in particular calls
+    inside a CUDA-graph capture -- copy nothing."""
+    xs = torch.linspace(-w_range, w_range, w).to(device)
+    ys = torch.linspace(-h_range, h_range, h).to(device)
+    return xs, ys
 
 
 def _cov_inv_torch(scales, rotations, eps):

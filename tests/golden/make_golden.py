@@ -160,6 +160,17 @@ def module_case(ref, name, seed, n_per, emb, feats, H, W, out_dim=3, B=1):
          n_per=np.int64(n_per), emb=np.int64(emb), H=np.int64(H), W=np.int64(W))
 
 
+def koleo_case(name, seed):
+    """The diversity regulariser used beside the module (src/igs/reg.py:5-40)."""
+    import igs.reg as ref_reg
+
+    gen = torch.Generator().manual_seed(seed)
+    f = torch.randn(3, 17, 8, generator=gen, requires_grad=True)
+    loss = ref_reg.koleo_diversity_loss(f)
+    loss.backward()
+    save(name, features=f, loss=loss.detach(), g_features=f.grad)
+
+
 def main():
     ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     torch.set_num_threads(os.cpu_count() or 1)
@@ -174,6 +185,7 @@ def main():
     render_case(ref, "render_tall", 18, 1, 130, 48, 12, 3, 0.1, 0.4)
     kernel_case(ref, "kernel_xy_c3", 21, 2, 45, 12, 20, 3)
     module_case(ref, "module_small", 31, 4, 64, 16, 32, 32)
+    koleo_case("koleo", 5)
     # BASELINE config 0 at full size (B=1, N=2048, 256x256, C=3), seed 0
     render_case(ref, "cfg0_full", 0, 1, 2048, 256, 256, 3, 0.25, 0.75, slim=True)
 
