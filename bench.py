@@ -334,6 +334,13 @@ def run_b200(args):
         step_e2e()
     e2e_times = timed(step_e2e, steps)
 
+    # the kernels' bounded waits report through a status word: one more forward, read it
+    probe_fwd = _lib.forward("sr", on_dev["positions"], on_dev["scales"], on_dev["rotations"], None, on_dev["alphas"],
+                             on_dev["colors"], on_dev["x"][:, 0], on_dev["y"][:, 0], 1e-6, keep_workspace=True)
+    if _lib.read_status(probe_fwd[2]) != 0:
+        raise SystemExit("igs_b200: a kernel reported a timed-out wait (status word non-zero)")
+    del probe_fwd
+
     total_ms = torch.tensor([sum(times), sum(e2e_times)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
