@@ -365,6 +365,7 @@ def run_b200(args):
         # canonical count for arbitrary sample points (fwd 9+C, bwd 18+2C).  `frac` follows
         # the canonical count, so it can exceed 1; `executed_frac` is the pipe's utilisation.
         separable = (os.environ.get("IGS_B200_NO_SEPARABLE") != "1" and C <= 4 and cfg.H >= 4 and cfg.W >= 16)
+        # (with more than 4 channels only the forward has a separable instantiation: counted as general)
         if separable:
             executed = {"forward": 5 + C, "backward": 8 + 2 * C}
         else:

@@ -172,7 +172,9 @@ def koleo_case(name, seed):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference   (the reference's source tree)")
+    ref = load_reference(sys.argv[1])
     torch.set_num_threads(os.cpu_count() or 1)
     per_gaussian_cross_check(ref)
     render_case(ref, "render_small_c3", 11, 2, 70, 20, 28, 3, 0.25, 0.75)
