@@ -105,8 +105,14 @@ struct BwdSepCfg {
     static constexpr int THREADS = 128;
     static constexpr int GPT = 2;  // gaussians per thread
     static constexpr int GAUSS_PER_CTA = THREADS * GPT;
-    static constexpr int CHUNK_BLOCKS = 64;  // 2x4-pixel blocks per shared-memory stage
-    static constexpr int STAGES = 2;
+#ifndef IGS_BWDSEP_CHUNK
+#define IGS_BWDSEP_CHUNK 64
+#endif
+#ifndef IGS_BWDSEP_STAGES
+#define IGS_BWDSEP_STAGES 2
+#endif
+    static constexpr int CHUNK_BLOCKS = IGS_BWDSEP_CHUNK;  // 2x4-pixel blocks per shared-memory stage
+    static constexpr int STAGES = IGS_BWDSEP_STAGES;
 #ifdef IGS_BWDSEP_MINCTAS
     static constexpr int MIN_CTAS = IGS_BWDSEP_MINCTAS;
 #else

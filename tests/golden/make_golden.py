@@ -160,6 +160,32 @@ def module_case(ref, name, seed, n_per, emb, feats, H, W, out_dim=3, B=1):
          n_per=np.int64(n_per), emb=np.int64(emb), H=np.int64(H), W=np.int64(W))
 
 
+def module_variants_case(ref, name, seed):
+    """The module's two optional inputs: a caller-supplied (here warped) sampling grid
+    [B,2,H,W] with the row coordinate first (src/igs/gs2d.py:650-653), and
+    pos_map_offset=True with a scale factor (:654-667), where every feature's gaussians
+    are offset by the grid position of that feature."""
+    torch.manual_seed(seed)
+    B, n_per, emb, H, W, scale = 2, 4, 32, 32, 32, 8
+    feats = (H // scale) * (W // scale)
+    tgt = torch.rand(B, 3, H, W)
+    xg, yg = ref.GaussianSplatting2D.xy_grid((H, W), "cpu")
+    warp = 0.05 * torch.sin(3 * xg) * torch.cos(2 * yg)
+    grid = torch.stack([(yg + warp).expand(B, H, W), (xg - warp).expand(B, H, W)], dim=1).contiguous()
+    out = {}
+    for tag, kwargs, pmo in (("grid", dict(grid=grid), False), ("posmap", dict(size=(H, W), scale=scale), True)):
+        m = ref.GaussianSplatting2D(n_per, emb, 3, pos_map_offset=pmo)
+        feat = torch.randn(B, feats, emb).requires_grad_()
+        img, gs_feature = m(feat, **kwargs)
+        loss = torch.nn.functional.mse_loss(img, tgt)
+        loss.backward()
+        out.update({f"{tag}_weight": m.proj.weight, f"{tag}_bias": m.proj.bias, f"{tag}_feature": feat,
+                    f"{tag}_out": img, f"{tag}_g_weight": m.proj.weight.grad, f"{tag}_g_bias": m.proj.bias.grad,
+                    f"{tag}_g_feature": feat.grad})
+    save(name, target=tgt, grid=grid, n_per=np.int64(n_per), emb=np.int64(emb), H=np.int64(H), W=np.int64(W),
+         scale=np.int64(scale), **out)
+
+
 def koleo_case(name, seed):
     """The diversity regulariser used beside the module (src/igs/reg.py:5-40)."""
     import igs.reg as ref_reg
@@ -187,6 +213,7 @@ def main():
     render_case(ref, "render_tall", 18, 1, 130, 48, 12, 3, 0.1, 0.4)
     kernel_case(ref, "kernel_xy_c3", 21, 2, 45, 12, 20, 3)
     module_case(ref, "module_small", 31, 4, 64, 16, 32, 32)
+    module_variants_case(ref, "module_variants", 32)
     koleo_case("koleo", 5)
     # BASELINE config 0 at full size (B=1, N=2048, 256x256, C=3), seed 0
     render_case(ref, "cfg0_full", 0, 1, 2048, 256, 256, 3, 0.25, 0.75, slim=True)

@@ -163,3 +163,28 @@ def test_cfg1_module_at_init(dev):
              # d/d log_scale = d/d scale * exp(log_scale); undo it to compare scale gradients
              "scales": g[..., 2:4] / (sc - 1e-6)}
     subset_check(d, out.detach(), out.grad.detach(), grads, n_pix=256, n_gauss=32, seed=1)
+
+
+@pytest.mark.parametrize("tag", ["grid", "posmap"])
+def test_module_optional_inputs_match_reference_fixture(tag, dev):
+    """The module with a caller-supplied warped sampling grid (general kernels) and with
+    pos_map_offset=True plus a scale factor, against outputs of the reference module."""
+    from igs_b200 import GaussianSplatting2D
+    from tests._util import assert_close, load_golden
+
+    g = load_golden("module_variants")
+    t = lambda k: torch.from_numpy(g[k]).to(dev)
+    m = GaussianSplatting2D(int(g["n_per"]), int(g["emb"]), 3, pos_map_offset=(tag == "posmap")).to(dev)
+    with torch.no_grad():
+        m.proj.weight.copy_(t(f"{tag}_weight"))
+        m.proj.bias.copy_(t(f"{tag}_bias"))
+    feat = t(f"{tag}_feature").requires_grad_()
+    if tag == "grid":
+        out, _ = m(feat, grid=t("grid"))
+    else:
+        out, _ = m(feat, size=(int(g["H"]), int(g["W"])), scale=int(g["scale"]))
+    torch.nn.functional.mse_loss(out, t("target")).backward()
+    assert_close(_np(out), g[f"{tag}_out"], TOL, f"{tag} image")
+    assert_close(_np(m.proj.weight.grad), g[f"{tag}_g_weight"], TOL, f"{tag} d_weight")
+    assert_close(_np(m.proj.bias.grad), g[f"{tag}_g_bias"], TOL, f"{tag} d_bias")
+    assert_close(_np(feat.grad), g[f"{tag}_g_feature"], TOL, f"{tag} d_feature")
