@@ -41,6 +41,7 @@ SIGNATURES = {
     "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 8 + [_sz, _i, _vp]),
     "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
     "igs_read_status": (_i, [_vp, _i, _vp, ctypes.POINTER(_i)]),
+    "igs_set_culling": (_i, [_i]),
     "igs_profile_enable": (_i, [_i]),
     "igs_profile_reset": (_i, []),
     "igs_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
@@ -78,7 +79,11 @@ def load() -> ctypes.CDLL:
                     "Run `python -m igs_b200.build`; there is no CPU or PyTorch fallback.") from exc
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
-            fn = getattr(lib, name)  # AttributeError here = header and library out of sync
+            fn = getattr(lib, name, None)
+            if fn is None:
+                if os.environ.get("IGS_B200_LIB"):
+                    continue  # an older development build without this entry point
+                raise AttributeError(f"{LIB_PATH} does not export {name}: header and library out of sync")
             fn.restype = res
             fn.argtypes = args
         _lib = lib
@@ -216,6 +221,11 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
 
 
 KERNEL_NAMES = ("pack", "forward", "reduce_normalize", "pixel_terms", "backward", "finalize", "coord_grad", "grid_check")
+
+
+def set_culling(on: bool) -> None:
+    """Process-wide switch of the lossless (gaussian, pixel tile) culling; default on."""
+    check("igs_set_culling", load().igs_set_culling(int(bool(on))))
 
 
 def profile_enable(on: bool) -> None:

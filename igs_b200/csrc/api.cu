@@ -230,6 +230,37 @@ static Strides get_strides(const int64_t* s, int H, int W) {
     return {(long long)s[0], (long long)s[1], (long long)s[2]};
 }
 
+// ---- lossless culling switch (igs_set_culling) ----
+static std::atomic<int> g_culling{1};
+
+// Classifies the sample grid (GridKind) and initialises the status area's grid word:
+// launches the separability check when the strides do not settle the question.
+static cudaError_t prepare_grid(unsigned char* ws, const float* x, const float* y, const Strides& sx, const Strides& sy,
+                                int B, int H, int W, bool separable_available, GridKind* kind, cudaStream_t st) {
+    int* flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    *kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && separable_available);
+    if (*kind != GRID_CHECK_ON_DEVICE) return cudaMemsetAsync(flag, 0, sizeof(int), st);
+    GridCheckArgs ga;
+    ga.x = x; ga.y = y;
+    ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;
+    ga.ys_b = sy.b; ga.ys_h = sy.h; ga.ys_w = sy.w;
+    ga.flag = flag;
+    ga.B = B; ga.H = H; ga.W = W;
+    return launch_grid_check(ga, st);
+}
+
+// The part of the prologue's arguments that describes the sample grid (for the reach
+// statistics and the axis-monotonicity bit the culling code relies on).
+static void pack_grid_args(PackArgs* pa, unsigned char* ws, const float* x, const float* y, const Strides& sx,
+                           const Strides& sy, int B, int N, int H, int W) {
+    pa->x = x; pa->y = y;
+    pa->xs_b = sx.b; pa->xs_w = sx.w;
+    pa->ys_b = sy.b; pa->ys_h = sy.h;
+    pa->narrow_count = reinterpret_cast<int*>(ws) + NARROW_COUNT_WORD;
+    pa->grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    pa->B = B; pa->N = N; pa->H = H; pa->W = W;
+}
+
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
@@ -270,6 +301,13 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
 
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    // separable grid (x by column, y by row)?  known from the strides, or checked on the device
+    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    GridKind grid_kind;
+    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.tiles_sep > 0, &grid_kind, st);
+    if (e != cudaSuccess) return (int)e;
+
     PackArgs pa;
     std::memset(&pa, 0, sizeof(pa));
     pa.pos = pos;
@@ -279,6 +317,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     pa.alpha = alpha;
     pa.colors = colors;
     pa.geo = nullptr;
+    pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
     for (int k = 0; k < p.ch.n; ++k) pa.frec[k] = reinterpret_cast<float*>(ws + p.off_frec[k]);
     pa.ch = p.ch;
     pa.M = (long long)B * N;
@@ -289,20 +328,6 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     if (e != cudaSuccess) return (int)e;
 
     const bool in_kernel = normalize && p.n_split == 1;
-    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
-    // separable grid (x by column, y by row)?  known from the strides, or checked on the device
-    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
-    const GridKind grid_kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && p.tiles_sep > 0);
-    if (grid_kind == GRID_CHECK_ON_DEVICE) {
-        GridCheckArgs ga;
-        ga.x = x; ga.y = y;
-        ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;
-        ga.ys_b = sy.b; ga.ys_h = sy.h; ga.ys_w = sy.w;
-        ga.flag = grid_flag;
-        ga.B = B; ga.H = H; ga.W = W;
-        e = launch_grid_check(ga, st);
-        if (e != cudaSuccess) return (int)e;
-    }
     for (int k = 0; k < p.ch.n; ++k) {
         FwdArgs fa;
         std::memset(&fa, 0, sizeof(fa));
@@ -325,15 +350,23 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         fa.eps = eps;
         fa.tiles_x = p.tiles_x;
         const GridKind gk = forward_has_separable(p.ch.ct[k]) ? grid_kind : GRID_GENERAL;
-        fa.grid_flag = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
+        fa.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
         if (gk != GRID_GENERAL) {
-            e = launch_forward_chunk(p.ch.ct[k], true, fa, p, st);
+            // the separable kernel comes as a plain and a culling instantiation; both are
+            // launched and the count of narrow gaussians picks one (the other returns at once)
+            fa.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
+            e = launch_forward_chunk(p.ch.ct[k], true, false, fa, p, st);
             if (e != cudaSuccess) return (int)e;
+            if (fa.cull_sel) {
+                e = launch_forward_chunk(p.ch.ct[k], true, true, fa, p, st);
+                if (e != cudaSuccess) return (int)e;
+            }
         }
         if (gk != GRID_SEPARABLE) {
             // a chunk without a separable instantiation runs whatever the flag says
-            if (gk == GRID_GENERAL) fa.grid_flag = nullptr;
-            e = launch_forward_chunk(p.ch.ct[k], false, fa, p, st);
+            if (gk == GRID_GENERAL) fa.grid_sel = nullptr;
+            fa.cull_sel = nullptr;
+            e = launch_forward_chunk(p.ch.ct[k], false, false, fa, p, st);
             if (e != cudaSuccess) return (int)e;
         }
     }
@@ -400,6 +433,13 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     e = cudaMemsetAsync(ws, 0, sizeof(int), st);
     if (e != cudaSuccess) return (int)e;
 
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    // separable grid?  (same decision procedure as the forward)
+    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+    GridKind grid_kind;
+    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.sep_ok != 0, &grid_kind, st);
+    if (e != cudaSuccess) return (int)e;
+
     PackArgs pa;
     std::memset(&pa, 0, sizeof(pa));
     pa.pos = pos;
@@ -409,6 +449,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     pa.alpha = alpha;
     pa.colors = colors;
     pa.geo = reinterpret_cast<float*>(ws + p.off_geo);
+    pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
     pa.ch = p.ch;
     pa.M = (long long)B * N;
     pa.C = C;
@@ -417,7 +458,6 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     e = launch_pack(pa, st);
     if (e != cudaSuccess) return (int)e;
 
-    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
     PixelTermArgs ta;
     std::memset(&ta, 0, sizeof(ta));
     ta.x = x;
@@ -432,20 +472,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     ta.npairs = p.npairs;
     ta.nrp = p.nrp;
     ta.ncb = p.ncb;
-    // separable grid?  (same decision procedure as the forward)
-    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
-    const GridKind grid_kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && p.sep_ok);
-    if (grid_kind == GRID_CHECK_ON_DEVICE) {
-        GridCheckArgs ga;
-        ga.x = x; ga.y = y;
-        ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;
-        ga.ys_b = sy.b; ga.ys_h = sy.h; ga.ys_w = sy.w;
-        ga.flag = grid_flag;
-        ga.B = B; ga.H = H; ga.W = W;
-        e = launch_grid_check(ga, st);
-        if (e != cudaSuccess) return (int)e;
-    }
-    ta.grid_flag = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
+    ta.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
     ta.B = B; ta.H = H; ta.W = W; ta.C = C;
     ta.mode = mode;
     ta.eps = eps;
@@ -470,7 +497,9 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.nrp = p.nrp;
         ba.ncb = p.ncb;
         ba.rp_per_slab = p.rp_per_slab;
-        ba.grid_flag = ta.grid_flag;
+        ba.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
+        ba.grid_word = grid_flag;
+        ba.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
         ba.pairs_per_slab = p.pairs_per_slab;
         ba.B = B; ba.N = N; ba.C = C;
         ba.c0 = p.ch.c0[k];
@@ -479,11 +508,15 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.moment_plane0 = N_MOMENTS * k;
         ba.color_plane0 = N_MOMENTS * p.ch.n;
         if (grid_kind != GRID_GENERAL) {
-            e = launch_backward_chunk(p.ch.ct[k], true, ba, p, st);
+            e = launch_backward_chunk(p.ch.ct[k], true, false, ba, p, st);
             if (e != cudaSuccess) return (int)e;
+            if (ba.cull_sel) {
+                e = launch_backward_chunk(p.ch.ct[k], true, true, ba, p, st);
+                if (e != cudaSuccess) return (int)e;
+            }
         }
         if (grid_kind != GRID_SEPARABLE) {
-            e = launch_backward_chunk(p.ch.ct[k], false, ba, p, st);
+            e = launch_backward_chunk(p.ch.ct[k], false, false, ba, p, st);
             if (e != cudaSuccess) return (int)e;
         }
     }
@@ -657,6 +690,11 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_cov_inv_00,
                          d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, workspace, workspace_bytes, device,
                          stream);
+}
+
+int igs_set_culling(int on) {
+    g_culling.store(on ? 1 : 0, std::memory_order_relaxed);
+    return IGS_OK;
 }
 
 int igs_profile_enable(int on) {

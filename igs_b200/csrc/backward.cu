@@ -27,7 +27,7 @@ namespace igs {
 // per-pixel upstream terms
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) pixel_terms_kernel(PixelTermArgs a) {
-    if (a.grid_flag && *a.grid_flag == 0) return;  // separable grid: the block-record kernel runs
+    if (a.grid_sel && !(*a.grid_sel & GRID_NOT_SEPARABLE)) return;  // separable grid: the block-record kernel runs
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*npairs
     if (i >= (long long)a.B * a.npairs) return;
     const long long b = i / a.npairs, pair = i - b * a.npairs;
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN
     using Cfg = BwdCfg<CT, GPT>;
     constexpr int T = Cfg::THREADS, PC = Cfg::CHUNK_PAIRS, NS = Cfg::STAGES, RS = Cfg::RS, NACC = Cfg::NACC;
 
-    if (a.grid_flag && *a.grid_flag == 0) return;  // separable grid: splat_backward_sep_kernel runs
+    if (a.grid_sel && !(*a.grid_sel & GRID_NOT_SEPARABLE)) return;  // separable grid: splat_backward_sep_kernel runs
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* stage_base = reinterpret_cast<float*>(smem_raw);
@@ -302,8 +302,9 @@ static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s
     return cudaGetLastError();
 }
 
-cudaError_t launch_backward_chunk(int ct, bool separable, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
-    if (separable) return launch_backward_sep_chunk(ct, a, p, s);
+cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const BwdArgs& a, const BwdPlan& p,
+                                  cudaStream_t s) {
+    if (separable) return launch_backward_sep_chunk(ct, culling, a, p, s);
     const bool two = p.gauss_per_thread >= 2;
     switch (ct) {
         case 1: return two ? launch_one<1, IGS_BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);

@@ -15,7 +15,7 @@ struct PixelTermArgs {
     const float* out;   // [B, C, HW]  (exact mode only)
     const float* gout;  // [B, C, HW]
     float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]  or, separable, [B, nrp*ncb, bwd_sep_rec_floats(ct)]
-    const int* grid_flag;     // 0 = separable; nullptr = run unconditionally
+    const int* grid_sel;      // grid word (bit 0 = not a separable grid) picking the kernel; nullptr = run
     Chunks ch;
     long long npairs;
     int nrp, ncb;             // separable: row pairs and 4-column blocks per row pair
@@ -30,7 +30,11 @@ struct BwdArgs {
     const float* prec;    // records of this chunk
     float* part;          // [n_slab, B, planes, N]
     int* status;
-    const int* grid_flag;  // 0 = separable; nullptr = run unconditionally
+    // Selection on the device (nullptr = run unconditionally): a kernel returns at once
+    // unless the word picks it.
+    const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable kernel
+    const int* cull_sel;   // count of narrow gaussians: at least one in eight (and monotone axes,
+    const int* grid_word;  //   bit 1 of the grid word clear) -> skipping / plain separable kernel
     long long npairs, pairs_per_slab;
     int nrp, ncb, rp_per_slab;  // separable: row pairs, blocks per row pair, row pairs per slab
     int B, N, C;
@@ -76,10 +80,11 @@ struct CoordGradArgs {
 };
 
 cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStream_t s);
-cudaError_t launch_backward_chunk(int ct, bool separable, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const BwdArgs& a, const BwdPlan& p,
+                                  cudaStream_t s);
 bool backward_has_separable(int ct);
 cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
-cudaError_t launch_backward_sep_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
 cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
 

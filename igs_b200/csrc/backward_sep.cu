@@ -21,7 +21,7 @@ namespace igs {
 // per-pixel upstream terms, block records
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
-    if (a.grid_flag && *a.grid_flag != 0) return;
+    if (a.grid_sel && (*a.grid_sel & GRID_NOT_SEPARABLE)) return;
     const long long per_b = (long long)a.nrp * a.ncb;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*nrp*ncb
     if (i >= (long long)a.B * per_b) return;
@@ -125,15 +125,21 @@ struct BwdSepCfg {
 #endif
     static constexpr int RS = bwd_sep_rec_floats(CT);
     static constexpr int PF = bwd_sep_pair_floats(CT);
+    static constexpr int SKIP_RUN = 8;  // blocks (32 columns) per skip decision
     static constexpr size_t SMEM = (size_t)STAGES * CHUNK_BLOCKS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
 };
 
-template <int CT>
+template <int CT, bool CULL>
 __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTAS) splat_backward_sep_kernel(BwdArgs a) {
     using Cfg = BwdSepCfg<CT>;
     constexpr int T = Cfg::THREADS, GPT = Cfg::GPT, PCB = Cfg::CHUNK_BLOCKS, NS = Cfg::STAGES, RS = Cfg::RS, PF = Cfg::PF;
+    constexpr int SKIP_RUN = Cfg::SKIP_RUN;
 
-    if (a.grid_flag && *a.grid_flag != 0) return;  // not a separable grid: the general kernel runs
+    if (a.grid_sel && (*a.grid_sel & GRID_NOT_SEPARABLE)) return;  // not a separable grid: the general kernel runs
+    // of the skipping / plain pair, the one the gaussians' reach and the axes call for
+    if (a.cull_sel && ((!(*a.grid_word & GRID_NOT_MONOTONE) &&
+                        (long long)(*a.cull_sel) * 8 >= (long long)a.B * a.N) != CULL))
+        return;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* stage_base = reinterpret_cast<float*>(smem_raw);
@@ -146,6 +152,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
     // ---- this thread's gaussians ----
     int n[GPT];
     f2 px[GPT], py[GPT], A[GPT], B2[GPT], Cq[GPT], col[GPT][CT];
+    float box_x0[GPT], box_x1[GPT], box_y0[GPT], box_y1[GPT];
 #pragma unroll
     for (int g = 0; g < GPT; ++g) {
         n[g] = blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
@@ -157,12 +164,24 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         A[g] = pk(g0.z, g0.z);
         B2[g] = pk(g0.w, g0.w);
         Cq[g] = pk(g1.x, g1.x);
+        // the box outside which this gaussian's weight is exactly zero (pack.cu)
+        box_x0[g] = g0.x - g1.z;
+        box_x1[g] = g0.x + g1.z;
+        box_y0[g] = g0.y - g1.w;
+        box_y1[g] = g0.y + g1.w;
 #pragma unroll
         for (int c = 0; c < CT; ++c) {
             const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
             col[g][c] = pk(v, v);
         }
     }
+    // Skipping: a run of up to SKIP_RUN blocks of a row pair is passed over when no lane
+    // of the warp owns a gaussian whose box meets the run's pixels (every term would be an
+    // exact zero).  Needs non-decreasing axes (the run's x range is taken from its two ends)
+    // and is only tried when enough gaussians are narrow for it to pay.
+    constexpr bool cull = CULL;
+    float strip_y0 = 0.f, strip_y1 = 0.f;
+    int must = 0;  // blocks of the current run still to be processed without voting again
 
     // totals: M0, Mx, My, Mxx, Mxy, Myy, E_c;  row-pair state: per row r of the pair
     f2 M[GPT][N_MOMENTS], E[GPT][CT];
@@ -220,8 +239,21 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         const int cnt = min(PCB, n_total - chunk * PCB);
         const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * PCB * RS);
 
+        auto fold_row_pair = [&]() {
+            // row pair complete: fold its row sums into the moments
+#pragma unroll
+            for (int g = 0; g < GPT; ++g)
+#pragma unroll
+                for (int row = 0; row < 2; ++row) {
+                    M[g][0] = add2(M[g][0], hs[g][row]);
+                    M[g][1] = add2(M[g][1], hxs[g][row]);
+                    M[g][2] = fma2(dyd[g][row], hs[g][row], M[g][2]);
+                    M[g][4] = fma2(dyd[g][row], hxs[g][row], M[g][4]);
+                    M[g][5] = fma2(mul2(dyd[g][row], dyd[g][row]), hs[g][row], M[g][5]);
+                }
+        };
 #pragma unroll(Cfg::UNROLL)
-        for (int i = 0; i < cnt; ++i) {
+        for (int i = 0; i < cnt;) {
             const float4* r = rec + (size_t)i * (RS / 4);
             const float4 xc = r[0];
             const f2 xcp[2] = {pk(xc.x, xc.y), pk(xc.z, xc.w)};
@@ -229,6 +261,8 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 // new row pair: row terms of the exponent, fresh row sums
                 const float4 yr = r[1];
                 const f2 yy = pk(yr.x, yr.y);
+                strip_y0 = fminf(yr.x, yr.y);
+                strip_y1 = fmaxf(yr.x, yr.y);
 #pragma unroll
                 for (int g = 0; g < GPT; ++g) {
                     const f2 dyr = sub2(yy, py[g]);
@@ -242,6 +276,25 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                     hs[g][0] = hs[g][1] = hxs[g][0] = hxs[g][1] = 0ull;
                 }
             }
+            if (cull && must == 0) {
+                const int run = min(min(SKIP_RUN, cnt - i), a.ncb - cb);
+                const float run_x0 = xc.x, run_x1 = rec[(size_t)(i + run - 1) * (RS / 4)].w;
+                bool need = false;
+#pragma unroll
+                for (int g = 0; g < GPT; ++g)
+                    need |= !(box_x1[g] < run_x0 || box_x0[g] > run_x1 || box_y1[g] < strip_y0 || box_y0[g] > strip_y1);
+                if (!__any_sync(0xffffffffu, need)) {
+                    i += run;
+                    cb += run;
+                    if (cb == a.ncb) {
+                        cb = 0;
+                        fold_row_pair();
+                    }
+                    continue;
+                }
+                must = run;
+            }
+            if (cull) --must;
             f2 dxc[GPT][2], adx[GPT][2];
 #pragma unroll
             for (int g = 0; g < GPT; ++g)
@@ -277,19 +330,10 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                     for (int c = 0; c < CT; ++c) E[g][c] = fma2(gterm[1 + c], e, E[g][c]);
                 }
             }
+            ++i;
             if (++cb == a.ncb) {
-                // row pair complete: fold its row sums into the moments
                 cb = 0;
-#pragma unroll
-                for (int g = 0; g < GPT; ++g)
-#pragma unroll
-                    for (int row = 0; row < 2; ++row) {
-                        M[g][0] = add2(M[g][0], hs[g][row]);
-                        M[g][1] = add2(M[g][1], hxs[g][row]);
-                        M[g][2] = fma2(dyd[g][row], hs[g][row], M[g][2]);
-                        M[g][4] = fma2(dyd[g][row], hxs[g][row], M[g][4]);
-                        M[g][5] = fma2(mul2(dyd[g][row], dyd[g][row]), hs[g][row], M[g][5]);
-                    }
+                fold_row_pair();
             }
         }
         __syncthreads();
@@ -317,14 +361,14 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
     }
 }
 
-template <int CT>
+template <int CT, bool CULL>
 static cudaError_t launch_sep_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
     using Cfg = BwdSepCfg<CT>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(splat_backward_sep_kernel<CT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(splat_backward_sep_kernel<CT, CULL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
@@ -332,7 +376,7 @@ static cudaError_t launch_sep_one(const BwdArgs& a, const BwdPlan& p, cudaStream
     dim3 grid((unsigned)((a.N + Cfg::GAUSS_PER_CTA - 1) / Cfg::GAUSS_PER_CTA), (unsigned)p.n_slab, (unsigned)a.B);
     {
         KernelTimer timer(K_BACKWARD, s);
-        splat_backward_sep_kernel<CT><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_backward_sep_kernel<CT, CULL><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
@@ -341,12 +385,12 @@ static cudaError_t launch_sep_one(const BwdArgs& a, const BwdPlan& p, cudaStream
 // instantiations exist for single-chunk channel counts up to 4, two gaussians per thread
 bool backward_has_separable(int ct) { return ct <= 4 && backward_gauss_per_thread(ct) == BwdSepCfg<3>::GPT; }
 
-cudaError_t launch_backward_sep_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
+cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s) {
     switch (ct) {
-        case 1: return launch_sep_one<1>(a, p, s);
-        case 2: return launch_sep_one<2>(a, p, s);
-        case 3: return launch_sep_one<3>(a, p, s);
-        case 4: return launch_sep_one<4>(a, p, s);
+        case 1: return culling ? launch_sep_one<1, true>(a, p, s) : launch_sep_one<1, false>(a, p, s);
+        case 2: return culling ? launch_sep_one<2, true>(a, p, s) : launch_sep_one<2, false>(a, p, s);
+        case 3: return culling ? launch_sep_one<3, true>(a, p, s) : launch_sep_one<3, false>(a, p, s);
+        case 4: return culling ? launch_sep_one<4, true>(a, p, s) : launch_sep_one<4, false>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }

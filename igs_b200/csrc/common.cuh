@@ -13,7 +13,7 @@ namespace igs {
 // Record layouts
 // ---------------------------------------------------------------------------
 // Geometry record, one per gaussian, 8 floats (32 B):
-//   {px, py, A, B2, Cq, alpha, c00, c01}      and a second array holds c11
+//   {px, py, A, B2, Cq, alpha, hx, hy}
 // with the exponent coefficients pre-scaled so that the weight is
 //   e = 2^(A*dx^2 + B2*dx*dy + Cq*dy^2),  A = k*c00, B2 = 2k*c01, Cq = k*c11,
 //   k = -0.5*log2(e).
@@ -21,12 +21,23 @@ constexpr int GEO_FLOATS = 8;
 constexpr float EXP2_SCALE = -0.72134752044448170368f;  // -0.5 * log2(e)
 
 // Forward record, one per gaussian and channel chunk, padded to a multiple of 4 floats:
-//   {px, py, A, B2,  Cq, al, al*c0, al*c1,  al*c2, ...}
+//   {px, py, A, B2,  Cq, al, al*c0, al*c1,  al*c2, ..., hx, hy}
+// (hx, hy: half-widths of the box outside which the weight is exactly zero, see pack.cu).
 // Each value is stored once and duplicated into an f32x2 operand in registers (a move on
 // the otherwise idle ALU pipe): a record then costs 3 sixteen-byte broadcast reads at
 // C = 3 instead of the 5 a pre-duplicated record needs, and the shared-memory return path
 // (4 cycles per 16-byte warp read) stops co-limiting the kernel.
-__host__ __device__ constexpr int fwd_rec_floats(int ct) { return (6 + ct + 3) / 4 * 4; }
+__host__ __device__ constexpr int fwd_rec_floats(int ct) { return (8 + ct + 3) / 4 * 4; }
+
+// Exponents (log2 units) below -CULL_T are treated as "certainly flushed to zero":
+// ex2.approx.ftz returns exactly 0 below -126; the margin absorbs fp32 rounding.
+constexpr float CULL_T = 130.0f;
+
+// Words of the workspace's 256-byte status area.
+constexpr int STATUS_WORD = 0;       // kernels: a bounded wait gave up
+constexpr int GRID_FLAG_WORD = 1;    // grid check: bit 0 = not separable, bit 1 = axes not monotone
+constexpr int NARROW_COUNT_WORD = 2; // pack: gaussians whose reach is well inside the image
+constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2;
 
 // Backward pixel record, one per PAIR of consecutive pixels and channel chunk:
 //   {x0,x1, y0,y1, gS0,gS1, gn0_0,gn0_1, ...}  padded to 4 floats

@@ -51,13 +51,15 @@ struct FwdCfg {
     static constexpr int UNROLL = CT <= 3 ? 4 : 2;
 #endif
     static constexpr int RS = fwd_rec_floats(CT);
-    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
+    // stages | mbarriers | flags (16 B) | surviving-gaussian list of the current stage | per-warp scratch
+    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16 +
+                                   CHUNK_G * sizeof(unsigned short) + 8 * 4 * sizeof(float);
 };
 
 // Separable tiles: 16 rows x 64 columns per CTA, 2 rows x 4 columns per thread.
 constexpr int SEP_TILE_H = 16, SEP_TILE_W = 64;
 
-template <int CT, int PX_, bool SEP>
+template <int CT, int PX_, bool SEP, bool CULL>
 __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN_CTAS)
     splat_forward_kernel(FwdArgs a) {
     using Cfg = FwdCfg<CT, PX_>;
@@ -65,12 +67,17 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
     static_assert(!SEP || PX_ == 8, "the separable patch is 2 rows x 4 columns");
 
     // only the instantiation that matches the grid's kind does the work
-    if (a.grid_flag && ((*a.grid_flag != 0) == SEP)) return;
+    if (a.grid_sel && (((*a.grid_sel & GRID_NOT_SEPARABLE) != 0) == SEP)) return;
+    // ... and, of the culling / non-culling pair, the one the gaussians' reach calls for:
+    // culling pays when at least one gaussian in eight is narrow (counted by pack_kernel)
+    if (a.cull_sel && (((long long)(*a.cull_sel) * 8 >= (long long)a.B * a.N) != CULL)) return;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* stage_base = reinterpret_cast<float*>(smem_raw);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NS * G * RS * sizeof(float));
     int* s_failed = reinterpret_cast<int*>(bars + NS);
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(s_failed + 4);
+    float* s_warp = reinterpret_cast<float*>(s_list + G);  // [4 warps][4] bounding box partials, then counts
 
     const int tid = threadIdx.x;
     const int b = blockIdx.z, split = blockIdx.y;
@@ -123,6 +130,52 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
         for (int c = 0; c < CT; ++c) acc[j][c] = 0ull;
     }
 
+    // ---- culling: is it worth it, and what is this CTA's bounding box of sample points? ----
+    // (gaussians whose zero-weight box misses the CTA's box contribute exactly 0 to every
+    // pixel here and are skipped; decided per launch from the count of narrow gaussians)
+    bool cull = CULL;
+    float bx0 = 0.f, bx1 = 0.f, by0 = 0.f, by1 = 0.f;
+    if constexpr (CULL) {
+        float lo_x = INFINITY, hi_x = -INFINITY, lo_y = INFINITY, hi_y = -INFINITY;
+        bool bad = false;
+        constexpr int NX = SEP ? 2 : NP, NY = SEP ? 1 : NP;
+#pragma unroll
+        for (int j = 0; j < NX; ++j) {
+            float v0, v1;
+            upk(xx[j], v0, v1);
+            lo_x = fminf(lo_x, fminf(v0, v1));
+            hi_x = fmaxf(hi_x, fmaxf(v0, v1));
+            bad |= !(v0 == v0) || !(v1 == v1);
+        }
+#pragma unroll
+        for (int j = 0; j < NY; ++j) {
+            float v0, v1;
+            upk(yy[j], v0, v1);
+            lo_y = fminf(lo_y, fminf(v0, v1));
+            hi_y = fmaxf(hi_y, fmaxf(v0, v1));
+            bad |= !(v0 == v0) || !(v1 == v1);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            lo_x = fminf(lo_x, __shfl_xor_sync(0xffffffffu, lo_x, o));
+            hi_x = fmaxf(hi_x, __shfl_xor_sync(0xffffffffu, hi_x, o));
+            lo_y = fminf(lo_y, __shfl_xor_sync(0xffffffffu, lo_y, o));
+            hi_y = fmaxf(hi_y, __shfl_xor_sync(0xffffffffu, hi_y, o));
+        }
+        if ((tid & 31) == 0) {
+            float* w = s_warp + (tid >> 5) * 4;
+            w[0] = lo_x; w[1] = hi_x; w[2] = lo_y; w[3] = hi_y;
+        }
+        // a NaN coordinate anywhere in the tile: no culling here (its pixel must see every gaussian)
+        bad = __syncthreads_or(bad);
+        bx0 = fminf(fminf(s_warp[0], s_warp[4]), fminf(s_warp[8], s_warp[12]));
+        bx1 = fmaxf(fmaxf(s_warp[1], s_warp[5]), fmaxf(s_warp[9], s_warp[13]));
+        by0 = fminf(fminf(s_warp[2], s_warp[6]), fminf(s_warp[10], s_warp[14]));
+        by1 = fmaxf(fmaxf(s_warp[3], s_warp[7]), fmaxf(s_warp[11], s_warp[15]));
+        __syncthreads();  // s_warp is reused for the per-stage counts
+        cull = !bad;
+    }
+
     // ---- gaussian range of this split, streamed in stages ----
     const int n_begin = split * a.per_split;
     const int n_end = min(a.N, n_begin + a.per_split);
@@ -165,8 +218,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
         }
         const int cnt = min(G, n_total - chunk * G);
         const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * G * RS);
-#pragma unroll(Cfg::UNROLL)
-        for (int g = 0; g < cnt; ++g) {
+        auto splat = [&](int g) {
             const float4* rf = rec + (size_t)g * (RS / 4);
             float vals[RS];
 #pragma unroll
@@ -209,6 +261,32 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
                     for (int c = 0; c < CT; ++c) acc[j][c] = fma2(e, col[c], acc[j][c]);
                 }
             }
+        };
+        if (!CULL || !cull) {
+#pragma unroll(Cfg::UNROLL)
+            for (int g = 0; g < cnt; ++g) splat(g);
+        } else {
+            // ordered list of the stage's gaussians whose box meets this CTA's box
+            bool keep = false;
+            if (tid < cnt) {
+                const float* rt = reinterpret_cast<const float*>(rec) + (size_t)tid * RS;
+                const float gx = rt[0], gy = rt[1], hx = rt[6 + CT], hy = rt[7 + CT];  // centre and reach
+                keep = !(gx + hx < bx0 || gx - hx > bx1 || gy + hy < by0 || gy - hy > by1);
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, keep);
+            int* s_count = reinterpret_cast<int*>(s_warp);
+            if ((tid & 31) == 0) s_count[tid >> 5] = __popc(ballot);
+            __syncthreads();
+            int base = 0, n_keep = 0;
+#pragma unroll
+            for (int w = 0; w < T / 32; ++w) {
+                if (w < (tid >> 5)) base += s_count[w];
+                n_keep += s_count[w];
+            }
+            if (keep) s_list[base + __popc(ballot & ((1u << (tid & 31)) - 1u))] = (unsigned short)tid;
+            __syncthreads();
+#pragma unroll(Cfg::UNROLL)
+            for (int i = 0; i < n_keep; ++i) splat(s_list[i]);
         }
         __syncthreads();  // every lane is done with this stage
         if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
@@ -277,14 +355,14 @@ __global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
     }
 }
 
-template <int CT, int PX_, bool SEP>
+template <int CT, int PX_, bool SEP, bool CULL>
 static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
     using Cfg = FwdCfg<CT, PX_>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, SEP>,
+        cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, SEP, CULL>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
@@ -292,7 +370,7 @@ static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s
     dim3 grid((unsigned)(SEP ? p.tiles_sep : p.tiles), (unsigned)p.n_split, (unsigned)a.B);
     {
         KernelTimer timer(K_FORWARD, s);
-        splat_forward_kernel<CT, PX_, SEP><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_forward_kernel<CT, PX_, SEP, CULL><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
@@ -306,27 +384,41 @@ int forward_px_per_thread(int ct) { return ct > 4 ? IGS_FWD_WIDE_PX : 8; }
 // separable instantiations exist where the general one uses 8 pixels per thread
 bool forward_has_separable(int ct) { return ct <= 4 || IGS_FWD_WIDE_PX == 8; }
 
-cudaError_t launch_forward_chunk(int ct, bool separable, const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
+cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const FwdArgs& a, const FwdPlan& p,
+                                 cudaStream_t s) {
+    if (separable && culling) {
+        switch (ct) {
+            case 1: return launch_one<1, 8, true, true>(a, p, s);
+            case 2: return launch_one<2, 8, true, true>(a, p, s);
+            case 3: return launch_one<3, 8, true, true>(a, p, s);
+            case 4: return launch_one<4, 8, true, true>(a, p, s);
+#if IGS_FWD_WIDE_PX == 8
+            case 8: return launch_one<8, 8, true, true>(a, p, s);
+            case 16: return launch_one<16, 8, true, true>(a, p, s);
+#endif
+        }
+        return cudaErrorInvalidValue;
+    }
     if (separable) {
         switch (ct) {
-            case 1: return launch_one<1, 8, true>(a, p, s);
-            case 2: return launch_one<2, 8, true>(a, p, s);
-            case 3: return launch_one<3, 8, true>(a, p, s);
-            case 4: return launch_one<4, 8, true>(a, p, s);
+            case 1: return launch_one<1, 8, true, false>(a, p, s);
+            case 2: return launch_one<2, 8, true, false>(a, p, s);
+            case 3: return launch_one<3, 8, true, false>(a, p, s);
+            case 4: return launch_one<4, 8, true, false>(a, p, s);
 #if IGS_FWD_WIDE_PX == 8
-            case 8: return launch_one<8, 8, true>(a, p, s);
-            case 16: return launch_one<16, 8, true>(a, p, s);
+            case 8: return launch_one<8, 8, true, false>(a, p, s);
+            case 16: return launch_one<16, 8, true, false>(a, p, s);
 #endif
         }
         return cudaErrorInvalidValue;
     }
     switch (ct) {
-        case 1: return launch_one<1, 8, false>(a, p, s);
-        case 2: return launch_one<2, 8, false>(a, p, s);
-        case 3: return launch_one<3, 8, false>(a, p, s);
-        case 4: return launch_one<4, 8, false>(a, p, s);
-        case 8: return launch_one<8, IGS_FWD_WIDE_PX, false>(a, p, s);
-        case 16: return launch_one<16, IGS_FWD_WIDE_PX, false>(a, p, s);
+        case 1: return launch_one<1, 8, false, false>(a, p, s);
+        case 2: return launch_one<2, 8, false, false>(a, p, s);
+        case 3: return launch_one<3, 8, false, false>(a, p, s);
+        case 4: return launch_one<4, 8, false, false>(a, p, s);
+        case 8: return launch_one<8, IGS_FWD_WIDE_PX, false, false>(a, p, s);
+        case 16: return launch_one<16, IGS_FWD_WIDE_PX, false, false>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -347,10 +439,10 @@ static int occ(int device) {
     using Cfg = FwdCfg<CT, PX_>;
     static int cached[64];
     if (device >= 0 && device < 64 && cached[device]) return cached[device];
-    cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)Cfg::SMEM);
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT, PX_, false>, Cfg::THREADS,
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_forward_kernel<CT, PX_, false, false>, Cfg::THREADS,
                                                       Cfg::SMEM) != cudaSuccess ||
         n <= 0) {
         cudaGetLastError();

@@ -14,7 +14,10 @@ struct FwdArgs {
     float* wsum;     // [B, HW]         (in_kernel_normalize && write_s)
     float* partial;  // [n_split, B, C+1, HW] otherwise
     int* status;
-    const int* grid_flag;  // device word: 0 = separable grid; nullptr = run unconditionally
+    // Selection on the device (nullptr = run unconditionally): an instantiation returns at
+    // once unless the word picks it.
+    const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable
+    const int* cull_sel;   // count of narrow gaussians: at least one in eight -> culling / plain
     int tiles_x;           // separable tiling: CTAs per tile row
     int B, N, H, W, C;
     int c0, cr;  // first channel and real channel count of this chunk
@@ -33,7 +36,8 @@ struct ReduceArgs {
     float eps;
 };
 
-cudaError_t launch_forward_chunk(int ct, bool separable, const FwdArgs& a, const FwdPlan& p, cudaStream_t s);
+cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const FwdArgs& a, const FwdPlan& p,
+                                 cudaStream_t s);
 cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s);
 
 }  // namespace igs

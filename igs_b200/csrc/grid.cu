@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(256) grid_check_kernel(GridCheckArgs a) {
         // one would (a NaN coordinate simply selects the general kernel)
         bad = (xv != a.x[b * a.xs_b + w * a.xs_w]) || (yv != a.y[b * a.ys_b + h * a.ys_h]);
     }
-    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.flag, 1);
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.flag, GRID_NOT_SEPARABLE);
 }
 
 GridKind classify_grid(long long xs_h, long long ys_w, int H, int W, bool kernels_available) {

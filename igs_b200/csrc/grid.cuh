@@ -5,9 +5,6 @@
 
 namespace igs {
 
-// word of the workspace's status area that holds the grid flag (0 = separable)
-constexpr int GRID_FLAG_WORD = 1;
-
 enum GridKind {
     GRID_GENERAL = 0,          // run the general kernels only
     GRID_SEPARABLE = 1,        // known on the host (stride-0 views): separable kernels only

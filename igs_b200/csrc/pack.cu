@@ -1,41 +1,92 @@
 // Per-gaussian prologue kernel: one thread per gaussian turns the caller's raw
-// parameters into the geometry record (backward) and the duplicated forward
-// records (one array per channel chunk).
+// parameters into the geometry record (backward) and the forward records (one array per
+// channel chunk), and measures how far the gaussian reaches.
+//
+// Reach.  With the exponent q = A dx^2 + B2 dx dy + Cq dy^2 in log2 units, the weight
+// ex2.approx.ftz(q) is exactly zero once q < -126 (results below 2^-126 are flushed).  For a
+// negative-definite form the set q >= -CULL_T is an ellipse whose bounding box has the
+// half-widths hx = sqrt(4 T (-Cq) / D), hy = sqrt(4 T (-A) / D), D = 4 A Cq - B2^2; a
+// pixel outside that box receives exactly nothing from the gaussian, which is what lets
+// the splat kernels skip (gaussian, pixel tile) combinations without changing a bit of
+// the result.  An indefinite form has no such box: hx = hy = +inf.
 #include "pack.cuh"
 
 namespace igs {
 
 __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= a.M) return;
-    const float px = a.pos[2 * i], py = a.pos[2 * i + 1];
-    float c00, c01, c11;
-    if (a.kind == SHAPE_SCALE_ROT) {
-        const CovInv ci = cov_inv_from_scale_rot(a.shape0[2 * i], a.shape0[2 * i + 1], a.shape1[i], a.eps);
-        c00 = ci.c00;
-        c01 = ci.c01;
-        c11 = ci.c11;
-    } else {
-        c00 = a.shape0[i];
-        c01 = a.shape1[i];
-        c11 = a.shape2[i];
+    bool narrow = false;
+    if (i < a.M) {
+        const float px = a.pos[2 * i], py = a.pos[2 * i + 1];
+        float c00, c01, c11;
+        if (a.kind == SHAPE_SCALE_ROT) {
+            const CovInv ci = cov_inv_from_scale_rot(a.shape0[2 * i], a.shape0[2 * i + 1], a.shape1[i], a.eps);
+            c00 = ci.c00;
+            c01 = ci.c01;
+            c11 = ci.c11;
+        } else {
+            c00 = a.shape0[i];
+            c01 = a.shape1[i];
+            c11 = a.shape2[i];
+        }
+        const float A = EXP2_SCALE * c00, B2 = 2.0f * EXP2_SCALE * c01, Cq = EXP2_SCALE * c11;
+        const float al = a.alpha[i];
+
+        float hx = INFINITY, hy = INFINITY;
+        const float D = 4.0f * A * Cq - B2 * B2;
+        if (A < 0.f && Cq < 0.f && D > 0.f) {
+            // a little wider than exact, so that fp32 rounding here can never cull a non-zero weight
+            hx = 1.001f * sqrtf(4.0f * CULL_T * (-Cq) / D);
+            hy = 1.001f * sqrtf(4.0f * CULL_T * (-A) / D);
+            if (!(hx == hx) || !(hy == hy)) hx = hy = INFINITY;
+        }
+        if (a.narrow_count && a.x && a.W > 1 && a.H > 1) {
+            // "narrow" = the box covers less than three quarters of the sampled extent in x or y
+            const long long b = i / a.N;
+            const float x0 = a.x[b * a.xs_b], x1 = a.x[b * a.xs_b + (long long)(a.W - 1) * a.xs_w];
+            const float y0 = a.y[b * a.ys_b], y1 = a.y[b * a.ys_b + (long long)(a.H - 1) * a.ys_h];
+            narrow = (2.f * hx < 0.75f * fabsf(x1 - x0)) || (2.f * hy < 0.75f * fabsf(y1 - y0));
+        }
+
+        if (a.geo) {
+            float4* g = reinterpret_cast<float4*>(a.geo + i * GEO_FLOATS);
+            g[0] = make_float4(px, py, A, B2);
+            g[1] = make_float4(Cq, al, hx, hy);
+        }
+        for (int k = 0; k < a.ch.n; ++k) {
+            float* rec = a.frec[k];
+            if (!rec) continue;
+            const int ct = a.ch.ct[k], cr = a.ch.cr[k], c0 = a.ch.c0[k];
+            const int rs = fwd_rec_floats(ct);
+            float* r = rec + i * rs;
+            r[0] = px; r[1] = py; r[2] = A; r[3] = B2; r[4] = Cq; r[5] = al;
+            // colours pre-multiplied by alpha: numerator += e * (alpha * colour)
+            for (int c = 0; c < ct; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * a.C + c0 + c] : 0.f;
+            r[6 + ct] = hx;
+            r[7 + ct] = hy;
+            for (int c = 8 + ct; c < rs; ++c) r[c] = 0.f;
+        }
     }
-    const float A = EXP2_SCALE * c00, B2 = 2.0f * EXP2_SCALE * c01, Cq = EXP2_SCALE * c11;
-    const float al = a.alpha[i];
-    if (a.geo) {
-        float4* g = reinterpret_cast<float4*>(a.geo + i * GEO_FLOATS);
-        g[0] = make_float4(px, py, A, B2);
-        g[1] = make_float4(Cq, al, 0.f, 0.f);
+    if (a.narrow_count) {
+        const int n = __syncthreads_count(narrow);
+        if (threadIdx.x == 0 && n) atomicAdd(a.narrow_count, n);
     }
-    for (int k = 0; k < a.ch.n; ++k) {
-        float* rec = a.frec[k];
-        if (!rec) continue;
-        const int ct = a.ch.ct[k], cr = a.ch.cr[k], c0 = a.ch.c0[k];
-        const int rs = fwd_rec_floats(ct);
-        // colours pre-multiplied by alpha: numerator += e * (alpha * colour)
-        float* r = rec + i * rs;
-        r[0] = px; r[1] = py; r[2] = A; r[3] = B2; r[4] = Cq; r[5] = al;
-        for (int c = 0; c < rs - 6; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * a.C + c0 + c] : 0.f;
+    // Are the first row of x and the first column of y non-decreasing?  (The separable
+    // backward kernel takes the ends of a run of columns as its x range when it skips.)
+    if (a.grid_flag && a.x) {
+        bool bad = false;
+        const long long per_b = (long long)a.W + a.H, total = a.B * per_b;
+        for (long long j = i; j < total; j += (long long)gridDim.x * blockDim.x) {
+            const long long b = j / per_b, k = j - b * per_b;
+            if (k < a.W - 1) {
+                const float* p = a.x + b * a.xs_b + k * a.xs_w;
+                bad |= !(p[0] <= p[a.xs_w]);
+            } else if (k >= a.W && k - a.W < a.H - 1) {
+                const float* p = a.y + b * a.ys_b + (k - a.W) * a.ys_h;
+                bad |= !(p[0] <= p[a.ys_h]);
+            }
+        }
+        if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.grid_flag, GRID_NOT_MONOTONE);
     }
 }
 
@@ -43,6 +94,10 @@ cudaError_t launch_pack(const PackArgs& a, cudaStream_t s) {
     if (a.M <= 0) return cudaSuccess;
     const int threads = 256;
     const long long blocks = (a.M + threads - 1) / threads;
+    if (a.narrow_count) {
+        cudaError_t e = cudaMemsetAsync(a.narrow_count, 0, sizeof(int), s);
+        if (e != cudaSuccess) return e;
+    }
     {
         KernelTimer timer(K_PACK, s);
         pack_kernel<<<(unsigned)blocks, threads, 0, s>>>(a);

@@ -14,6 +14,12 @@ struct PackArgs {
     const float* shape2;  // unused        | cov_inv_11 [M]
     const float* alpha;   // [M]
     const float* colors;  // [M,C]
+    const float* x;       // sample coordinates (only their extent is read) or nullptr
+    const float* y;
+    long long xs_b, xs_w, ys_b, ys_h;
+    int* narrow_count;    // device counter of narrow gaussians, or nullptr
+    int* grid_flag;       // receives GRID_NOT_MONOTONE when an axis is not non-decreasing, or nullptr
+    int B, N, H, W;       // batch, gaussians per batch element, image size
     float* geo;           // [M,8] or nullptr
     float* frec[MAX_CHUNKS];  // per channel chunk, [M, fwd_rec_floats(ct)] or nullptr
     Chunks ch;

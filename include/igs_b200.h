@@ -163,6 +163,15 @@ int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_ti
                       int* fwd_splits, int* bwd_threads, int* bwd_slabs);
 
 /*
+ * Lossless culling, on by default.  A weight ex2(q) is exactly zero once its exponent is
+ * below -126, so a gaussian whose zero-weight box misses a tile of pixels contributes
+ * exactly nothing there; the kernels skip such (gaussian, tile) combinations when
+ * enough gaussians are narrow for the test to pay.  Results are bit-identical with
+ * culling off (this switch exists to verify that, and for timing).  Process-wide.
+ */
+int igs_set_culling(int on);
+
+/*
  * Per-kernel device timing for reports.  While enabled, every kernel launch of the
  * library is bracketed by CUDA events recorded on the launch's own stream;
  * igs_profile_read waits for the recorded events and returns the accumulated device
