@@ -47,9 +47,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_b8", "cfg4"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_b8", "cfg4", "narrow"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-culling", action="store_true", help="switch the lossless culling off (for comparison)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     return ap.parse_args()
 
@@ -248,6 +249,8 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
+    if args.no_culling:
+        _lib.set_culling(False)
 
     cfg = workloads.CONFIGS[args.workload]
     warmup = max(args.warmup, 3)
@@ -339,6 +342,13 @@ def run_b200(args):
                              on_dev["colors"], on_dev["x"][:, 0], on_dev["y"][:, 0], 1e-6, keep_workspace=True)
     if _lib.read_status(probe_fwd[2]) != 0:
         raise SystemExit("igs_b200: a kernel reported a timed-out wait (status word non-zero)")
+    # third word of the status area: gaussians the prologue counted as narrow; the culling
+    # instantiations run when that is at least one gaussian in eight
+    n_narrow = int(probe_fwd[2][:16].view(torch.int32)[2])
+    n_local = host["positions"].shape[0] * host["positions"].shape[1]
+    culling = {"enabled": not args.no_culling, "narrow_gaussians": n_narrow, "gaussians": n_local,
+               "active": (not args.no_culling) and n_narrow * 8 >= n_local,
+               "note": "lossless: skipped terms are exact zeros; value counts all B*N*H*W evaluations"}
     del probe_fwd
 
     total_ms = torch.tensor([sum(times), sum(e2e_times)], dtype=torch.float64, device=dev)
@@ -426,6 +436,7 @@ def run_b200(args):
                     "achieved_gbs": hbm_bytes / (statistics.mean(times) * 1e-3) / 1e9,
                     "peak_gbs": peaks.get("hbm_gbs"), "note": "not the bound: the path is FP32/MUFU issue-bound"},
             "kernel_ms_per_step": {k: v[0] / steps for k, v in prof.items() if v[1]},
+            "culling": culling,
             "plan": _lib.describe_plan(cfg.B, host["positions"].shape[1], cfg.H, cfg.W, cfg.C, dev),
         }
         if world == 1 and not args.no_cpu_baseline:

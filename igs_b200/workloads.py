@@ -41,6 +41,10 @@ CONFIGS = {
     "cfg3": SplatConfig("cfg3", 1, 16384, 512, 512, 3, 0.05, 0.30, seed=3),
     # large feature-map render
     "cfg4": SplatConfig("cfg4", 64, 65536, 512, 512, 16, 0.02, 0.20, normal_colors=True, seed=4),
+    # the regime of the reference's per-image fit (scripts/2dgs_img_comp.py: thousands of
+    # gaussians of scale ~e^-5 on a 1024x1024 image): almost every (gaussian, pixel) weight is
+    # exactly zero, which the lossless culling exploits
+    "narrow": SplatConfig("narrow", 1, 16384, 1024, 1024, 3, 0.004, 0.012, seed=7),
     # one GPU's share of config 4 when its batch of 64 is spread over 8 GPUs
     "cfg4_b8": SplatConfig("cfg4_b8", 8, 65536, 512, 512, 16, 0.02, 0.20, normal_colors=True, seed=4),
 }
