@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-culling", action="store_true", help="switch the lossless culling off (for comparison)")
+    ap.add_argument("--backward-sort", choices=["auto", "on", "off"], default="auto",
+                    help="spatial processing order of the backward's gaussians (results are the same bits)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     return ap.parse_args()
 
@@ -249,6 +251,7 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
+    _lib.set_backward_sort(args.backward_sort)
     if args.no_culling:
         _lib.set_culling(False)
 
@@ -348,6 +351,7 @@ def run_b200(args):
     n_local = host["positions"].shape[0] * host["positions"].shape[1]
     culling = {"enabled": not args.no_culling, "narrow_gaussians": n_narrow, "gaussians": n_local,
                "active": (not args.no_culling) and n_narrow * 8 >= n_local,
+               "backward_sort": args.backward_sort,
                "note": "lossless: skipped terms are exact zeros; value counts all B*N*H*W evaluations"}
     del probe_fwd
 
@@ -396,7 +400,10 @@ def run_b200(args):
                     "launch_ms": ms / steps, "launches": n,
                     "algorithmic_instr_per_eval": instr[name],
                     "executed_instr_per_eval": executed[name],
-                    "executed_frac": ev_rank * executed[name] / per_pass_s / fp32_peak,
+                    # with culling active an unknown share of the evaluations is skipped as exact
+                    # zeros, so the issue count is not known and no utilisation is claimed
+                    "executed_frac": None if culling["active"]
+                    else ev_rank * executed[name] / per_pass_s / fp32_peak,
                     "mix_ceiling_frac": None if separable else mix_ceiling[name] / fp32_peak,
                     "grid": "separable (xy_grid), detected on the device" if separable else "general",
                     "peak_source": "measured live: FFMA-only kernel, best of scalar and f32x2 (igs_probe_fp32_rate)",
@@ -428,8 +435,8 @@ def run_b200(args):
                               "unit": "T lane-instr/s", "frac": step_ach / fp32_peak,
                               "algorithmic_instr_per_eval": 27 + 3 * C,
                               "executed_instr_per_eval": executed["forward"] + executed["backward"],
-                              "executed_frac": step_ach / fp32_peak * (executed["forward"] + executed["backward"])
-                              / (27 + 3 * C),
+                              "executed_frac": None if culling["active"] else step_ach / fp32_peak
+                              * (executed["forward"] + executed["backward"]) / (27 + 3 * C),
                               "nominal_peak": n_sm * 128 * (sm or 0) * 1e6 / 1e12 if sm else None},
             "probes": probes,
             "hbm": {"algorithmic_bytes_per_step": hbm_bytes,

@@ -38,10 +38,13 @@ SIGNATURES = {
     "igs_forward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _sz, _i, _vp]),
     "igs_forward_sr_static": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _i, _vp]),
     "igs_normalize": (_i, [_vp] + [_i] * 4 + [_f, _vp, _vp, _i, _vp]),
-    "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 8 + [_sz, _i, _vp]),
-    "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
+    "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
+    "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 10 + [_sz, _i, _vp]),
     "igs_read_status": (_i, [_vp, _i, _vp, ctypes.POINTER(_i)]),
     "igs_set_culling": (_i, [_i]),
+    "igs_spatial_order_workspace_bytes": (_sz, [_i, _i]),
+    "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
+    "igs_read_narrow_count": (_i, [_vp, _i, _vp, _vp]),
     "igs_profile_enable": (_i, [_i]),
     "igs_profile_reset": (_i, []),
     "igs_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
@@ -182,12 +185,84 @@ def normalize(sums: torch.Tensor, eps: float):
     return out, wsum
 
 
+def spatial_order(pos, x3, y3):
+    """[B,N] int32 permutation putting spatial neighbours next to each other (the `order`
+    argument of the backward)."""
+    dev = pos.device
+    B, N, _ = pos.shape
+    _, H, W = x3.shape
+    lib = load()
+    ws = _workspace(int(lib.igs_spatial_order_workspace_bytes(B, N)), dev)
+    order = torch.empty(B, N, dtype=torch.int32, device=dev)
+    check("igs_spatial_order",
+          lib.igs_spatial_order(_ptr(pos), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N, H, W, _ptr(order),
+                                _ptr(ws), ws.numel(), dev.index, _stream(dev)))
+    return order
+
+
+class _NarrowProbe:
+    """Host-side memory of whether a shape's gaussians were narrow at its recent backward
+    calls, learnt without ever blocking: now and then a backward queues a copy of the
+    device's narrow-gaussian count into pinned memory, and a later call picks the value up
+    once the copy's event has completed."""
+
+    EVERY = 32  # after the first few calls, look again every this many
+
+    def __init__(self):
+        self.host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self.event = None
+        self.calls = 0
+        self.narrow = False
+
+    def poll(self, total):
+        if self.event is not None and not torch.cuda.is_current_stream_capturing() and self.event.query():
+            self.narrow = int(self.host[0]) * 8 >= total
+            self.event = None
+        return self.narrow
+
+    def queue(self, ws):
+        self.calls += 1
+        if self.event is not None or not (self.calls <= 4 or self.calls % self.EVERY == 0):
+            return
+        dev = ws.device
+        if torch.cuda.is_current_stream_capturing():
+            return
+        check("igs_read_narrow_count",
+              load().igs_read_narrow_count(_ptr(ws), dev.index, _stream(dev), ctypes.c_void_p(self.host.data_ptr())))
+        self.event = torch.cuda.Event()
+        self.event.record(torch.cuda.current_stream(dev))
+
+
+_BACKWARD_SORT = "auto"
+_probes = {}
+
+
+def set_backward_sort(mode: str) -> None:
+    """'auto' (default): the backward takes its gaussians in spatial order once the shape's
+    recent calls have shown mostly narrow gaussians; 'on' / 'off': always / never.  The
+    gradients are the same bit for bit in every mode; only the time differs."""
+    global _BACKWARD_SORT
+    if mode not in ("auto", "on", "off"):
+        raise ValueError("mode must be 'auto', 'on' or 'off'")
+    _BACKWARD_SORT = mode
+    _probes.clear()
+
+
 def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps, grad_mode, want_xy,
-             keep_workspace=False):
-    """Returns dict of gradients; d_x / d_y only when want_xy."""
+             keep_workspace=False, order=None):
+    """Returns dict of gradients; d_x / d_y only when want_xy.  order: None = by the
+    set_backward_sort policy, or an explicit [B,N] int32 permutation."""
     dev = pos.device
     B, N, C = colors.shape
     _, H, W = x3.shape
+    probe = None
+    if order is None and B * N > 0:
+        if _BACKWARD_SORT == "on":
+            order = spatial_order(pos, x3, y3)
+        elif _BACKWARD_SORT == "auto":
+            probe = _probes.setdefault((dev.index, B, N, H, W), _NarrowProbe())
+            if probe.poll(B * N):
+                order = spatial_order(pos, x3, y3)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     f32 = dict(dtype=torch.float32, device=dev)
@@ -198,7 +273,8 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     d_y = torch.empty(B, H, W, **f32) if want_xy else None
     head = (_ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), _ptr(wsum), _ptr(out), _ptr(gout), B, N, H, W, C,
             float(eps), int(grad_mode))
-    tail = (_ptr(d_alpha), _ptr(d_col), _ptr(d_x), _ptr(d_y), _ptr(ws), ws.numel(), dev.index, _stream(dev))
+    tail = (_ptr(d_alpha), _ptr(d_col), _ptr(d_x), _ptr(d_y), _ptr(order), _ptr(ws), ws.numel(), dev.index,
+            _stream(dev))
     lib = load()
     if kind == "sr":
         d_s0 = torch.empty(B, N, 2, **f32)
@@ -213,6 +289,8 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
               lib.igs_backward_cov(_ptr(pos), _ptr(s0), _ptr(s1), _ptr(s2), _ptr(alphas), _ptr(colors), *head,
                                    _ptr(d_pos), _ptr(d_s0), _ptr(d_s1), _ptr(d_s2), *tail))
         res = {"positions": d_pos, "c00": d_s0, "c01": d_s1, "c11": d_s2, "alphas": d_alpha, "colors": d_col}
+    if probe is not None:
+        probe.queue(ws)
     if want_xy:
         res["x"], res["y"] = d_x, d_y
     if keep_workspace:

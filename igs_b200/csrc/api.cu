@@ -388,8 +388,8 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
                          const float* alpha, const float* colors, const float* x, const int64_t* xs, const float* y,
                          const int64_t* ys, const float* wsum, const float* out, const float* gout, int B, int N,
                          int H, int W, int C, float eps, int mode, float* d_pos, float* d_s0, float* d_s1,
-                         float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, void* workspace,
-                         size_t workspace_bytes, int device, void* stream) {
+                         float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, const int* order,
+                         void* workspace, size_t workspace_bytes, int device, void* stream) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
     if ((d_x == nullptr) != (d_y == nullptr)) return IGS_ERR_ARG;
@@ -491,6 +491,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.geo = pa.geo;
         ba.colors = colors;
         ba.prec = ta.prec[k];
+        ba.order = order;
         ba.part = reinterpret_cast<float*>(ws + p.off_part);
         ba.status = reinterpret_cast<int*>(ws);
         ba.npairs = p.npairs;
@@ -672,11 +673,11 @@ int igs_backward_sr(const float* positions, const float* scales, const float* ro
                     const float* colors, const float* x, const int64_t* x_strides, const float* y,
                     const int64_t* y_strides, const float* wsum, const float* out, const float* gout, int B, int N,
                     int H, int W, int C, float eps, int grad_mode, float* d_positions, float* d_scales,
-                    float* d_rotations, float* d_alphas, float* d_colors, float* d_x, float* d_y, void* workspace,
-                    size_t workspace_bytes, int device, void* stream) {
+                    float* d_rotations, float* d_alphas, float* d_colors, float* d_x, float* d_y, const int* order,
+                    void* workspace, size_t workspace_bytes, int device, void* stream) {
     return backward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_scales, d_rotations,
-                         nullptr, d_alphas, d_colors, d_x, d_y, workspace, workspace_bytes, device, stream);
+                         nullptr, d_alphas, d_colors, d_x, d_y, order, workspace, workspace_bytes, device, stream);
 }
 
 int igs_backward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01,
@@ -684,12 +685,12 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                      const int64_t* x_strides, const float* y, const int64_t* y_strides, const float* wsum,
                      const float* out, const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
                      float* d_positions, float* d_cov_inv_00, float* d_cov_inv_01, float* d_cov_inv_11,
-                     float* d_alphas, float* d_colors, float* d_x, float* d_y, void* workspace, size_t workspace_bytes,
-                     int device, void* stream) {
+                     float* d_alphas, float* d_colors, float* d_x, float* d_y, const int* order, void* workspace,
+                     size_t workspace_bytes, int device, void* stream) {
     return backward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_cov_inv_00,
-                         d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, workspace, workspace_bytes, device,
-                         stream);
+                         d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, order, workspace, workspace_bytes,
+                         device, stream);
 }
 
 int igs_set_culling(int on) {
@@ -733,6 +734,16 @@ int igs_read_status(const void* workspace, int device, void* stream, int* host_s
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     return *host_status ? IGS_ERR_STATUS : IGS_OK;
+}
+
+int igs_read_narrow_count(const void* workspace, int device, void* stream, int* host_count) {
+    if (!workspace || !host_count) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    return (int)cudaMemcpyAsync(host_count, reinterpret_cast<const int*>(workspace) + NARROW_COUNT_WORD, sizeof(int),
+                                cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -28,6 +28,7 @@ struct BwdArgs {
     const float* geo;     // [B, N, 8]
     const float* colors;  // [B, N, C]
     const float* prec;    // records of this chunk
+    const int* order;     // [B, N] permutation: processing slot -> gaussian index, or nullptr
     float* part;          // [n_slab, B, planes, N]
     int* status;
     // Selection on the device (nullptr = run unconditionally): a kernel returns at once

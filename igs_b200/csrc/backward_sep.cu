@@ -155,7 +155,11 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
     float box_x0[GPT], box_x1[GPT], box_y0[GPT], box_y1[GPT];
 #pragma unroll
     for (int g = 0; g < GPT; ++g) {
-        n[g] = blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        // slot in processing order -> gaussian index (a caller-supplied spatial order puts
+        // neighbours into the same warp; without one the order is the identity)
+        const int slot = a.order ? blockIdx.x * Cfg::GAUSS_PER_CTA + tid * GPT + g
+                                 : blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        n[g] = slot < a.N ? (a.order ? a.order[(long long)b * a.N + slot] : slot) : a.N;
         const int nn = n[g] < a.N ? n[g] : a.N - 1;
         const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
         const float4 g0 = gp[0], g1 = gp[1];

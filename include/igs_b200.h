@@ -126,14 +126,18 @@ int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, floa
  *   grad_mode == IGS_GRAD_EXACT (may be NULL otherwise); gout [B,C,H,W] is NOT
  *   modified (the reference divides it in place, :371).
  *   d_x, d_y [B,H,W] contiguous, both NULL to skip (src/igs/gs2d.py:433-434).
+ *   order: NULL, or a permutation [B,N] (int32) of each batch element's gaussians giving
+ *   the order in which threads take them.  Results do not depend on it, bit for bit; a
+ *   spatial order (neighbours adjacent) lets whole warps skip pixel runs none of their
+ *   gaussians reach, which is where the culling of the backward gets its speed.
  */
 int igs_backward_sr(const float* positions, const float* scales, const float* rotations,
                     const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
                     const float* y, const int64_t* y_strides, const float* wsum, const float* out,
                     const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
                     float* d_positions, float* d_scales, float* d_rotations, float* d_alphas,
-                    float* d_colors, float* d_x, float* d_y, void* workspace, size_t workspace_bytes,
-                    int device, void* stream);
+                    float* d_colors, float* d_x, float* d_y, const int* order, void* workspace,
+                    size_t workspace_bytes, int device, void* stream);
 
 /*
  * Backward to inverse-covariance entries.  Replaces
@@ -146,8 +150,8 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                      const float* wsum, const float* out, const float* gout, int B, int N, int H, int W,
                      int C, float eps, int grad_mode, float* d_positions, float* d_cov_inv_00,
                      float* d_cov_inv_01, float* d_cov_inv_11, float* d_alphas, float* d_colors,
-                     float* d_x, float* d_y, void* workspace, size_t workspace_bytes, int device,
-                     void* stream);
+                     float* d_x, float* d_y, const int* order, void* workspace, size_t workspace_bytes,
+                     int device, void* stream);
 
 /*
  * Synchronises `stream`, copies the workspace's status word to *host_status
@@ -170,6 +174,33 @@ int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_ti
  * culling off (this switch exists to verify that, and for timing).  Process-wide.
  */
 int igs_set_culling(int on);
+
+/*
+ * A spatial order for the `order` argument of igs_backward_*: order[b, slot] = index of
+ * the gaussian taken in that slot, neighbours in the image next to each other (Morton
+ * order of a 64 x 64 lattice over the sampled extent; x, y and their strides as for the
+ * forward, only the first row of x and the first column of y are read).  Worth computing
+ * when most gaussians are narrow (igs_read_narrow_count) and the grid is separable: the
+ * backward then skips most pixel runs.  The order within a lattice cell may differ from
+ * run to run; the gradients computed with it do not.  No counterpart in the reference,
+ * whose backward is a dense torch expression (src/igs/gs2d.py:331-436).
+ *   workspace: igs_spatial_order_workspace_bytes(B, N) bytes of device memory.
+ */
+size_t igs_spatial_order_workspace_bytes(int B, int N);
+int igs_spatial_order(const float* positions, const float* x, const int64_t* x_strides, const float* y,
+                      const int64_t* y_strides, int B, int N, int H, int W, int* order,
+                      void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
+ * Asynchronous read of the narrow-gaussian count the last forward or backward on this
+ * workspace left: the number of gaussians (over the whole batch) whose zero-weight box
+ * covers less than three quarters of the sampled extent in x or y.  The copy is queued on
+ * `stream` into *host_count (HOST pointer, pinned for a copy that does not block); the
+ * value is there once the stream has reached that point.  The culling kernels are selected
+ * on the device when count * 8 >= B * N; a host uses the same test to decide whether a
+ * spatial order pays.
+ */
+int igs_read_narrow_count(const void* workspace, int device, void* stream, int* host_count);
 
 /*
  * Per-kernel device timing for reports.  While enabled, every kernel launch of the

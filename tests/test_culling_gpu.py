@@ -96,3 +96,101 @@ def test_culling_with_reversed_axes_and_wide_gaussians_mixed():
     assert torch.equal(o_on, o_off)
     for k in g_on:
         assert torch.equal(g_on[k], g_off[k]), k
+
+
+def _backward_with(d, gout, x, y, order):
+    """Gradients through the library call itself, with an explicit processing order."""
+    from igs_b200 import _lib
+
+    x3, y3 = x[:, 0], y[:, 0]
+    out, wsum = _lib.forward("sr", d["positions"], d["scales"], d["rotations"], None, d["alphas"], d["colors"], x3, y3,
+                             1e-6)
+    res = _lib.backward("sr", d["positions"], d["scales"], d["rotations"], None, d["alphas"], d["colors"], x3, y3,
+                        wsum, out, gout, 1e-6, 0, False, order=order)
+    torch.cuda.synchronize()
+    return res
+
+
+def test_spatial_order_is_a_permutation_with_neighbours_adjacent():
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 3, 5000, 64, 96
+    d, _, x, y = _case(B, N, H, W, 3, 0.004, 0.03, seed=21, dev=dev)
+    order = _lib.spatial_order(d["positions"], x[:, 0], y[:, 0])
+    assert order.dtype == torch.int32 and order.shape == (B, N)
+    assert torch.equal(order.long().sort(dim=1).values, torch.arange(N, device=dev).expand(B, N))
+    # a run of 64 consecutive slots (one warp's gaussians) spans a small patch, not the image
+    p = torch.gather(d["positions"], 1, order.long()[..., None].expand(B, N, 2))
+    runs = p[:, : N // 64 * 64].reshape(B, -1, 64, 2)
+    span = (runs.amax(2) - runs.amin(2)).amax(-1)  # [B, runs]: larger side of the run's box
+    assert float(span.median()) < 0.5, float(span.median())  # the image spans 2
+
+
+@pytest.mark.parametrize("kind", ["spatial", "random", "reversed"])
+def test_processing_order_changes_no_bit(kind):
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 2, 3001, 96, 160  # N odd: the last thread's second slot is empty
+    d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.03, seed=23, dev=dev)
+    d["scales"][:, ::89] = 0.7
+    if kind == "spatial":
+        order = _lib.spatial_order(d["positions"], x[:, 0], y[:, 0])
+    elif kind == "random":
+        gen = torch.Generator().manual_seed(5)
+        order = torch.stack([torch.randperm(N, generator=gen) for _ in range(B)]).to(torch.int32).to(dev)
+    else:
+        order = torch.arange(N - 1, -1, -1, dtype=torch.int32, device=dev).expand(B, N).contiguous()
+    _lib.set_backward_sort("off")
+    try:
+        want = _backward_with(d, gout, x, y, None)
+    finally:
+        _lib.set_backward_sort("auto")
+    got = _backward_with(d, gout, x, y, order)
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+
+
+def test_processing_order_on_general_grid_and_wide_channels():
+    """The general kernels (warped grid) and a 16-channel chunk honour the order too."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 777, 48, 80
+    d, gout, x, y = _case(B, N, H, W, 16, 0.01, 0.2, seed=29, dev=dev)
+    x = (x + 0.01 * torch.sin(7 * y)).contiguous()
+    gen = torch.Generator().manual_seed(6)
+    order = torch.randperm(N, generator=gen).to(torch.int32).to(dev)[None].contiguous()
+    _lib.set_backward_sort("off")
+    try:
+        want = _backward_with(d, gout, x, y, None)
+    finally:
+        _lib.set_backward_sort("auto")
+    got = _backward_with(d, gout, x, y, order)
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+
+
+def test_auto_policy_learns_that_gaussians_are_narrow():
+    """'auto' starts unsorted, reads the device's narrow count without blocking, and sorts
+    from a later call on; the gradients stay the same bits throughout."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 4096, 128, 128
+    d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.02, seed=31, dev=dev)
+    _lib.set_backward_sort("auto")  # forgets what earlier tests taught it
+    first = _backward_with(d, gout, x, y, None)
+    probe = _lib._probes[(dev.index, B, N, H, W)]
+    assert probe.calls == 1 and not probe.narrow
+    for _ in range(3):
+        again = _backward_with(d, gout, x, y, None)  # each call synchronises, so the copy has landed
+    assert probe.narrow
+    for k in first:
+        assert torch.equal(again[k], first[k]), k
+    # wide gaussians never switch it on
+    d2, gout2, x2, y2 = _case(B, N, 100, W, 3, 0.3, 0.6, seed=32, dev=dev)
+    for _ in range(4):
+        _backward_with(d2, gout2, x2, y2, None)
+    assert not _lib._probes[(dev.index, B, N, 100, W)].narrow
