@@ -163,7 +163,7 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
     return IGS_OK;
 }
 
-int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs) {
     if (B < 0 || N < 0 || H < 0 || W < 0) return IGS_ERR_ARG;
     if (B > 65535) return IGS_ERR_LIMIT;
     int rc = make_chunks(C, &p->ch);
@@ -175,24 +175,43 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
     p->chunk_pairs = backward_chunk_pairs(ct);
     p->stages = 2;
     p->npairs = (HW + 1) / 2;
+    p->nrp = (H + 1) / 2;
+    p->ncb = (W + 3) / 4;
+    p->sep_ok = (p->ch.n == 1 && backward_has_separable(ct)) ? 1 : 0;
     const long long per_cta = (long long)p->threads * p->gauss_per_thread;
     const long long groups = ((long long)N + per_cta - 1) / per_cta;
     const long long slots = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
     const long long base = groups * (B > 0 ? B : 1);
-    int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);
-    long long per = (p->npairs + ns - 1) / ns;
-    per = (per + p->chunk_pairs - 1) / p->chunk_pairs * p->chunk_pairs;
-    if (per <= 0) per = p->chunk_pairs;
-    p->pairs_per_slab = per;
-    p->n_slab = (int)((p->npairs + per - 1) / per);
-    if (p->n_slab < 1) p->n_slab = 1;
+    const int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);
+    // Fine partition: slabs of 8 row pairs, at most 96 of them, never fewer than the plain
+    // partition has.  A function of the shape alone, like the plain one, so the result's bits
+    // depend on whether an order was passed but not on the order or on the gaussians.
+    int ns_fine = ns;
+    if (p->sep_ok) {
+        const int want = (p->nrp + 7) / 8;
+        ns_fine = want < 96 ? want : 96;
+        if (ns_fine < ns) ns_fine = ns;
+    }
+    auto slabs_for = [&](int parts, long long* per_out) {
+        long long per = (p->npairs + parts - 1) / parts;
+        per = (per + p->chunk_pairs - 1) / p->chunk_pairs * p->chunk_pairs;
+        if (per <= 0) per = p->chunk_pairs;
+        *per_out = per;
+        const int n = (int)((p->npairs + per - 1) / per);
+        return n < 1 ? 1 : n;
+    };
+    long long per_plain = 0, per_fine = 0;
+    const int n_plain = slabs_for(ns, &per_plain);
+    // the fine count is kept as asked (slabs past the image's end are empty and write zeros)
+    slabs_for(ns_fine, &per_fine);
+    const bool fine = fine_slabs && ns_fine > n_plain;
+    p->pairs_per_slab = fine ? per_fine : per_plain;
+    p->n_slab = fine ? ns_fine : n_plain;
+    const int n_slab_max = ns_fine > n_plain ? ns_fine : n_plain;
     p->planes = N_MOMENTS * p->ch.n + C;
     // separable variant: same slab count, slabs are ranges of whole row pairs
-    p->nrp = (H + 1) / 2;
-    p->ncb = (W + 3) / 4;
     p->rp_per_slab = (p->nrp + p->n_slab - 1) / p->n_slab;
     if (p->rp_per_slab < 1) p->rp_per_slab = 1;
-    p->sep_ok = (p->ch.n == 1 && backward_has_separable(ct)) ? 1 : 0;
 
     size_t off = STATUS_BYTES;
     const long long M = (long long)B * N;
@@ -208,7 +227,7 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p) {
         off = align_up(off + rec_bytes, 256);
     }
     p->off_part = off;
-    off = align_up(off + (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float), 256);
+    off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
     p->bytes = off;
     return IGS_OK;
 }
@@ -426,7 +445,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     }
 
     BwdPlan p;
-    rc = plan_backward(B, N, H, W, C, device, &p);
+    rc = plan_backward(B, N, H, W, C, device, &p, order != nullptr);
     if (rc) return rc;
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);

@@ -126,11 +126,16 @@ struct BwdSepCfg {
     static constexpr int RS = bwd_sep_rec_floats(CT);
     static constexpr int PF = bwd_sep_pair_floats(CT);
     static constexpr int SKIP_RUN = 8;  // blocks (32 columns) per skip decision
-    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_BLOCKS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16;
+#ifndef IGS_BWDSEP_CULL_LESS
+#define IGS_BWDSEP_CULL_LESS 1  // resident CTAs per SM the skipping kernel gives up for registers (no spills)
+#endif
+    // stages, their barriers, the failure flag, and 32 words for the CTA-wide box reduction
+    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_BLOCKS * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16 + 128;
 };
 
 template <int CT, bool CULL>
-__global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTAS) splat_backward_sep_kernel(BwdArgs a) {
+__global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTAS - (CULL ? IGS_BWDSEP_CULL_LESS : 0))
+    splat_backward_sep_kernel(BwdArgs a) {
     using Cfg = BwdSepCfg<CT>;
     constexpr int T = Cfg::THREADS, GPT = Cfg::GPT, PCB = Cfg::CHUNK_BLOCKS, NS = Cfg::STAGES, RS = Cfg::RS, PF = Cfg::PF;
     constexpr int SKIP_RUN = Cfg::SKIP_RUN;
@@ -173,6 +178,10 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         box_x1[g] = g0.x + g1.z;
         box_y0[g] = g0.y - g1.w;
         box_y1[g] = g0.y + g1.w;
+        if (CULL && n[g] >= a.N) {  // an empty slot reaches nothing
+            box_x0[g] = box_y0[g] = INFINITY;
+            box_x1[g] = box_y1[g] = -INFINITY;
+        }
 #pragma unroll
         for (int c = 0; c < CT; ++c) {
             const float v = (c < a.cr) ? a.colors[((long long)b * a.N + nn) * a.C + a.c0 + c] : 0.f;
@@ -203,8 +212,93 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
     // ---- this slab's row pairs, as a stream of blocks ----
     const int rp_begin = min(a.nrp, slab * a.rp_per_slab);
     const int rp_end = min(a.nrp, rp_begin + a.rp_per_slab);
-    const long long blk_begin = (long long)rp_begin * a.ncb;
-    const int n_total = (rp_end - rp_begin) * a.ncb;
+    // The stream is rows [rp0, rp0 + n_rp) x column blocks [cb0, cb0 + seg) of the block
+    // records: everything in the plain kernel; in the skipping kernel only the rectangle of
+    // blocks the box around ALL of this CTA's gaussians meets (non-decreasing axes make it a
+    // rectangle), so a CTA of neighbouring gaussians neither loads nor visits the rest.  The
+    // slabs stay fixed ranges of rows whatever the gaussians: which pixels a partial sum
+    // covers, and with it every bit of the result, depends on the shape alone.
+    int rp0 = rp_begin, n_rp = rp_end - rp_begin, cb0 = 0, seg_c = a.ncb;
+    if constexpr (CULL) {
+        float* s_box = reinterpret_cast<float*>(s_failed + 4);  // [4 warps][4], then 4 ints
+        int* s_rng = reinterpret_cast<int*>(s_box + 16);
+        float u[4] = {INFINITY, -INFINITY, INFINITY, -INFINITY};  // x0, x1, y0, y1 of the union
+        bool open_box = false;  // a NaN or infinite box: no restriction
+#pragma unroll
+        for (int g = 0; g < GPT; ++g) {
+            if (n[g] >= a.N) continue;
+            open_box |= !(box_x1[g] - box_x0[g] < INFINITY) || !(box_y1[g] - box_y0[g] < INFINITY);
+            u[0] = fminf(u[0], box_x0[g]);
+            u[1] = fmaxf(u[1], box_x1[g]);
+            u[2] = fminf(u[2], box_y0[g]);
+            u[3] = fmaxf(u[3], box_y1[g]);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            u[0] = fminf(u[0], __shfl_xor_sync(0xffffffffu, u[0], d));
+            u[1] = fmaxf(u[1], __shfl_xor_sync(0xffffffffu, u[1], d));
+            u[2] = fminf(u[2], __shfl_xor_sync(0xffffffffu, u[2], d));
+            u[3] = fmaxf(u[3], __shfl_xor_sync(0xffffffffu, u[3], d));
+        }
+        if ((tid & 31) == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s_box[(tid >> 5) * 4 + k] = u[k];
+        }
+        if (tid < 4) s_rng[tid] = (tid & 1) ? -1 : 0x7fffffff;  // lo row, hi row, lo column, hi column
+        const bool any_open = __syncthreads_or(open_box);
+#pragma unroll
+        for (int w = 0; w < T / 32; ++w) {
+            u[0] = fminf(u[0], s_box[w * 4 + 0]);
+            u[1] = fmaxf(u[1], s_box[w * 4 + 1]);
+            u[2] = fminf(u[2], s_box[w * 4 + 2]);
+            u[3] = fmaxf(u[3], s_box[w * 4 + 3]);
+        }
+        if (!any_open) {
+            const float* rec0 = a.prec + (long long)b * a.nrp * a.ncb * RS;
+            int lo = 0x7fffffff, hi = -1;
+            for (int rp = rp_begin + tid; rp < rp_end; rp += T) {
+                const float4 yr = reinterpret_cast<const float4*>(rec0 + (long long)rp * a.ncb * RS)[1];
+                if (!(u[3] < fminf(yr.x, yr.y) || u[2] > fmaxf(yr.x, yr.y))) {
+                    lo = min(lo, rp);
+                    hi = max(hi, rp);
+                }
+            }
+            int clo = 0x7fffffff, chi = -1;
+            for (int cb = tid; cb < a.ncb; cb += T) {
+                const float4 xc = reinterpret_cast<const float4*>(rec0 + (long long)cb * RS)[0];
+                if (!(u[1] < xc.x || u[0] > xc.w)) {
+                    clo = min(clo, cb);
+                    chi = max(chi, cb);
+                }
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+                hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+                clo = min(clo, __shfl_xor_sync(0xffffffffu, clo, d));
+                chi = max(chi, __shfl_xor_sync(0xffffffffu, chi, d));
+            }
+            if ((tid & 31) == 0) {
+                atomicMin(&s_rng[0], lo);
+                atomicMax(&s_rng[1], hi);
+                atomicMin(&s_rng[2], clo);
+                atomicMax(&s_rng[3], chi);
+            }
+            __syncthreads();
+            lo = s_rng[0], hi = s_rng[1], clo = s_rng[2], chi = s_rng[3];
+            if (hi < lo || chi < clo) {
+                n_rp = 0;  // nothing of this slab is reached: the sums stay zero
+            } else {
+                rp0 = lo;
+                n_rp = hi - lo + 1;
+                cb0 = clo;
+                seg_c = chi - clo + 1;
+            }
+        }
+    }
+    const int seg = CULL ? seg_c : a.ncb;  // column blocks per row pair in the stream
+    const long long blk_begin = CULL ? (long long)rp0 * a.ncb + cb0 : (long long)rp_begin * a.ncb;
+    const int n_total = CULL ? n_rp * seg : (rp_end - rp_begin) * a.ncb;
     const int n_chunks = (n_total + PCB - 1) / PCB;
     const float* src = a.prec + ((long long)b * a.nrp * a.ncb + blk_begin) * RS;
 
@@ -220,7 +314,21 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         const int cnt = min(PCB, n_total - chunk * PCB);
         const uint32_t bytes = (uint32_t)cnt * RS * sizeof(float);
         mbar_expect_tx(&bars[st], bytes);
-        bulk_g2s(stage_base + (size_t)st * PCB * RS, src + (long long)chunk * PCB * RS, bytes, &bars[st]);
+        if constexpr (!CULL) {
+            bulk_g2s(stage_base + (size_t)st * PCB * RS, src + (long long)chunk * PCB * RS, bytes, &bars[st]);
+        } else {
+            // the chunk is a run of the virtual stream: one copy per row pair it touches
+            float* dstp = stage_base + (size_t)st * PCB * RS;
+            int v = chunk * PCB, left = cnt;
+            while (left > 0) {
+                const int r = v / seg, c = v - r * seg;
+                const int len = min(left, seg - c);
+                bulk_g2s(dstp, src + ((long long)r * a.ncb + c) * RS, (uint32_t)len * RS * sizeof(float), &bars[st]);
+                dstp += (size_t)len * RS;
+                v += len;
+                left -= len;
+            }
+        }
     };
     if (tid == 0) {
         for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
@@ -281,7 +389,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 }
             }
             if (cull && must == 0) {
-                const int run = min(min(SKIP_RUN, cnt - i), a.ncb - cb);
+                const int run = min(min(SKIP_RUN, cnt - i), seg - cb);
                 const float run_x0 = xc.x, run_x1 = rec[(size_t)(i + run - 1) * (RS / 4)].w;
                 bool need = false;
 #pragma unroll
@@ -290,7 +398,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 if (!__any_sync(0xffffffffu, need)) {
                     i += run;
                     cb += run;
-                    if (cb == a.ncb) {
+                    if (cb == seg) {
                         cb = 0;
                         fold_row_pair();
                     }
@@ -335,7 +443,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 }
             }
             ++i;
-            if (++cb == a.ncb) {
+            if (++cb == seg) {
                 cb = 0;
                 fold_row_pair();
             }

@@ -55,7 +55,10 @@ struct BwdPlan {
 
 int make_chunks(int C, Chunks* out);
 int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p);
-int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p);
+// fine_slabs: the partition used when the caller passes a spatial order (many short slabs, so
+// that the few slabs each gaussian group reaches still fill the machine).  The workspace
+// size covers both partitions.
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs = false);
 
 // Body of igs_forward_sr / igs_forward_cov (kind = ShapeKind).  use_plan, when given,
 // replaces the plan the call would compute itself.
