@@ -353,6 +353,22 @@ def run_b200(args):
                "active": (not args.no_culling) and n_narrow * 8 >= n_local,
                "backward_sort": args.backward_sort,
                "note": "lossless: skipped terms are exact zeros; value counts all B*N*H*W evaluations"}
+    if culling["active"]:
+        # one backward through the library call, with the order the policy would pass, to read
+        # how many (gaussian, pixel) evaluations the culling kernels really did
+        x3, y3 = on_dev["x"][:, 0], on_dev["y"][:, 0]
+        sorted_bwd = args.backward_sort != "off"
+        order = _lib.spatial_order(on_dev["positions"], x3, y3) if sorted_bwd else None
+        _lib.set_backward_sort("off")
+        probe_bwd = _lib.backward("sr", on_dev["positions"], on_dev["scales"], on_dev["rotations"], None,
+                                  on_dev["alphas"], on_dev["colors"], x3, y3, probe_fwd[1], probe_fwd[0],
+                                  torch.ones_like(probe_fwd[0]), 1e-6, 0, False, keep_workspace=True, order=order)
+        _lib.set_backward_sort(args.backward_sort)
+        dense = n_local * cfg.H * cfg.W
+        ex_f, ex_b = _lib.read_executed(probe_fwd[2]), _lib.read_executed(probe_bwd["_workspace"])
+        culling["executed_evals"] = {"forward": ex_f or dense, "backward": ex_b or dense, "dense": dense}
+        culling["executed_share"] = {"forward": (ex_f or dense) / dense, "backward": (ex_b or dense) / dense}
+        del probe_bwd
     del probe_fwd
 
     total_ms = torch.tensor([sum(times), sum(e2e_times)], dtype=torch.float64, device=dev)
@@ -387,6 +403,14 @@ def run_b200(args):
         instr = {"forward": 9 + C, "backward": 18 + 2 * C}
         suffix = "_sep" if separable else ""
 
+        share = culling.get("executed_share", {"forward": 1.0, "backward": 1.0})
+        if culling["active"]:
+            # the headline counts all B*N*H*W evaluations; this is the rate of those really done
+            # (forward and backward weighted by their canonical instruction counts)
+            w = (share["forward"] * (9 + C) + share["backward"] * (18 + 2 * C)) / (27 + 3 * C)
+            culling["executed_evals_per_s"] = value * w
+            culling["culled_share"] = 1.0 - w
+
         def kernel_roof(name):
             ms, n = prof[name]
             if n == 0:
@@ -400,10 +424,9 @@ def run_b200(args):
                     "launch_ms": ms / steps, "launches": n,
                     "algorithmic_instr_per_eval": instr[name],
                     "executed_instr_per_eval": executed[name],
-                    # with culling active an unknown share of the evaluations is skipped as exact
-                    # zeros, so the issue count is not known and no utilisation is claimed
-                    "executed_frac": None if culling["active"]
-                    else ev_rank * executed[name] / per_pass_s / fp32_peak,
+                    # with culling active only the evaluations the kernel did not skip are issued
+                    # (the culling kernels count them)
+                    "executed_frac": ev_rank * share[name] * executed[name] / per_pass_s / fp32_peak,
                     "mix_ceiling_frac": None if separable else mix_ceiling[name] / fp32_peak,
                     "grid": "separable (xy_grid), detected on the device" if separable else "general",
                     "peak_source": "measured live: FFMA-only kernel, best of scalar and f32x2 (igs_probe_fp32_rate)",
@@ -435,8 +458,9 @@ def run_b200(args):
                               "unit": "T lane-instr/s", "frac": step_ach / fp32_peak,
                               "algorithmic_instr_per_eval": 27 + 3 * C,
                               "executed_instr_per_eval": executed["forward"] + executed["backward"],
-                              "executed_frac": None if culling["active"] else step_ach / fp32_peak
-                              * (executed["forward"] + executed["backward"]) / (27 + 3 * C),
+                              "executed_frac": step_ach / fp32_peak * (share["forward"] * executed["forward"]
+                                                                       + share["backward"] * executed["backward"])
+                              / (27 + 3 * C),
                               "nominal_peak": n_sm * 128 * (sm or 0) * 1e6 / 1e12 if sm else None},
             "probes": probes,
             "hbm": {"algorithmic_bytes_per_step": hbm_bytes,

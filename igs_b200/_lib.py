@@ -45,6 +45,7 @@ SIGNATURES = {
     "igs_spatial_order_workspace_bytes": (_sz, [_i, _i]),
     "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
     "igs_read_narrow_count": (_i, [_vp, _i, _vp, _vp]),
+    "igs_read_executed": (_i, [_vp, _i, _vp, ctypes.POINTER(ctypes.c_ulonglong)]),
     "igs_profile_enable": (_i, [_i]),
     "igs_profile_reset": (_i, []),
     "igs_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
@@ -143,6 +144,15 @@ def read_status(ws: torch.Tensor) -> int:
     rc = load().igs_read_status(_ptr(ws), ws.device.index, _stream(ws.device), ctypes.byref(host))
     if rc not in (0, -5):
         check("igs_read_status", rc)
+    return int(host.value)
+
+
+def read_executed(ws: torch.Tensor) -> int:
+    """(gaussian, pixel) evaluations the culling kernel of the last call on ws did not skip;
+    0 when the plain kernel ran."""
+    host = ctypes.c_ulonglong(0)
+    check("igs_read_executed", load().igs_read_executed(_ptr(ws), ws.device.index, _stream(ws.device),
+                                                         ctypes.byref(host)))
     return int(host.value)
 
 

@@ -317,7 +317,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     }
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
-    cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(int), st);
+    cudaError_t e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
     if (e != cudaSuccess) return (int)e;
 
     const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
@@ -374,6 +374,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
             // the separable kernel comes as a plain and a culling instantiation; both are
             // launched and the count of narrow gaussians picks one (the other returns at once)
             fa.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
+            fa.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
             e = launch_forward_chunk(p.ch.ct[k], true, false, fa, p, st);
             if (e != cudaSuccess) return (int)e;
             if (fa.cull_sel) {
@@ -449,7 +450,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     if (rc) return rc;
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
-    e = cudaMemsetAsync(ws, 0, sizeof(int), st);
+    e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
     if (e != cudaSuccess) return (int)e;
 
     const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
@@ -520,6 +521,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
         ba.grid_word = grid_flag;
         ba.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
+        ba.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
         ba.pairs_per_slab = p.pairs_per_slab;
         ba.B = B; ba.N = N; ba.C = C;
         ba.c0 = p.ch.c0[k];
@@ -753,6 +755,19 @@ int igs_read_status(const void* workspace, int device, void* stream, int* host_s
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     return *host_status ? IGS_ERR_STATUS : IGS_OK;
+}
+
+int igs_read_executed(const void* workspace, int device, void* stream, unsigned long long* host_count) {
+    if (!workspace || !host_count) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(host_count, reinterpret_cast<const unsigned long long*>(workspace) + EXEC_COUNT_WORD / 2,
+                                    sizeof(unsigned long long), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return (int)e;
 }
 
 int igs_read_narrow_count(const void* workspace, int device, void* stream, int* host_count) {

@@ -34,6 +34,7 @@ struct BwdArgs {
     // Selection on the device (nullptr = run unconditionally): a kernel returns at once
     // unless the word picks it.
     const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable kernel
+    unsigned long long* exec_count;  // skipping kernel: evaluations it did not skip (may be null)
     const int* cull_sel;   // count of narrow gaussians: at least one in eight (and monotone axes,
     const int* grid_word;  //   bit 1 of the grid word clear) -> skipping / plain separable kernel
     long long npairs, pairs_per_slab;

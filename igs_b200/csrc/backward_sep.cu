@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
     constexpr bool cull = CULL;
     float strip_y0 = 0.f, strip_y1 = 0.f;
     int must = 0;  // blocks of the current run still to be processed without voting again
+    int visited = 0;  // blocks this warp did not skip (counted by the skipping kernel only)
 
     // totals: M0, Mx, My, Mxx, Mxy, Myy, E_c;  row-pair state: per row r of the pair
     f2 M[GPT][N_MOMENTS], E[GPT][CT];
@@ -406,7 +407,10 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 }
                 must = run;
             }
-            if (cull) --must;
+            if (cull) {
+                --must;
+                ++visited;
+            }
             f2 dxc[GPT][2], adx[GPT][2];
 #pragma unroll
             for (int g = 0; g < GPT; ++g)
@@ -450,6 +454,11 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
         }
         __syncthreads();
         if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+    }
+
+    if constexpr (CULL) {
+        // a visited block is 8 pixels against the GPT gaussians of each of the warp's 32 lanes
+        if ((tid & 31) == 0 && a.exec_count) atomicAdd(a.exec_count, (unsigned long long)visited * (8 * 32 * GPT));
     }
 
 #pragma unroll

@@ -37,6 +37,7 @@ constexpr float CULL_T = 130.0f;
 constexpr int STATUS_WORD = 0;       // kernels: a bounded wait gave up
 constexpr int GRID_FLAG_WORD = 1;    // grid check: bit 0 = not separable, bit 1 = axes not monotone
 constexpr int NARROW_COUNT_WORD = 2; // pack: gaussians whose reach is well inside the image
+constexpr int EXEC_COUNT_WORD = 4;   // (64 bits) culling kernels: (gaussian, pixel) evaluations not skipped
 constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2;
 
 // Backward pixel record, one per PAIR of consecutive pixels and channel chunk:

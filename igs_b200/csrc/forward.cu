@@ -201,6 +201,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
         for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
     }
 
+    int evaluated = 0;  // gaussians this CTA did not skip (counted by the culling kernel only)
     for (int chunk = 0; chunk < n_chunks; ++chunk) {
         const int st = chunk % NS;
         const uint32_t parity = (chunk / NS) & 1;
@@ -263,6 +264,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
             }
         };
         if (!CULL || !cull) {
+            if constexpr (CULL) evaluated += cnt;
 #pragma unroll(Cfg::UNROLL)
             for (int g = 0; g < cnt; ++g) splat(g);
         } else {
@@ -285,11 +287,17 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
             }
             if (keep) s_list[base + __popc(ballot & ((1u << (tid & 31)) - 1u))] = (unsigned short)tid;
             __syncthreads();
+            evaluated += n_keep;
 #pragma unroll(Cfg::UNROLL)
             for (int i = 0; i < n_keep; ++i) splat(s_list[i]);
         }
         __syncthreads();  // every lane is done with this stage
         if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+    }
+
+    if constexpr (CULL) {
+        // every thread of the CTA evaluated its pixels (padding included) against each kept gaussian
+        if (tid == 0 && a.exec_count) atomicAdd(a.exec_count, (unsigned long long)evaluated * (T * 2 * NP));
     }
 
     // ---- epilogue ----

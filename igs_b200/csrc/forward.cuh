@@ -18,6 +18,7 @@ struct FwdArgs {
     // once unless the word picks it.
     const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable
     const int* cull_sel;   // count of narrow gaussians: at least one in eight -> culling / plain
+    unsigned long long* exec_count;  // culling kernel: evaluations it did not skip (may be null)
     int tiles_x;           // separable tiling: CTAs per tile row
     int B, N, H, W, C;
     int c0, cr;  // first channel and real channel count of this chunk

@@ -8,7 +8,7 @@
 // most runs are.  The gradients do not depend on the order, bit for bit: each gaussian's
 // sums are taken over the same pixels in the same sequence whichever thread owns it.
 //
-// How.  A counting sort on the Morton code of the gaussian's cell in a 64 x 64 lattice laid
+// How.  A counting sort on the Hilbert-curve index of the gaussian's cell in a 64 x 64 lattice laid
 // over the sampled extent (first row of x, first column of y): count per cell, exclusive
 // scan per batch element, scatter through an atomic cursor per cell.  The order inside a
 // cell is whatever the atomics give, and may differ from run to run; it is a permutation
@@ -18,7 +18,7 @@
 namespace igs {
 
 constexpr int ORDER_CELLS_1D = 64;
-constexpr int ORDER_CELLS = ORDER_CELLS_1D * ORDER_CELLS_1D;  // 4096 Morton codes
+constexpr int ORDER_CELLS = ORDER_CELLS_1D * ORDER_CELLS_1D;  // 4096 curve positions
 constexpr int ORDER_SCAN_THREADS = 1024;
 
 struct OrderArgs {
@@ -32,11 +32,27 @@ struct OrderArgs {
     int B, N, H, W;
 };
 
-__device__ __forceinline__ unsigned spread6(unsigned v) {  // abcdef -> 0a0b0c0d0e0f
-    v = (v | (v << 4)) & 0x30Fu;
-    v = (v | (v << 2)) & 0x333u;
-    v = (v | (v << 1)) & 0x555u;
-    return v;
+// Position of cell (x, y) along the Hilbert curve through the lattice.  Consecutive
+// positions are adjacent cells, so ANY run of consecutive gaussians (a warp's, a CTA's)
+// stays compact; the Morton order jumps across the image wherever a run straddles a
+// quadrant boundary.
+__device__ __forceinline__ unsigned hilbert_index(unsigned x, unsigned y) {
+    unsigned d = 0;
+#pragma unroll
+    for (unsigned s = ORDER_CELLS_1D / 2; s > 0; s >>= 1) {
+        const unsigned rx = (x & s) ? 1u : 0u, ry = (y & s) ? 1u : 0u;
+        d += s * s * ((3u * rx) ^ ry);
+        if (ry == 0) {  // rotate the quadrant so that the sub-curve enters and leaves at the right corners
+            if (rx == 1) {
+                x = (ORDER_CELLS_1D - 1) - x;
+                y = (ORDER_CELLS_1D - 1) - y;
+            }
+            const unsigned t = x;
+            x = y;
+            y = t;
+        }
+    }
+    return d;
 }
 
 __device__ __forceinline__ int cell_of(float p, float e0, float e1) {
@@ -54,7 +70,7 @@ __global__ void __launch_bounds__(256) order_count_kernel(OrderArgs a) {
     const float x0 = a.x[b * a.xs_b], x1 = a.x[b * a.xs_b + (long long)(a.W - 1) * a.xs_w];
     const float y0 = a.y[b * a.ys_b], y1 = a.y[b * a.ys_b + (long long)(a.H - 1) * a.ys_h];
     const int cx = cell_of(a.pos[2 * i], x0, x1), cy = cell_of(a.pos[2 * i + 1], y0, y1);
-    const unsigned key = spread6((unsigned)cx) | (spread6((unsigned)cy) << 1);
+    const unsigned key = hilbert_index((unsigned)cx, (unsigned)cy);
     a.keys[i] = (unsigned short)key;
     atomicAdd(a.hist + b * ORDER_CELLS + key, 1);
 }

@@ -127,9 +127,13 @@ int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, floa
  *   modified (the reference divides it in place, :371).
  *   d_x, d_y [B,H,W] contiguous, both NULL to skip (src/igs/gs2d.py:433-434).
  *   order: NULL, or a permutation [B,N] (int32) of each batch element's gaussians giving
- *   the order in which threads take them.  Results do not depend on it, bit for bit; a
- *   spatial order (neighbours adjacent) lets whole warps skip pixel runs none of their
- *   gaussians reach, which is where the culling of the backward gets its speed.
+ *   the order in which threads take them (igs_spatial_order makes a good one).  In a
+ *   spatial order the gaussians of a CTA share a patch of the image, and the skipping
+ *   kernel visits only the pixels that patch reaches.  Passing an order also selects a
+ *   finer partition of the rows into slabs (fixed by the shape), so that the few slabs
+ *   a patch touches still fill the GPU.  The gradients do not depend on WHICH permutation
+ *   is passed, bit for bit; against order == NULL they agree to fp32 rounding (the
+ *   per-slab sums associate differently).
  */
 int igs_backward_sr(const float* positions, const float* scales, const float* rotations,
                     const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
@@ -177,7 +181,7 @@ int igs_set_culling(int on);
 
 /*
  * A spatial order for the `order` argument of igs_backward_*: order[b, slot] = index of
- * the gaussian taken in that slot, neighbours in the image next to each other (Morton
+ * the gaussian taken in that slot, neighbours in the image next to each other (Hilbert-curve
  * order of a 64 x 64 lattice over the sampled extent; x, y and their strides as for the
  * forward, only the first row of x and the first column of y are read).  Worth computing
  * when most gaussians are narrow (igs_read_narrow_count) and the grid is separable: the
@@ -201,6 +205,14 @@ int igs_spatial_order(const float* positions, const float* x, const int64_t* x_s
  * spatial order pays.
  */
 int igs_read_narrow_count(const void* workspace, int device, void* stream, int* host_count);
+
+/*
+ * For reports: the number of (gaussian, pixel) evaluations the culling kernel of the last
+ * forward or backward on this workspace did NOT skip (tile padding included), or 0 when
+ * the plain kernel ran (it evaluates all B*N*H*W).  With several channel chunks the count
+ * covers all of them.  Copies to *host_count (HOST pointer) and waits for the stream.
+ */
+int igs_read_executed(const void* workspace, int device, void* stream, unsigned long long* host_count);
 
 /*
  * Per-kernel device timing for reports.  While enabled, every kernel launch of the
