@@ -418,9 +418,12 @@ def run_b200(args):
             # device time of this kernel per pass (with the on-device grid check, the
             # instantiation that does not match returns at once; its launch is included)
             per_pass_s = ms / steps * 1e-3
-            ach = ev_rank * instr[name] / per_pass_s
+            # evaluations really done: all of them, or what the culling kernel reports it kept
+            ach = ev_rank * share[name] * instr[name] / per_pass_s
             return {"bound": "fp32_fma_pipe", "kernel": f"splat_{name}{suffix}_kernel", "achieved": ach / 1e12,
                     "peak": fp32_peak / 1e12, "unit": "T lane-instr/s", "frac": ach / fp32_peak,
+                    "evaluations_counted": "all B*N*H*W" if share[name] == 1.0 else
+                    f"executed only: {100 * share[name]:.2f} % of B*N*H*W (the rest are exact zeros, skipped)",
                     "launch_ms": ms / steps, "launches": n,
                     "algorithmic_instr_per_eval": instr[name],
                     "executed_instr_per_eval": executed[name],
@@ -434,7 +437,8 @@ def run_b200(args):
 
         roof = kernel_roof("backward")
         roof_f = kernel_roof("forward")
-        step_ach = ev_rank * (27 + 3 * C) / (statistics.mean(times) * 1e-3)
+        step_ach = ev_rank * (share["forward"] * (9 + C) + share["backward"] * (18 + 2 * C)) \
+            / (statistics.mean(times) * 1e-3)
         hbm_bytes = (2 * cfg.B * cfg.N * (6 + C) * 4 + 2 * cfg.B * cfg.H * cfg.W * 4 + cfg.B * (C + 1) * cfg.H * cfg.W * 4
                      + cfg.B * (2 * C + 3) * cfg.H * cfg.W * 4 + cfg.B * cfg.N * (6 + C) * 4)
         peaks = {}
@@ -460,7 +464,7 @@ def run_b200(args):
                               "executed_instr_per_eval": executed["forward"] + executed["backward"],
                               "executed_frac": step_ach / fp32_peak * (share["forward"] * executed["forward"]
                                                                        + share["backward"] * executed["backward"])
-                              / (27 + 3 * C),
+                              / (share["forward"] * (9 + C) + share["backward"] * (18 + 2 * C)),
                               "nominal_peak": n_sm * 128 * (sm or 0) * 1e6 / 1e12 if sm else None},
             "probes": probes,
             "hbm": {"algorithmic_bytes_per_step": hbm_bytes,
