@@ -188,7 +188,10 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     // depend on whether an order was passed but not on the order or on the gaussians.
     int ns_fine = ns;
     if (p->sep_ok) {
-        const int want = (p->nrp + 7) / 8;
+#ifndef IGS_FINE_RP
+#define IGS_FINE_RP 8
+#endif
+        const int want = (p->nrp + IGS_FINE_RP - 1) / IGS_FINE_RP;
         ns_fine = want < 96 ? want : 96;
         if (ns_fine < ns) ns_fine = ns;
     }
@@ -533,7 +536,10 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
             e = launch_backward_chunk(p.ch.ct[k], true, false, ba, p, st);
             if (e != cudaSuccess) return (int)e;
             if (ba.cull_sel) {
-                e = launch_backward_chunk(p.ch.ct[k], true, true, ba, p, st);
+                // the skipping kernel: with a processing order, the one whose warps each follow
+                // their own gaussians' reach; without, the one that skips per CTA
+                e = order ? launch_backward_warp_chunk(p.ch.ct[k], ba, p, st)
+                          : launch_backward_chunk(p.ch.ct[k], true, true, ba, p, st);
                 if (e != cudaSuccess) return (int)e;
             }
         }

@@ -87,6 +87,7 @@ cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const Bw
 bool backward_has_separable(int ct);
 cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
 cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
 cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
 
