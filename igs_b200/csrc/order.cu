@@ -1,12 +1,14 @@
 // igs_spatial_order: a permutation of each batch element's gaussians that puts spatial
 // neighbours next to each other, for the `order` argument of igs_backward_*.
 //
-// Why.  The separable backward kernel gives each thread two gaussians and walks all pixel
-// blocks; with culling a warp skips a run of blocks when none of its 64 gaussians reaches
-// it.  Gaussians in arbitrary order leave every warp with gaussians all over the image, so
-// almost no run is skipped; in spatial order a warp's gaussians share a small patch and
-// most runs are.  The gradients do not depend on the order, bit for bit: each gaussian's
-// sums are taken over the same pixels in the same sequence whichever thread owns it.
+// Why.  With narrow gaussians the backward can skip every pixel outside a gaussian's
+// zero-weight box, but it skips per warp: the kernel for ordered calls
+// (backward_warp.cu) gives each thread one gaussian and lets a warp stream only the
+// rectangle of pixel blocks the box around its 32 gaussians meets.  Gaussians in arbitrary
+// order leave every warp with gaussians all over the image and nothing to skip; in spatial
+// order a warp's gaussians share a small patch.  The gradients do not depend on the order,
+// bit for bit: each gaussian's sums are taken over the same pixels in the same sequence
+// whichever thread owns it.
 //
 // How.  A counting sort on the Hilbert-curve index of the gaussian's cell in a 64 x 64 lattice laid
 // over the sampled extent (first row of x, first column of y): count per cell, exclusive

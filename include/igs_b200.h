@@ -128,8 +128,8 @@ int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, floa
  *   d_x, d_y [B,H,W] contiguous, both NULL to skip (src/igs/gs2d.py:433-434).
  *   order: NULL, or a permutation [B,N] (int32) of each batch element's gaussians giving
  *   the order in which threads take them (igs_spatial_order makes a good one).  In a
- *   spatial order the gaussians of a CTA share a patch of the image, and the skipping
- *   kernel visits only the pixels that patch reaches.  Passing an order also selects a
+ *   spatial order the 32 gaussians of a warp share a patch of the image, and the skipping
+ *   kernel lets each warp visit only the pixels its patch reaches.  Passing an order also selects a
  *   finer partition of the rows into slabs (fixed by the shape), so that the few slabs
  *   a patch touches still fill the GPU.  The gradients do not depend on WHICH permutation
  *   is passed, bit for bit; against order == NULL they agree to fp32 rounding (the

@@ -122,7 +122,7 @@ def test_spatial_order_is_a_permutation_with_neighbours_adjacent():
     order = _lib.spatial_order(d["positions"], x[:, 0], y[:, 0])
     assert order.dtype == torch.int32 and order.shape == (B, N)
     assert torch.equal(order.long().sort(dim=1).values, torch.arange(N, device=dev).expand(B, N))
-    # a run of 64 consecutive slots (one warp's gaussians) spans a small patch, not the image
+    # a run of 64 consecutive slots (two warps' gaussians) spans a small patch, not the image
     p = torch.gather(d["positions"], 1, order.long()[..., None].expand(B, N, 2))
     runs = p[:, : N // 64 * 64].reshape(B, -1, 64, 2)
     span = (runs.amax(2) - runs.amin(2)).amax(-1)  # [B, runs]: larger side of the run's box
@@ -172,7 +172,7 @@ def test_processing_order_changes_no_bit(kind):
 @pytest.mark.parametrize("C", [1, 2, 3, 4])
 def test_culling_changes_no_bit_with_an_order(C):
     """With an order the skipping is done warp by warp (each warp follows the reach of its
-    own 64 gaussians); against the dense kernel on the same row partition: same bits.  A
+    own 32 gaussians); against the dense kernel on the same row partition: same bits.  A
     few image-wide and one indefinite gaussian (infinite box) are mixed in."""
     from igs_b200 import _lib
 
