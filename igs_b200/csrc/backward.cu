@@ -106,6 +106,9 @@ cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStrea
 #ifndef IGS_BWD_GPT
 #define IGS_BWD_GPT 2
 #endif
+#ifndef IGS_BWD_GPT_16  // gaussians per thread in the 16-channel instantiation (165 registers,
+#define IGS_BWD_GPT_16 2  // 12 warps per SM: 248.8 ms against 254.7 ms with one, B=8 N=65536 512x512)
+#endif
 
 template <int CT, int GPT>
 struct BwdCfg {
@@ -121,7 +124,7 @@ struct BwdCfg {
 #ifdef IGS_BWD_UNROLL
     static constexpr int UNROLL = IGS_BWD_UNROLL;
 #else
-    static constexpr int UNROLL = GPT >= 2 ? 4 : 2;
+    static constexpr int UNROLL = CT > 4 ? (GPT >= 2 ? 1 : 2) : (GPT >= 2 ? 4 : 2);
 #endif
     static constexpr bool TWO_LEVEL = (CT <= 4 && GPT == 1);
     static constexpr int RS = bwd_rec_floats(CT);
@@ -316,7 +319,7 @@ cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const Bw
         case 3: return two ? launch_one<3, IGS_BWD_GPT>(a, p, s) : launch_one<3, 1>(a, p, s);
         case 4: return two ? launch_one<4, IGS_BWD_GPT>(a, p, s) : launch_one<4, 1>(a, p, s);
         case 8: return launch_one<8, 1>(a, p, s);
-        case 16: return launch_one<16, 1>(a, p, s);
+        case 16: return launch_one<16, IGS_BWD_GPT_16>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -339,7 +342,7 @@ static int occ(int device) {
 }
 
 // two gaussians per thread where the registers allow it (up to 4 channels per chunk)
-int backward_gauss_per_thread(int ct) { return ct > 4 ? 1 : IGS_BWD_GPT; }
+int backward_gauss_per_thread(int ct) { return ct > 8 ? IGS_BWD_GPT_16 : (ct > 4 ? 1 : IGS_BWD_GPT); }
 
 int backward_ctas_per_sm(int ct, int device) {
     const bool two = backward_gauss_per_thread(ct) >= 2;
@@ -349,7 +352,7 @@ int backward_ctas_per_sm(int ct, int device) {
         case 3: return two ? occ<3, IGS_BWD_GPT>(device) : occ<3, 1>(device);
         case 4: return two ? occ<4, IGS_BWD_GPT>(device) : occ<4, 1>(device);
         case 8: return occ<8, 1>(device);
-        default: return occ<16, 1>(device);
+        default: return occ<16, IGS_BWD_GPT_16>(device);
     }
 }
 int backward_threads(int) { return 128; }
