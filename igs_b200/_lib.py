@@ -46,6 +46,8 @@ SIGNATURES = {
     "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
     "igs_read_narrow_count": (_i, [_vp, _i, _vp, _vp]),
     "igs_read_executed": (_i, [_vp, _i, _vp, ctypes.POINTER(ctypes.c_ulonglong)]),
+    "igs_mse_loss": (_i, [_vp, _vp, ctypes.c_longlong, _vp, _vp, _sz, _i, _vp]),
+    "igs_mse_grad": (_i, [_vp, _vp, ctypes.c_longlong, _vp, _vp, _i, _vp]),
     "igs_profile_enable": (_i, [_i]),
     "igs_profile_reset": (_i, []),
     "igs_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
@@ -306,6 +308,28 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     if keep_workspace:
         res["_workspace"] = ws
     return res
+
+
+MSE_WORKSPACE_BYTES = 4096
+
+
+def mse_loss(out: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    """mean((out - target)^2) as a device scalar; both contiguous fp32 of one shape."""
+    dev = out.device
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    ws = _workspace(MSE_WORKSPACE_BYTES, dev)
+    check("igs_mse_loss", load().igs_mse_loss(_ptr(out), _ptr(target), out.numel(), _ptr(loss), _ptr(ws), ws.numel(),
+                                              dev.index, _stream(dev)))
+    return loss
+
+
+def mse_grad(out: torch.Tensor, target: torch.Tensor, upstream: torch.Tensor | None) -> torch.Tensor:
+    """upstream * 2 (out - target) / n, shaped like out; upstream a device scalar or None."""
+    dev = out.device
+    gout = torch.empty_like(out)
+    check("igs_mse_grad", load().igs_mse_grad(_ptr(out), _ptr(target), out.numel(), _ptr(upstream), _ptr(gout),
+                                              dev.index, _stream(dev)))
+    return gout
 
 
 KERNEL_NAMES = ("pack", "forward", "reduce_normalize", "pixel_terms", "backward", "finalize", "coord_grad", "grid_check")

@@ -215,6 +215,22 @@ int igs_read_narrow_count(const void* workspace, int device, void* stream, int* 
 int igs_read_executed(const void* workspace, int device, void* stream, unsigned long long* host_count);
 
 /*
+ * The L2 loss behind the renderer in the reference's fit scripts
+ * (F.mse_loss(rendered_image, target_image), scripts/2dgs_img_comp.py:135,
+ * scripts/gs2d_test.py:56), as two calls so that a host-side autograd can hand the
+ * upstream scalar to the second:
+ *   igs_mse_loss: *loss (device scalar) = mean((out - target)^2) over n elements;
+ *   igs_mse_grad: gout[i] = upstream * 2 (out[i] - target[i]) / n, upstream a device
+ *                 scalar or NULL for 1.
+ * No atomics: the loss is repeatable to the bit.  workspace: IGS_MSE_WORKSPACE_BYTES.
+ */
+#define IGS_MSE_WORKSPACE_BYTES 4096
+int igs_mse_loss(const float* out, const float* target, long long n, float* loss, void* workspace,
+                 size_t workspace_bytes, int device, void* stream);
+int igs_mse_grad(const float* out, const float* target, long long n, const float* upstream, float* gout,
+                 int device, void* stream);
+
+/*
  * Per-kernel device timing for reports.  While enabled, every kernel launch of the
  * library is bracketed by CUDA events recorded on the launch's own stream;
  * igs_profile_read waits for the recorded events and returns the accumulated device

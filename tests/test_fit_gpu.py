@@ -46,3 +46,35 @@ def test_fit_resolution_schedule():
     assert hist[69] < hist[0] and hist[-1] < hist[0]
     out = model((128, 128))
     assert out.shape == (1, 3, 128, 128)
+
+
+@pytest.mark.parametrize("shape", [(1, 3, 64, 80), (2, 16, 33, 7), (1, 1, 1, 1), (1, 3, 1024, 1024)])
+def test_library_mse_matches_torch(shape):
+    """The loss kernels behind fit(): value and gradient of F.mse_loss, with an upstream
+    scalar other than one, and the same bits on every call."""
+    from igs_b200 import fit
+
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(sum(shape))
+    out = torch.rand(shape, generator=gen).to(dev).requires_grad_()
+    tgt = torch.rand(shape, generator=gen).to(dev)
+    loss = fit.mse_loss(out, tgt)
+    (loss * 3.0).backward()
+    ref_out = out.detach().clone().requires_grad_()
+    ref = torch.nn.functional.mse_loss(ref_out, tgt)
+    (ref * 3.0).backward()
+    assert loss.shape == () and abs(float(loss) - float(ref)) <= 1e-6 * max(1.0, abs(float(ref)))
+    assert torch.allclose(out.grad, ref_out.grad, rtol=1e-6, atol=1e-12)
+    assert torch.equal(fit.mse_loss(out.detach(), tgt), loss.detach())
+
+
+def test_mse_falls_back_to_torch_for_what_the_kernels_do_not_take():
+    from igs_b200 import fit
+
+    dev = torch.device("cuda", 0)
+    out = torch.rand(1, 3, 8, 8, device=dev).transpose(2, 3).requires_grad_()  # not contiguous
+    tgt = torch.rand(1, 3, 8, 8, device=dev)
+    loss = fit.mse_loss(out, tgt)
+    loss.backward()
+    assert torch.allclose(loss, torch.nn.functional.mse_loss(out.detach(), tgt))
+    assert out.grad is not None
