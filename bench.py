@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_b8", "cfg4", "narrow"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_b8", "cfg4", "narrow", "narrow64k"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-culling", action="store_true", help="switch the lossless culling off (for comparison)")

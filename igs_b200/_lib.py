@@ -40,6 +40,9 @@ SIGNATURES = {
     "igs_normalize": (_i, [_vp] + [_i] * 4 + [_f, _vp, _vp, _i, _vp]),
     "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
     "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 10 + [_sz, _i, _vp]),
+    "igs_forward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _sz, _i, _vp]),
+    "igs_backward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 3
+                             + [_sz, _i, _vp]),
     "igs_read_status": (_i, [_vp, _i, _vp, ctypes.POINTER(_i)]),
     "igs_set_culling": (_i, [_i]),
     "igs_spatial_order_workspace_bytes": (_sz, [_i, _i]),
@@ -186,6 +189,43 @@ def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, 
     return out, wsum
 
 
+def forward_feature(feat, pos_off, x3, y3, eps):
+    """The forward on the module's projection output feat [B,N,6+C] (contiguous); pos_off
+    [B,N,2] or None.  Returns (out, wsum)."""
+    dev = feat.device
+    B, N, per = feat.shape
+    C = per - 6
+    _, H, W = x3.shape
+    fb, _ = workspace_bytes(B, N, H, W, C, dev)
+    ws = _workspace(fb, dev)
+    out = torch.empty(B, C, H, W, dtype=torch.float32, device=dev)
+    wsum = torch.empty(B, H, W, dtype=torch.float32, device=dev)
+    check("igs_forward_feature",
+          load().igs_forward_feature(_ptr(feat), _ptr(pos_off), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N,
+                                     H, W, C, float(eps), 1, _ptr(out), _ptr(wsum), _ptr(ws), ws.numel(), dev.index,
+                                     _stream(dev)))
+    return out, wsum
+
+
+def backward_feature(feat, pos_off, x3, y3, wsum, out, gout, eps, grad_mode):
+    """Gradient with respect to feat, [B,N,6+C] (the unused column gets zeros)."""
+    dev = feat.device
+    B, N, per = feat.shape
+    C = per - 6
+    _, H, W = x3.shape
+    order, probe = _order_by_policy(None, feat, pos_off, x3, y3, B, N, H, W)
+    _, bb = workspace_bytes(B, N, H, W, C, dev)
+    ws = _workspace(bb, dev)
+    d_feat = torch.empty_like(feat)
+    check("igs_backward_feature",
+          load().igs_backward_feature(_ptr(feat), _ptr(pos_off), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3),
+                                      _ptr(wsum), _ptr(out), _ptr(gout), B, N, H, W, C, float(eps), int(grad_mode),
+                                      _ptr(d_feat), _ptr(order), _ptr(ws), ws.numel(), dev.index, _stream(dev)))
+    if probe is not None:
+        probe.queue(ws)
+    return d_feat
+
+
 def normalize(sums: torch.Tensor, eps: float):
     """sums [B,C+1,H,W] -> (out [B,C,H,W], wsum [B,H,W])."""
     dev = sums.device
@@ -260,6 +300,23 @@ def set_backward_sort(mode: str) -> None:
     _probes.clear()
 
 
+def _order_by_policy(pos, feat, pos_off, x3, y3, B, N, H, W):
+    """(order or None, probe or None) for one backward call under the set_backward_sort
+    policy.  pos [B,N,2] contiguous, or None with feat [B,N,6+C] (+ pos_off) to take the
+    positions from."""
+    if B * N == 0 or _BACKWARD_SORT == "off":
+        return None, None
+    dev = x3.device
+    probe = None
+    if _BACKWARD_SORT == "auto":
+        probe = _probes.setdefault((dev.index, B, N, H, W), _NarrowProbe())
+        if not probe.poll(B * N):
+            return None, probe
+    if pos is None:
+        pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off
+    return spatial_order(pos.contiguous(), x3, y3), probe
+
+
 def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps, grad_mode, want_xy,
              keep_workspace=False, order=None):
     """Returns dict of gradients; d_x / d_y only when want_xy.  order: None = by the
@@ -268,13 +325,8 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     B, N, C = colors.shape
     _, H, W = x3.shape
     probe = None
-    if order is None and B * N > 0:
-        if _BACKWARD_SORT == "on":
-            order = spatial_order(pos, x3, y3)
-        elif _BACKWARD_SORT == "auto":
-            probe = _probes.setdefault((dev.index, B, N, H, W), _NarrowProbe())
-            if probe.poll(B * N):
-                order = spatial_order(pos, x3, y3)
+    if order is None:
+        order, probe = _order_by_policy(pos, None, None, x3, y3, B, N, H, W)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     f32 = dict(dtype=torch.float32, device=dev)

@@ -283,16 +283,29 @@ static void pack_grid_args(PackArgs* pa, unsigned char* ws, const float* x, cons
     pa->B = B; pa->N = N; pa->H = H; pa->W = W;
 }
 
+static ParamLayout layout_or_default(const ParamLayout* layout, int kind, int C) {
+    if (layout) return *layout;
+    ParamLayout l;
+    std::memset(&l, 0, sizeof(l));
+    l.pos_s = 2;
+    l.s0_s = kind == SHAPE_SCALE_ROT ? 2 : 1;
+    l.s1_s = 1;
+    l.col_s = C;
+    return l;
+}
+
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
-                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan) {
+                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan, const ParamLayout* layout) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
     if (B == 0 || HW == 0) return IGS_OK;
     if (!x || !y) return IGS_ERR_ARG;
-    if (N > 0 && (!pos || !s0 || !s1 || !alpha || !colors || (kind == SHAPE_COV_INV && !s2))) return IGS_ERR_ARG;
+    // (only a caller-described layout may leave the opacities out: all ones)
+    if (N > 0 && (!pos || !s0 || !s1 || (!alpha && !layout) || !colors || (kind == SHAPE_COV_INV && !s2)))
+        return IGS_ERR_ARG;
     int rc = check_device(device);
     if (rc) return rc;
     DeviceGuard guard(device);
@@ -339,6 +352,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     pa.alpha = alpha;
     pa.colors = colors;
     pa.geo = nullptr;
+    pa.lay = layout_or_default(layout, kind, C);
     pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
     for (int k = 0; k < p.ch.n; ++k) pa.frec[k] = reinterpret_cast<float*>(ws + p.off_frec[k]);
     pa.ch = p.ch;
@@ -412,16 +426,19 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
                          const int64_t* ys, const float* wsum, const float* out, const float* gout, int B, int N,
                          int H, int W, int C, float eps, int mode, float* d_pos, float* d_s0, float* d_s1,
                          float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, const int* order,
-                         void* workspace, size_t workspace_bytes, int device, void* stream) {
+                         void* workspace, size_t workspace_bytes, int device, void* stream,
+                         const ParamLayout* layout = nullptr) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
+    if (layout && (d_x || d_y)) return IGS_ERR_ARG;  // coordinate gradients: separate tensors only
     if ((d_x == nullptr) != (d_y == nullptr)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
     if (B == 0) return IGS_OK;
     if (HW > 0 && (!x || !y || !wsum || !gout || (mode == IGS_GRAD_EXACT && !out))) return IGS_ERR_ARG;
-    if (N > 0 && (!pos || !s0 || !s1 || !alpha || !colors || !d_pos || !d_s0 || !d_s1 || !d_alpha || !d_colors ||
-                  (kind == SHAPE_COV_INV && (!s2 || !d_s2))))
+    if (N > 0 && (!pos || !s0 || !s1 || !colors || !d_pos || !d_s0 || !d_s1 || !d_colors ||
+                  (!layout && (!alpha || !d_alpha)) || (kind == SHAPE_COV_INV && (!s2 || !d_s2))))
         return IGS_ERR_ARG;
+    if (layout && (N == 0 || HW == 0)) return IGS_ERR_ARG;  // the feature-level wrapper handles these itself
     int rc = check_device(device);
     if (rc) return rc;
     DeviceGuard guard(device);
@@ -472,6 +489,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     pa.alpha = alpha;
     pa.colors = colors;
     pa.geo = reinterpret_cast<float*>(ws + p.off_geo);
+    pa.lay = layout_or_default(layout, kind, C);
     pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
     pa.ch = p.ch;
     pa.M = (long long)B * N;
@@ -526,7 +544,8 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
         ba.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
         ba.pairs_per_slab = p.pairs_per_slab;
-        ba.B = B; ba.N = N; ba.C = C;
+        ba.B = B; ba.N = N;
+        ba.C = pa.lay.col_s;  // the kernels use it as the colours' row stride only
         ba.c0 = p.ch.c0[k];
         ba.cr = p.ch.cr[k];
         ba.planes = p.planes;
@@ -563,6 +582,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     fa.d_shape2 = d_s2;
     fa.d_alpha = d_alpha;
     fa.d_colors = d_colors;
+    fa.lay = pa.lay;
     fa.B = B; fa.N = N; fa.C = C;
     fa.n_slab = p.n_slab;
     fa.planes = p.planes;
@@ -748,6 +768,53 @@ int igs_profile_read(int kernel_id, double* total_ms, long long* launches) {
     if (total_ms) *total_ms = g_total_ms[kernel_id];
     if (launches) *launches = g_timed_launches[kernel_id];
     return IGS_OK;
+}
+
+// The module's projection output as the parameter tensor: row = {x, y, log sx, log sy,
+// rotation, (unused), colours}, opacities all ones.
+static ParamLayout feature_layout(int C, const float* pos_offset, float* d_feature) {
+    ParamLayout l;
+    std::memset(&l, 0, sizeof(l));
+    l.pos_s = l.s0_s = l.s1_s = l.col_s = 6 + C;
+    l.log_scale = 1;
+    l.pos_off = pos_offset;
+    l.d_unused = d_feature ? d_feature + 5 : nullptr;
+    return l;
+}
+
+int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,
+                        const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C, float eps,
+                        int normalize, float* out, float* wsum, void* workspace, size_t workspace_bytes, int device,
+                        void* stream) {
+    if (C < 1) return IGS_ERR_ARG;
+    const ParamLayout l = feature_layout(C, pos_offset, nullptr);
+    return forward_impl(SHAPE_SCALE_ROT, gs_feature, gs_feature ? gs_feature + 2 : nullptr,
+                        gs_feature ? gs_feature + 4 : nullptr, nullptr, nullptr, gs_feature ? gs_feature + 6 : nullptr, x,
+                        x_strides, y, y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes,
+                        device, stream, nullptr, &l);
+}
+
+int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,
+                         const float* y, const int64_t* y_strides, const float* wsum, const float* out,
+                         const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
+                         float* d_feature, const int* order, void* workspace, size_t workspace_bytes, int device,
+                         void* stream) {
+    if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    if (B == 0 || N == 0) return IGS_OK;
+    if (!gs_feature || !d_feature) return IGS_ERR_ARG;
+    if ((long long)H * W == 0) {  // nothing to sum over: every gradient is zero
+        int rc = check_device(device);
+        if (rc) return rc;
+        DeviceGuard guard(device);
+        if (!guard.ok) return IGS_ERR_DEVICE;
+        return (int)cudaMemsetAsync(d_feature, 0, (size_t)B * N * (6 + C) * sizeof(float),
+                                    static_cast<cudaStream_t>(stream));
+    }
+    const ParamLayout l = feature_layout(C, pos_offset, d_feature);
+    return backward_impl(SHAPE_SCALE_ROT, gs_feature, gs_feature + 2, gs_feature + 4, nullptr, nullptr, gs_feature + 6, x,
+                         x_strides, y, y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_feature,
+                         d_feature + 2, d_feature + 4, nullptr, nullptr, d_feature + 6, nullptr, nullptr, order, workspace,
+                         workspace_bytes, device, stream, &l);
 }
 
 int igs_read_status(const void* workspace, int device, void* stream, int* host_status) {

@@ -373,20 +373,27 @@ __global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
 #pragma unroll
             for (int k = 0; k < N_MOMENTS; ++k) M[k] += src[(long long)(q * N_MOMENTS + k) * plane];
     }
-    const float al = a.alpha[i];
+    const ParamLayout& L = a.lay;
+    const float al = a.alpha ? a.alpha[i] : 1.0f;
     for (int c = 0; c < a.C; ++c) {
         float e = 0.f;
         for (int s = 0; s < a.n_slab; ++s)
             e += a.part[(((long long)s * a.B + b) * a.planes + a.n_chunks * N_MOMENTS + c) * plane + n];
-        a.d_colors[i * a.C + c] = al * e;
+        a.d_colors[i * L.col_s + c] = al * e;
     }
     float c00, c01, c11;
     CovInv ci;
-    float sx = 0.f, sy = 0.f;
+    float sx = 0.f, sy = 0.f, ex = 1.f, ey = 1.f;  // ex, ey: d scale / d (what the caller stores)
     if (a.kind == SHAPE_SCALE_ROT) {
-        sx = a.shape0[2 * i];
-        sy = a.shape0[2 * i + 1];
-        ci = cov_inv_from_scale_rot(sx, sy, a.shape1[i], a.eps);
+        sx = a.shape0[(long long)L.s0_s * i];
+        sy = a.shape0[(long long)L.s0_s * i + 1];
+        if (L.log_scale) {
+            ex = expf(sx);
+            ey = expf(sy);
+            sx = ex + a.eps;
+            sy = ey + a.eps;
+        }
+        ci = cov_inv_from_scale_rot(sx, sy, a.shape1[(long long)L.s1_s * i], a.eps);
         c00 = ci.c00;
         c01 = ci.c01;
         c11 = ci.c11;
@@ -395,9 +402,10 @@ __global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
         c01 = a.shape1[i];
         c11 = a.shape2[i];
     }
-    a.d_alpha[i] = M[0];
-    a.d_pos[2 * i] = al * (c00 * M[1] + c01 * M[2]);
-    a.d_pos[2 * i + 1] = al * (c11 * M[2] + c01 * M[1]);
+    if (a.d_alpha) a.d_alpha[i] = M[0];
+    if (L.d_unused) L.d_unused[(long long)L.pos_s * i] = 0.f;
+    a.d_pos[(long long)L.pos_s * i] = al * (c00 * M[1] + c01 * M[2]);
+    a.d_pos[(long long)L.pos_s * i + 1] = al * (c11 * M[2] + c01 * M[1]);
     const float g00 = -0.5f * al * M[3], g01 = -al * M[4], g11 = -0.5f * al * M[5];
     if (a.kind == SHAPE_COV_INV) {
         a.d_shape0[i] = g00;
@@ -411,9 +419,9 @@ __global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
         const float gd = g00 * (id - A_ * D_ * id2) + g01 * (A_ * B_ * id2) + g11 * (-A_ * A_ * id2);
         const float gb = g00 * (2.f * B_ * D_ * id2) + g01 * (-id - 2.f * B_ * B_ * id2) + g11 * (2.f * A_ * B_ * id2);
         const float cs = ci.cs, sn = ci.sn;
-        a.d_shape0[2 * i] = 2.f * sx * (ga * cs * cs + gb * cs * sn + gd * sn * sn);
-        a.d_shape0[2 * i + 1] = 2.f * sy * (ga * sn * sn - gb * cs * sn + gd * cs * cs);
-        a.d_shape1[i] = -2.f * B_ * ga + (cs * cs - sn * sn) * (sx * sx - sy * sy) * gb + 2.f * B_ * gd;
+        a.d_shape0[(long long)L.s0_s * i] = ex * (2.f * sx * (ga * cs * cs + gb * cs * sn + gd * sn * sn));
+        a.d_shape0[(long long)L.s0_s * i + 1] = ey * (2.f * sy * (ga * sn * sn - gb * cs * sn + gd * cs * cs));
+        a.d_shape1[(long long)L.s1_s * i] = -2.f * B_ * ga + (cs * cs - sn * sn) * (sx * sx - sy * sy) * gb + 2.f * B_ * gd;
     }
 }
 

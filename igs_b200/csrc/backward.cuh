@@ -47,17 +47,18 @@ struct BwdArgs {
 };
 
 struct FinalizeArgs {
+    ParamLayout lay;    // strides of the parameter arrays AND of their gradient arrays
     const float* part;  // [n_slab, B, planes, N]
     const float* pos;
     const float* shape0;  // scales | cov_inv_00
     const float* shape1;  // rotations | cov_inv_01
     const float* shape2;  // - | cov_inv_11
-    const float* alpha;
+    const float* alpha;  // or nullptr for all ones
     float* d_pos;     // [B,N,2]
     float* d_shape0;  // d_scales [B,N,2] | d_cov_inv_00 [B,N]
     float* d_shape1;  // d_rotations [B,N] | d_cov_inv_01
     float* d_shape2;  // - | d_cov_inv_11
-    float* d_alpha;   // [B,N]
+    float* d_alpha;   // [B,N], or nullptr
     float* d_colors;  // [B,N,C]
     int B, N, C, n_slab, planes, n_chunks;
     int kind;

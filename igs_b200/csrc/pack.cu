@@ -17,10 +17,20 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     bool narrow = false;
     if (i < a.M) {
-        const float px = a.pos[2 * i], py = a.pos[2 * i + 1];
+        const ParamLayout& L = a.lay;
+        float px = a.pos[(long long)L.pos_s * i], py = a.pos[(long long)L.pos_s * i + 1];
+        if (L.pos_off) {
+            px += L.pos_off[2 * i];
+            py += L.pos_off[2 * i + 1];
+        }
         float c00, c01, c11;
         if (a.kind == SHAPE_SCALE_ROT) {
-            const CovInv ci = cov_inv_from_scale_rot(a.shape0[2 * i], a.shape0[2 * i + 1], a.shape1[i], a.eps);
+            float sx = a.shape0[(long long)L.s0_s * i], sy = a.shape0[(long long)L.s0_s * i + 1];
+            if (L.log_scale) {
+                sx = expf(sx) + a.eps;
+                sy = expf(sy) + a.eps;
+            }
+            const CovInv ci = cov_inv_from_scale_rot(sx, sy, a.shape1[(long long)L.s1_s * i], a.eps);
             c00 = ci.c00;
             c01 = ci.c01;
             c11 = ci.c11;
@@ -30,7 +40,7 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             c11 = a.shape2[i];
         }
         const float A = EXP2_SCALE * c00, B2 = 2.0f * EXP2_SCALE * c01, Cq = EXP2_SCALE * c11;
-        const float al = a.alpha[i];
+        const float al = a.alpha ? a.alpha[i] : 1.0f;
 
         float hx = INFINITY, hy = INFINITY;
         const float D = 4.0f * A * Cq - B2 * B2;
@@ -61,7 +71,7 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             float* r = rec + i * rs;
             r[0] = px; r[1] = py; r[2] = A; r[3] = B2; r[4] = Cq; r[5] = al;
             // colours pre-multiplied by alpha: numerator += e * (alpha * colour)
-            for (int c = 0; c < ct; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * a.C + c0 + c] : 0.f;
+            for (int c = 0; c < ct; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * L.col_s + c0 + c] : 0.f;
             r[6 + ct] = hx;
             r[7 + ct] = hy;
             for (int c = 8 + ct; c < rs; ++c) r[c] = 0.f;

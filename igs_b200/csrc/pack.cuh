@@ -8,11 +8,12 @@ namespace igs {
 enum ShapeKind { SHAPE_SCALE_ROT = 0, SHAPE_COV_INV = 1 };
 
 struct PackArgs {
+    ParamLayout lay;
     const float* pos;     // [M,2]
     const float* shape0;  // scales [M,2]  | cov_inv_00 [M]
     const float* shape1;  // rotations [M] | cov_inv_01 [M]
     const float* shape2;  // unused        | cov_inv_11 [M]
-    const float* alpha;   // [M]
+    const float* alpha;   // [M], or nullptr for all ones
     const float* colors;  // [M,C]
     const float* x;       // sample coordinates (only their extent is read) or nullptr
     const float* y;

@@ -60,12 +60,23 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p);
 // size covers both partitions.
 int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs = false);
 
+// Where the per-gaussian parameters live.  The default is the reference's separate
+// contiguous tensors; the feature-level entry points point all of them into the rows of one
+// [M, 6+C] tensor (the module's projection output) instead.  Strides are in floats.
+struct ParamLayout {
+    int pos_s, s0_s, s1_s, col_s;  // row strides of positions, shape0, shape1, colours
+    int log_scale;                 // shape0 holds log-scales: scale = exp(v) + eps
+    const float* pos_off;          // [M,2] added to the positions, or nullptr
+    float* d_unused;               // backward: a column (row stride pos_s) to fill with zeros, or nullptr
+};
+
 // Body of igs_forward_sr / igs_forward_cov (kind = ShapeKind).  use_plan, when given,
 // replaces the plan the call would compute itself.
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
-                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr);
+                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr,
+                 const ParamLayout* layout = nullptr);
 
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);

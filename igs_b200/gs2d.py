@@ -221,6 +221,48 @@ class _SplatFromScaleRotation(torch.autograd.Function):
         return g["positions"], g["colors"], g["scales"], g["rotations"], g["alphas"], gx, gy, None
 
 
+class _SplatFromFeature(torch.autograd.Function):
+    """What the module runs: the splat fed by the projection output itself.  The split into
+    position / log-scale / rotation / colour, ``exp(log_scale) + eps``, the all-ones
+    opacities and the optional position offset (reference :637-673) happen inside the
+    prologue kernel, and the backward writes the gradient of the whole [B,N,6+C] tensor, so
+    autograd sees one node instead of a dozen small ones."""
+
+    @staticmethod
+    def forward(ctx, gs_feature, pos_offset, x, y, eps):
+        _require_cuda_f32("gs_feature", gs_feature)
+        _require_cuda_f32("x_grid", x)
+        _require_cuda_f32("y_grid", y)
+        _same_device(gs_feature, x, y)
+        if gs_feature.dim() != 3 or gs_feature.shape[-1] < 7:
+            raise ValueError(f"gs_feature must be [B,N,6+C], got {tuple(gs_feature.shape)}")
+        B, N, _ = gs_feature.shape
+        feat = gs_feature.contiguous()
+        off = None
+        if pos_offset is not None:
+            _require_cuda_f32("pos_map", pos_offset)
+            if pos_offset.shape != (B, N, 2):
+                raise ValueError(f"the position offsets must be [B,N,2] = {(B, N, 2)}, got {tuple(pos_offset.shape)}")
+            off = pos_offset.contiguous()
+        x3, y3 = _grid_views(x, y, B)
+        out, wsum = _lib.forward_feature(feat, off, x3, y3, eps)
+        ctx.save_for_backward(x, y, feat, off if off is not None else feat.new_empty(0), wsum, out)
+        ctx.has_off = off is not None
+        ctx.eps = float(eps)
+        ctx.grad_mode = _GRAD_MODES[_grad_mode]
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_result):
+        x, y, feat, off, wsum, out = ctx.saved_tensors
+        x3, y3 = _grid_views(x, y, feat.shape[0])
+        d_feat = _lib.backward_feature(feat, off if ctx.has_off else None, x3, y3, wsum, out,
+                                       grad_result.contiguous(), ctx.eps, ctx.grad_mode)
+        d_off = d_feat[..., :2] if (ctx.has_off and ctx.needs_input_grad[1]) else None
+        return d_feat, d_off, None, None, None
+
+
 # names the reference module also exports (:265, :468-469); one implementation here
 GaussianSplatting2DChunkedKernel = GaussianSplatting2DKernel
 TorchGaussianSplatting2DKernel = GaussianSplatting2DKernel
@@ -304,8 +346,14 @@ class GaussianSplatting2D(nn.Module):
             pos_map = pos_map.flatten(2, 3).transpose(1, 2)
             assert pos_map.size(1) == feature.size(1)
             pos_map = pos_map[..., None, :].repeat(1, 1, self.num_gaussians_per_emb, 1).flatten(1, 2)
-            positions = positions + pos_map
 
+        if fused and not (x_grid.requires_grad or y_grid.requires_grad):
+            # the kernels read the projection output in place (same arithmetic as below)
+            offset = pos_map if self.pos_map_offset else None
+            return _SplatFromFeature.apply(gs_feature, offset, x_grid, y_grid, eps), gs_feature
+
+        if self.pos_map_offset:
+            positions = positions + pos_map
         alphas = torch.ones_like(logit_opacity[..., 0])
         scales = torch.exp(log_scales) + eps
         rotations = rotations[..., 0]

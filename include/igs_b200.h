@@ -158,6 +158,27 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                      int device, void* stream);
 
 /*
+ * The splat driven directly by the module's projection output.  Replaces what
+ * GaussianSplatting2D.forward does between its Linear layer and render
+ * (src/igs/gs2d.py:635-675): split of gs_feature [B,N,6+C] into position (2), log-scale
+ * (2), rotation (1), an unused opacity logit (1) and colours (C); scales = exp(log-scale)
+ * + eps; opacities all ones; optional pos_map offset added to the positions (:655-667).
+ * The forward reads the rows in place; the backward writes d_feature [B,N,6+C] in place
+ * of autograd through split / exp / add (column 5, the unused logit, gets zeros).
+ *   pos_offset: [B,N,2] contiguous or NULL; its gradient equals d_feature[..., 0:2].
+ *   Everything else as igs_forward_sr / igs_backward_sr; no d_x / d_y at this level.
+ */
+int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x,
+                        const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
+                        int H, int W, int C, float eps, int normalize, float* out, float* wsum,
+                        void* workspace, size_t workspace_bytes, int device, void* stream);
+int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x,
+                         const int64_t* x_strides, const float* y, const int64_t* y_strides,
+                         const float* wsum, const float* out, const float* gout, int B, int N, int H,
+                         int W, int C, float eps, int grad_mode, float* d_feature, const int* order,
+                         void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
  * Synchronises `stream`, copies the workspace's status word to *host_status
  * (HOST pointer) and returns IGS_ERR_STATUS if it is non-zero.
  */

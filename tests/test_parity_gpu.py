@@ -377,3 +377,40 @@ def test_headline_identities(headline, dev):
         assert max_err(_np(o12), _np(out + 2 * o2)) <= 1e-5
         unit = gaussian_splatting_2d(*args(torch.ones_like(c2)))
         assert float(unit.max()) <= 1.0 + 1e-6 and float(unit.min()) > 0.99
+
+
+@pytest.mark.parametrize("offset", [False, True])
+def test_feature_level_entry_matches_the_parameter_level_one(offset):
+    """The module's fused path (kernels read the projection output [B,N,6+C] in place and
+    write its whole gradient) against the same computation spelled out with torch ops
+    around the parameter-level Function: split, exp + eps, ones, optional offset."""
+    from igs_b200.gs2d import GaussianSplatting2D, _SplatFromFeature, gaussian_splatting_2d
+
+    dev = torch.device("cuda", 0)
+    B, N, C, H, W = 2, 333, 3, 40, 56
+    gen = torch.Generator().manual_seed(77)
+    feat = torch.randn(B, N, 6 + C, generator=gen) * 0.5
+    feat[..., 2:4] = feat[..., 2:4] - 2.0
+    off = (torch.rand(B, N, 2, generator=gen) * 0.4 - 0.2) if offset else None
+    gout = torch.randn(B, C, H, W, generator=gen).to(dev)
+    xg, yg = GaussianSplatting2D.xy_grid((H, W), dev)
+    xg, yg = xg[None].expand(B, -1, -1, -1), yg[None].expand(B, -1, -1, -1)
+
+    f1 = feat.to(dev).requires_grad_()
+    o1 = off.to(dev).requires_grad_() if offset else None
+    out1 = _SplatFromFeature.apply(f1, o1, xg, yg, 1e-6)
+    out1.backward(gout)
+
+    f2 = feat.to(dev).requires_grad_()
+    o2 = off.to(dev).requires_grad_() if offset else None
+    pos, log_sc, rot, logit, col = f2.split([2, 2, 1, 1, C], dim=-1)
+    if offset:
+        pos = pos + o2
+    out2 = gaussian_splatting_2d(pos, col, torch.exp(log_sc) + 1e-6, rot[..., 0], torch.ones_like(logit[..., 0]), xg, yg)
+    out2.backward(gout)
+
+    assert_close(_np(out1), _np(out2), 1e-6, "image")
+    assert_close(_np(f1.grad), _np(f2.grad), 1e-5, "d_feature")
+    assert bool((f1.grad[..., 5] == 0).all())
+    if offset:
+        assert_close(_np(o1.grad), _np(o2.grad), 1e-5, "d_offset")
