@@ -34,13 +34,13 @@ SIGNATURES = {
     "igs_strerror": (ctypes.c_char_p, [_i]),
     "igs_launch_count": (ctypes.c_longlong, []),
     "igs_workspace_bytes": (_i, [_i] * 6 + [ctypes.POINTER(_sz)] * 2),
-    "igs_forward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _sz, _i, _vp]),
-    "igs_forward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _sz, _i, _vp]),
+    "igs_forward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "igs_forward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "igs_forward_sr_static": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _i, _vp]),
     "igs_normalize": (_i, [_vp] + [_i] * 4 + [_f, _vp, _vp, _i, _vp]),
     "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
     "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 10 + [_sz, _i, _vp]),
-    "igs_forward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _sz, _i, _vp]),
+    "igs_forward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "igs_backward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 3
                              + [_sz, _i, _vp]),
     "igs_read_status": (_i, [_vp, _i, _vp, ctypes.POINTER(_i)]),
@@ -161,10 +161,11 @@ def read_executed(ws: torch.Tensor) -> int:
     return int(host.value)
 
 
-def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, keep_workspace=False):
+def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, keep_workspace=False, order=None):
     """kind 'sr': s0 = scales, s1 = rotations; kind 'cov': s0, s1, s2 = cov_inv_00/01/11.
     x3, y3 are [B,H,W] views (any strides).  Returns (out, wsum) or, with
-    normalize=False, (sums [B,C+1,H,W], None)."""
+    normalize=False, (sums [B,C+1,H,W], None).  order: [B,N] int32 permutation in which the
+    gaussians are summed, or None."""
     dev = pos.device
     B, N, C = colors.shape
     _, H, W = x3.shape
@@ -177,7 +178,7 @@ def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, 
         out = torch.empty(B, C + 1, H, W, dtype=torch.float32, device=dev)
         wsum = None
     tail = (_ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N, H, W, C, float(eps), int(bool(normalize)),
-            _ptr(out), _ptr(wsum), _ptr(ws), ws.numel(), dev.index, _stream(dev))
+            _ptr(out), _ptr(wsum), _ptr(order), _ptr(ws), ws.numel(), dev.index, _stream(dev))
     lib = load()
     if kind == "sr":
         check("igs_forward_sr", lib.igs_forward_sr(_ptr(pos), _ptr(s0), _ptr(s1), _ptr(alphas), _ptr(colors), *tail))
@@ -189,7 +190,7 @@ def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, 
     return out, wsum
 
 
-def forward_feature(feat, pos_off, x3, y3, eps):
+def forward_feature(feat, pos_off, x3, y3, eps, order=None, keep_workspace=False):
     """The forward on the module's projection output feat [B,N,6+C] (contiguous); pos_off
     [B,N,2] or None.  Returns (out, wsum)."""
     dev = feat.device
@@ -202,18 +203,23 @@ def forward_feature(feat, pos_off, x3, y3, eps):
     wsum = torch.empty(B, H, W, dtype=torch.float32, device=dev)
     check("igs_forward_feature",
           load().igs_forward_feature(_ptr(feat), _ptr(pos_off), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N,
-                                     H, W, C, float(eps), 1, _ptr(out), _ptr(wsum), _ptr(ws), ws.numel(), dev.index,
-                                     _stream(dev)))
+                                     H, W, C, float(eps), 1, _ptr(out), _ptr(wsum), _ptr(order), _ptr(ws), ws.numel(),
+                                     dev.index, _stream(dev)))
+    if keep_workspace:
+        return out, wsum, ws
     return out, wsum
 
 
-def backward_feature(feat, pos_off, x3, y3, wsum, out, gout, eps, grad_mode):
-    """Gradient with respect to feat, [B,N,6+C] (the unused column gets zeros)."""
+def backward_feature(feat, pos_off, x3, y3, wsum, out, gout, eps, grad_mode, order=None, policy=True):
+    """Gradient with respect to feat, [B,N,6+C] (the unused column gets zeros).  order /
+    policy as for backward()."""
     dev = feat.device
     B, N, per = feat.shape
     C = per - 6
     _, H, W = x3.shape
-    order, probe = _order_by_policy(None, feat, pos_off, x3, y3, B, N, H, W)
+    probe = None
+    if order is None and policy:
+        order, probe = order_by_policy(None, feat, pos_off, x3, y3)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     d_feat = torch.empty_like(feat)
@@ -300,10 +306,13 @@ def set_backward_sort(mode: str) -> None:
     _probes.clear()
 
 
-def _order_by_policy(pos, feat, pos_off, x3, y3, B, N, H, W):
-    """(order or None, probe or None) for one backward call under the set_backward_sort
-    policy.  pos [B,N,2] contiguous, or None with feat [B,N,6+C] (+ pos_off) to take the
-    positions from."""
+def order_by_policy(pos, feat, pos_off, x3, y3):
+    """(order or None, probe or None) for one forward / backward under the set_backward_sort
+    policy.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off) to take the positions
+    from.  The caller hands the probe the workspace of a call it made (probe.queue(ws)), so
+    that later calls learn how narrow the gaussians are."""
+    B, N = (pos if pos is not None else feat).shape[:2]
+    _, H, W = x3.shape
     if B * N == 0 or _BACKWARD_SORT == "off":
         return None, None
     dev = x3.device
@@ -318,15 +327,15 @@ def _order_by_policy(pos, feat, pos_off, x3, y3, B, N, H, W):
 
 
 def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps, grad_mode, want_xy,
-             keep_workspace=False, order=None):
-    """Returns dict of gradients; d_x / d_y only when want_xy.  order: None = by the
-    set_backward_sort policy, or an explicit [B,N] int32 permutation."""
+             keep_workspace=False, order=None, policy=True):
+    """Returns dict of gradients; d_x / d_y only when want_xy.  order: an explicit [B,N] int32
+    permutation, or None: then by the set_backward_sort policy if ``policy``, else none."""
     dev = pos.device
     B, N, C = colors.shape
     _, H, W = x3.shape
     probe = None
-    if order is None:
-        order, probe = _order_by_policy(pos, None, None, x3, y3, B, N, H, W)
+    if order is None and policy:
+        order, probe = order_by_policy(pos, None, None, x3, y3)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     f32 = dict(dtype=torch.float32, device=dev)

@@ -159,6 +159,8 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
     }
     p->off_partial = off;
     off = align_up(off + (size_t)p->n_split * B * (C + 1) * HW * sizeof(float), 256);
+    p->off_cbox = off;
+    off = align_up(off + (size_t)B * ((N + p->chunk_g - 1) / p->chunk_g) * 4 * sizeof(float), 256);
     p->bytes = off;
     return IGS_OK;
 }
@@ -297,7 +299,8 @@ static ParamLayout layout_or_default(const ParamLayout* layout, int kind, int C)
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
-                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan, const ParamLayout* layout) {
+                 size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan, const ParamLayout* layout,
+                 const int* order) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
@@ -332,6 +335,15 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         if (rc) return rc;
     }
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
+    const bool culling_on = g_culling.load(std::memory_order_relaxed);
+    if (order && culling_on && !use_plan && p.tiles_sep > 0 && (long long)p.tiles_sep * B >= sm_count(device)) {
+        // A caller that passes an order expects narrow gaussians: a CTA then streams a few
+        // stages only, and splitting the gaussians over several CTAs per tile would just add
+        // partial sums to write and add up.  (A function of the shape and of whether an order
+        // was passed, like every other choice that affects the bits of the result.)
+        p.n_split = 1;
+        p.per_split = (N + p.chunk_g - 1) / p.chunk_g * p.chunk_g;
+    }
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     cudaError_t e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
     if (e != cudaSuccess) return (int)e;
@@ -360,7 +372,15 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     pa.C = C;
     pa.eps = eps;
     pa.kind = kind;
+    // A caller's order: the records are written in that order, and the box around each
+    // stage's gaussians lets the culling kernel pass over whole stages.
+    const bool listed = order != nullptr && p.bytes > p.off_cbox && culling_on && p.per_split / p.chunk_g >= 8;
+    pa.order = order;
+    pa.chunk_g = p.chunk_g;
+    pa.cbox = listed ? reinterpret_cast<float*>(ws + p.off_cbox) : nullptr;
     e = launch_pack(pa, st);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_stage_boxes(pa, st);
     if (e != cudaSuccess) return (int)e;
 
     const bool in_kernel = normalize && p.n_split == 1;
@@ -392,6 +412,8 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
             // launched and the count of narrow gaussians picks one (the other returns at once)
             fa.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
             fa.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
+            fa.cbox = pa.cbox;
+            fa.chunks_per_b = (N + p.chunk_g - 1) / p.chunk_g;
             e = launch_forward_chunk(p.ch.ct[k], true, false, fa, p, st);
             if (e != cudaSuccess) return (int)e;
             if (fa.cull_sel) {
@@ -514,6 +536,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     ta.nrp = p.nrp;
     ta.ncb = p.ncb;
     ta.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
+    ta.flags = grid_flag;
     ta.B = B; ta.H = H; ta.W = W; ta.C = C;
     ta.mode = mode;
     ta.eps = eps;
@@ -698,17 +721,21 @@ int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_ti
 int igs_forward_sr(const float* positions, const float* scales, const float* rotations, const float* alphas,
                    const float* colors, const float* x, const int64_t* x_strides, const float* y,
                    const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
-                   float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+                   float* wsum, const int* order, void* workspace, size_t workspace_bytes, int device,
+                   void* stream) {
     return forward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
-                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream);
+                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream,
+                        nullptr, nullptr, order);
 }
 
 int igs_forward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01, const float* cov_inv_11,
                     const float* alphas, const float* colors, const float* x, const int64_t* x_strides, const float* y,
                     const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
-                    float* wsum, void* workspace, size_t workspace_bytes, int device, void* stream) {
+                    float* wsum, const int* order, void* workspace, size_t workspace_bytes, int device,
+                   void* stream) {
     return forward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
-                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream);
+                        y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream,
+                        nullptr, nullptr, order);
 }
 
 int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, float* out, float* wsum, int device,
@@ -784,14 +811,15 @@ static ParamLayout feature_layout(int C, const float* pos_offset, float* d_featu
 
 int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,
                         const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C, float eps,
-                        int normalize, float* out, float* wsum, void* workspace, size_t workspace_bytes, int device,
+                        int normalize, float* out, float* wsum, const int* order, void* workspace,
+                        size_t workspace_bytes, int device,
                         void* stream) {
     if (C < 1) return IGS_ERR_ARG;
     const ParamLayout l = feature_layout(C, pos_offset, nullptr);
     return forward_impl(SHAPE_SCALE_ROT, gs_feature, gs_feature ? gs_feature + 2 : nullptr,
                         gs_feature ? gs_feature + 4 : nullptr, nullptr, nullptr, gs_feature ? gs_feature + 6 : nullptr, x,
                         x_strides, y, y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes,
-                        device, stream, nullptr, &l);
+                        device, stream, nullptr, &l, order);
 }
 
 int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,

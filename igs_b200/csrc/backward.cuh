@@ -16,6 +16,7 @@ struct PixelTermArgs {
     const float* gout;  // [B, C, HW]
     float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]  or, separable, [B, nrp*ncb, bwd_sep_rec_floats(ct)]
     const int* grid_sel;      // grid word (bit 0 = not a separable grid) picking the kernel; nullptr = run
+    int* flags;               // grid word: receives UPSTREAM_NOT_FINITE (separable kernel), or nullptr
     Chunks ch;
     long long npairs;
     int nrp, ncb;             // separable: row pairs and 4-column blocks per row pair

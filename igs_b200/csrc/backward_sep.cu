@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
     for (int k = 0; k < 2; ++k) yv[k] = a.y[b * a.ys_b + (long long)min(h0 + k, a.H - 1) * a.ys_h];
 
     // pixel (r, k): valid flag, flat index, S + eps, gS over ALL channels
+    bool bad = false;  // a non-finite upstream term: the skipping kernels must not run
     float ok[2][4], Sp[2][4], gS[2][4];
     long long pp[2][4];
 #pragma unroll
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
                     acc += (g / Sp[r][k]) * a.out[(b * a.C + c) * HW + pp[r][k]];
             }
             gS[r][k] = ok[r][k] * ((a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp[r][k] * Sp[r][k]) : -acc);
+            bad |= !isfinite(gS[r][k]);
         }
 
     for (int q = 0; q < a.ch.n; ++q) {
@@ -78,12 +80,14 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
                         if (c < cr) {
                             const int kk = 2 * cp + k;
                             v = ok[r][kk] * (a.gout[(b * a.C + c0 + c) * HW + pp[r][kk]] / Sp[r][kk]);
+                            bad |= !isfinite(v);
                         }
                         pr[2 + 2 * c + k] = v;
                     }
                 }
             }
     }
+    if (bad && a.flags) atomicOr(a.flags, UPSTREAM_NOT_FINITE);
 }
 
 cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s) {
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
 
     if (a.grid_sel && (*a.grid_sel & GRID_NOT_SEPARABLE)) return;  // not a separable grid: the general kernel runs
     // of the skipping / plain pair, the one the gaussians' reach and the axes call for
-    if (a.cull_sel && ((!(*a.grid_word & GRID_NOT_MONOTONE) &&
+    if (a.cull_sel && ((!(*a.grid_word & NO_BACKWARD_SKIPPING) &&
                         (long long)(*a.cull_sel) * 8 >= (long long)a.B * a.N) != CULL))
         return;
 

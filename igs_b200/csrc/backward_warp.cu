@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
     // runs instead of the other separable kernels when the grid is separable with
     // non-decreasing axes and at least one gaussian in eight is narrow
     if (a.grid_sel && (*a.grid_sel & GRID_NOT_SEPARABLE)) return;
-    if ((*a.grid_word & GRID_NOT_MONOTONE) || (long long)(*a.cull_sel) * 8 < (long long)a.B * a.N) return;
+    if ((*a.grid_word & NO_BACKWARD_SKIPPING) || (long long)(*a.cull_sel) * 8 < (long long)a.B * a.N) return;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -35,10 +35,16 @@ constexpr float CULL_T = 130.0f;
 
 // Words of the workspace's 256-byte status area.
 constexpr int STATUS_WORD = 0;       // kernels: a bounded wait gave up
-constexpr int GRID_FLAG_WORD = 1;    // grid check: bit 0 = not separable, bit 1 = axes not monotone
+constexpr int GRID_FLAG_WORD = 1;    // bit 0 = grid not separable, bit 1 = axes not monotone, bit 2 = upstream not finite
 constexpr int NARROW_COUNT_WORD = 2; // pack: gaussians whose reach is well inside the image
 constexpr int EXEC_COUNT_WORD = 4;   // (64 bits) culling kernels: (gaussian, pixel) evaluations not skipped
 constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2;
+// Skipping a term w * t because w is exactly zero is only lossless while t is finite
+// (0 * NaN and 0 * inf are NaN).  Gaussians with a non-finite parameter get an infinite box
+// (pack.cu); a non-finite upstream value (gout / weight sum) sets this bit, and the backward
+// then runs its dense kernel, which propagates the NaN the way the reference does.
+constexpr int UPSTREAM_NOT_FINITE = 4;
+constexpr int NO_BACKWARD_SKIPPING = GRID_NOT_MONOTONE | UPSTREAM_NOT_FINITE;
 
 // Backward pixel record, one per PAIR of consecutive pixels and channel chunk:
 //   {x0,x1, y0,y1, gS0,gS1, gn0_0,gn0_1, ...}  padded to 4 floats

@@ -51,9 +51,18 @@ struct FwdCfg {
     static constexpr int UNROLL = CT <= 3 ? 4 : 2;
 #endif
     static constexpr int RS = fwd_rec_floats(CT);
-    // stages | mbarriers | flags (16 B) | surviving-gaussian list of the current stage | per-warp scratch
-    static constexpr size_t SMEM = (size_t)STAGES * CHUNK_G * RS * sizeof(float) + STAGES * sizeof(uint64_t) + 16 +
-                                   CHUNK_G * sizeof(unsigned short) + 8 * 4 * sizeof(float);
+    // The culling kernel spends little time per stage (most gaussians are skipped), so the
+    // latency of a stage's copy shows unless more copies are in flight.
+    static constexpr int STAGES_CULL = 4;
+    static constexpr int LIST_CAP = 1024;  // stages a CTA can list (ordered calls): 131072 gaussians per split
+    // stages | mbarriers | flags (16 B) | surviving-gaussian list of the current stage | per-warp scratch |
+    // list of the stages whose box meets the CTA's pixels
+    static constexpr size_t smem_bytes(int stages) {
+        return (size_t)stages * CHUNK_G * RS * sizeof(float) + stages * sizeof(uint64_t) + 16 +
+               CHUNK_G * sizeof(unsigned short) + 8 * 4 * sizeof(float) + LIST_CAP * sizeof(unsigned short);
+    }
+    static constexpr size_t SMEM = smem_bytes(STAGES);
+    static constexpr size_t SMEM_CULL = smem_bytes(STAGES_CULL);
 };
 
 // Separable tiles: 16 rows x 64 columns per CTA, 2 rows x 4 columns per thread.
@@ -63,7 +72,8 @@ template <int CT, int PX_, bool SEP, bool CULL>
 __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN_CTAS)
     splat_forward_kernel(FwdArgs a) {
     using Cfg = FwdCfg<CT, PX_>;
-    constexpr int T = Cfg::THREADS, NP = Cfg::PX / 2, G = Cfg::CHUNK_G, NS = Cfg::STAGES, RS = Cfg::RS;
+    constexpr int T = Cfg::THREADS, NP = Cfg::PX / 2, G = Cfg::CHUNK_G, RS = Cfg::RS;
+    constexpr int NS = CULL ? Cfg::STAGES_CULL : Cfg::STAGES;
     static_assert(!SEP || PX_ == 8, "the separable patch is 2 rows x 4 columns");
 
     // only the instantiation that matches the grid's kind does the work
@@ -78,6 +88,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
     int* s_failed = reinterpret_cast<int*>(bars + NS);
     unsigned short* s_list = reinterpret_cast<unsigned short*>(s_failed + 4);
     float* s_warp = reinterpret_cast<float*>(s_list + G);  // [4 warps][4] bounding box partials, then counts
+    unsigned short* s_stages = reinterpret_cast<unsigned short*>(s_warp + 32);  // [LIST_CAP]
 
     const int tid = threadIdx.x;
     const int b = blockIdx.z, split = blockIdx.y;
@@ -190,34 +201,71 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
     }
     __syncthreads();
 
-    auto issue = [&](int chunk) {
-        const int st = chunk % NS;
+    // Which stages to stream: all of them, or -- culling kernel, records in a spatial order --
+    // only those whose bounding box meets this CTA's pixels, listed in ascending order (so
+    // the sums run in the same sequence, minus terms that are exact zeros).
+    int n_list = n_chunks;
+    bool use_list = false;
+    if constexpr (CULL) {
+        if (a.cbox && cull && n_chunks <= Cfg::LIST_CAP) {
+            use_list = true;
+            const float4* boxes = reinterpret_cast<const float4*>(a.cbox) + ((long long)b * a.chunks_per_b + n_begin / G);
+            int* s_count = reinterpret_cast<int*>(s_warp);
+            int total = 0;
+            for (int base0 = 0; base0 < n_chunks; base0 += T) {
+                const int c = base0 + tid;
+                bool keep = false;
+                if (c < n_chunks) {
+                    const float4 q = boxes[c];  // x0, x1, y0, y1
+                    keep = !(q.y < bx0 || q.x > bx1 || q.w < by0 || q.z > by1);
+                }
+                const unsigned ballot = __ballot_sync(0xffffffffu, keep);
+                if ((tid & 31) == 0) s_count[tid >> 5] = __popc(ballot);
+                __syncthreads();
+                int before = 0, n_keep = 0;
+#pragma unroll
+                for (int w = 0; w < T / 32; ++w) {
+                    if (w < (tid >> 5)) before += s_count[w];
+                    n_keep += s_count[w];
+                }
+                if (keep) s_stages[total + before + __popc(ballot & ((1u << (tid & 31)) - 1u))] = (unsigned short)c;
+                total += n_keep;
+                __syncthreads();
+            }
+            n_list = total;
+        }
+    }
+    auto stage_chunk = [&](int k) { return (CULL && use_list) ? (int)s_stages[k] : k; };
+
+    auto issue = [&](int k) {
+        const int st = k % NS;
+        const int chunk = stage_chunk(k);
         const int cnt = min(G, n_total - chunk * G);
         const uint32_t bytes = (uint32_t)cnt * RS * sizeof(float);
         mbar_expect_tx(&bars[st], bytes);
         bulk_g2s(stage_base + (size_t)st * G * RS, src + (long long)chunk * G * RS, bytes, &bars[st]);
     };
     if (tid == 0) {
-        for (int c = 0; c < NS && c < n_chunks; ++c) issue(c);
+        for (int c = 0; c < NS && c < n_list; ++c) issue(c);
     }
 
     int evaluated = 0;  // gaussians this CTA did not skip (counted by the culling kernel only)
-    for (int chunk = 0; chunk < n_chunks; ++chunk) {
-        const int st = chunk % NS;
-        const uint32_t parity = (chunk / NS) & 1;
+    for (int k = 0; k < n_list; ++k) {
+        const int st = k % NS;
+        const uint32_t parity = (k / NS) & 1;
         if (!mbar_wait_bounded(&bars[st], parity)) *s_failed = 1;
         __syncthreads();
         if (*s_failed) {
             // give copies still in flight a bounded chance to land before the CTA
             // (and its shared memory) goes away, then report and leave
             if (tid == 0) {
-                for (int c = chunk + 1; c < n_chunks && c < chunk + NS; ++c)
+                for (int c = k + 1; c < n_list && c < k + NS; ++c)
                     mbar_wait_bounded(&bars[c % NS], (c / NS) & 1);
                 atomicOr(a.status, STATUS_WAIT_TIMEOUT);
             }
             return;
         }
-        const int cnt = min(G, n_total - chunk * G);
+        const int cnt = min(G, n_total - stage_chunk(k) * G);
         const float4* rec = reinterpret_cast<const float4*>(stage_base + (size_t)st * G * RS);
         auto splat = [&](int g) {
             const float4* rf = rec + (size_t)g * (RS / 4);
@@ -292,7 +340,7 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
             for (int i = 0; i < n_keep; ++i) splat(s_list[i]);
         }
         __syncthreads();  // every lane is done with this stage
-        if (tid == 0 && chunk + NS < n_chunks) issue(chunk + NS);
+        if (tid == 0 && k + NS < n_list) issue(k + NS);
     }
 
     if constexpr (CULL) {
@@ -366,19 +414,20 @@ __global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
 template <int CT, int PX_, bool SEP, bool CULL>
 static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s) {
     using Cfg = FwdCfg<CT, PX_>;
+    constexpr size_t smem = CULL ? Cfg::SMEM_CULL : Cfg::SMEM;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(splat_forward_kernel<CT, PX_, SEP, CULL>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     dim3 grid((unsigned)(SEP ? p.tiles_sep : p.tiles), (unsigned)p.n_split, (unsigned)a.B);
     {
         KernelTimer timer(K_FORWARD, s);
-        splat_forward_kernel<CT, PX_, SEP, CULL><<<grid, Cfg::THREADS, Cfg::SMEM, s>>>(a);
+        splat_forward_kernel<CT, PX_, SEP, CULL><<<grid, Cfg::THREADS, smem, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();

@@ -19,6 +19,10 @@ struct FwdArgs {
     const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable
     const int* cull_sel;   // count of narrow gaussians: at least one in eight -> culling / plain
     unsigned long long* exec_count;  // culling kernel: evaluations it did not skip (may be null)
+    // culling kernel, records in a spatial order: {x0,x1,y0,y1} around each stage's gaussians,
+    // [B, chunks_per_b, 4]; stages whose box misses the CTA's pixels are not even loaded
+    const float* cbox;
+    int chunks_per_b;
     int tiles_x;           // separable tiling: CTAs per tile row
     int B, N, H, W, C;
     int c0, cr;  // first channel and real channel count of this chunk

@@ -10,11 +10,13 @@
 // bit for bit: each gaussian's sums are taken over the same pixels in the same sequence
 // whichever thread owns it.
 //
-// How.  A counting sort on the Hilbert-curve index of the gaussian's cell in a 64 x 64 lattice laid
-// over the sampled extent (first row of x, first column of y): count per cell, exclusive
-// scan per batch element, scatter through an atomic cursor per cell.  The order inside a
-// cell is whatever the atomics give, and may differ from run to run; it is a permutation
-// every time, and that is all the backward needs.
+// How.  A stable counting sort on the Hilbert-curve index of the gaussian's cell in a 64 x 64
+// lattice laid over the sampled extent (first row of x, first column of y).  Gaussians are
+// taken in blocks of 1024: each block counts its gaussians per cell; a scan turns the
+// counts into the first slot of every (cell, block); each block then ranks its gaussians
+// within their cells in index order (warp by warp, __match_any_sync inside a warp).  Equal
+// cells keep their original order, no result depends on the timing of an atomic, so the
+// permutation is the same on every run.
 #include "common.cuh"
 
 namespace igs {
@@ -28,10 +30,11 @@ struct OrderArgs {
     const float* x;
     const float* y;
     long long xs_b, xs_w, ys_b, ys_h;
-    int* hist;             // [B, ORDER_CELLS]: counts, then cursors
+    int* cell_total;       // [B, ORDER_CELLS]: gaussians per cell, then the cell's first slot
+    int* block_hist;       // [B, n_blocks, ORDER_CELLS]: per block of 1024 gaussians, count then first slot
     unsigned short* keys;  // [B*N]
     int* order;            // [B,N]
-    int B, N, H, W;
+    int B, N, H, W, n_blocks;
 };
 
 // Position of cell (x, y) along the Hilbert curve through the lattice.  Consecutive
@@ -65,23 +68,42 @@ __device__ __forceinline__ int cell_of(float p, float e0, float e1) {
     return (int)t;
 }
 
-__global__ void __launch_bounds__(256) order_count_kernel(OrderArgs a) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)a.B * a.N) return;
-    const long long b = i / a.N;
+constexpr int ORDER_BLOCK = 1024;  // gaussians per sorting block
+
+__device__ __forceinline__ unsigned order_key(const OrderArgs& a, long long b, long long i) {
     const float x0 = a.x[b * a.xs_b], x1 = a.x[b * a.xs_b + (long long)(a.W - 1) * a.xs_w];
     const float y0 = a.y[b * a.ys_b], y1 = a.y[b * a.ys_b + (long long)(a.H - 1) * a.ys_h];
     const int cx = cell_of(a.pos[2 * i], x0, x1), cy = cell_of(a.pos[2 * i + 1], y0, y1);
-    const unsigned key = hilbert_index((unsigned)cx, (unsigned)cy);
-    a.keys[i] = (unsigned short)key;
-    atomicAdd(a.hist + b * ORDER_CELLS + key, 1);
+    return hilbert_index((unsigned)cx, (unsigned)cy);
 }
 
-// One CTA per batch element: counts -> exclusive prefix sums (the cursors' start values).
+// grid (blocks of gaussians, B): keys, this block's count per cell, and the cell totals
+__global__ void __launch_bounds__(ORDER_BLOCK) order_count_kernel(OrderArgs a) {
+    __shared__ int s_hist[ORDER_CELLS];
+    const int b = blockIdx.y, blk = blockIdx.x;
+    for (int c = threadIdx.x; c < ORDER_CELLS; c += ORDER_BLOCK) s_hist[c] = 0;
+    __syncthreads();
+    const int n = blk * ORDER_BLOCK + threadIdx.x;
+    if (n < a.N) {
+        const long long i = (long long)b * a.N + n;
+        const unsigned key = order_key(a, b, i);
+        a.keys[i] = (unsigned short)key;
+        atomicAdd(&s_hist[key], 1);  // integer counts: the result does not depend on the order of the adds
+    }
+    __syncthreads();
+    int* bh = a.block_hist + ((long long)b * a.n_blocks + blk) * ORDER_CELLS;
+    for (int c = threadIdx.x; c < ORDER_CELLS; c += ORDER_BLOCK) {
+        const int v = s_hist[c];
+        bh[c] = v;
+        if (v) atomicAdd(a.cell_total + (long long)b * ORDER_CELLS + c, v);
+    }
+}
+
+// One CTA per batch element: cell totals -> exclusive prefix sums (first slot of every cell).
 __global__ void __launch_bounds__(ORDER_SCAN_THREADS) order_scan_kernel(OrderArgs a) {
     constexpr int PER = ORDER_CELLS / ORDER_SCAN_THREADS;
     __shared__ int s_warp[ORDER_SCAN_THREADS / 32];
-    int* h = a.hist + (long long)blockIdx.x * ORDER_CELLS + threadIdx.x * PER;
+    int* h = a.cell_total + (long long)blockIdx.x * ORDER_CELLS + threadIdx.x * PER;
     int v[PER], sum = 0;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
@@ -115,17 +137,51 @@ __global__ void __launch_bounds__(ORDER_SCAN_THREADS) order_scan_kernel(OrderArg
     }
 }
 
-__global__ void __launch_bounds__(256) order_scatter_kernel(OrderArgs a) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)a.B * a.N) return;
-    const long long b = i / a.N;
-    const int slot = atomicAdd(a.hist + b * ORDER_CELLS + a.keys[i], 1);
-    // slot < N by construction (the cursors partition [0,N)); the guard keeps a corrupted
-    // workspace from turning into a stray write
-    if (slot >= 0 && slot < a.N) a.order[b * a.N + slot] = (int)(i - b * a.N);
+// thread per (batch element, cell): the cell's first slot, advanced block by block, replaces
+// each block's count by the first slot of that (cell, block)
+__global__ void __launch_bounds__(256) order_block_base_kernel(OrderArgs a) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)a.B * ORDER_CELLS) return;
+    const long long b = t / ORDER_CELLS, c = t - b * ORDER_CELLS;
+    int run = a.cell_total[t];
+    int* bh = a.block_hist + b * a.n_blocks * ORDER_CELLS + c;
+    for (int blk = 0; blk < a.n_blocks; ++blk) {
+        const int v = bh[(long long)blk * ORDER_CELLS];
+        bh[(long long)blk * ORDER_CELLS] = run;
+        run += v;
+    }
 }
 
-static size_t order_hist_bytes(int B) { return ((size_t)B * ORDER_CELLS * sizeof(int) + 255) / 256 * 256; }
+// grid (blocks of gaussians, B): slot = first slot of (cell, block) + rank of the gaussian
+// among the block's gaussians of that cell, in index order
+__global__ void __launch_bounds__(ORDER_BLOCK) order_scatter_kernel(OrderArgs a) {
+    __shared__ int s_next[ORDER_CELLS];
+    const int b = blockIdx.y, blk = blockIdx.x;
+    const int* bh = a.block_hist + ((long long)b * a.n_blocks + blk) * ORDER_CELLS;
+    for (int c = threadIdx.x; c < ORDER_CELLS; c += ORDER_BLOCK) s_next[c] = bh[c];
+    __syncthreads();
+    const int n = blk * ORDER_BLOCK + threadIdx.x;
+    const bool valid = n < a.N;
+    // threads past the end share a key no gaussian has, so they match only each other
+    const unsigned key = valid ? a.keys[(long long)b * a.N + n] : 0xffffffffu;
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const bool leader = rank == 0;
+    for (int w = 0; w < ORDER_BLOCK / 32; ++w) {  // warps in index order
+        if (warp == w && valid) {
+            const int slot = s_next[key] + rank;
+            // slot < N by construction; the guard keeps a corrupted workspace from turning into a stray write
+            if (slot >= 0 && slot < a.N) a.order[(long long)b * a.N + slot] = n;
+        }
+        __syncthreads();
+        if (warp == w && valid && leader) s_next[key] += __popc(peers);
+        __syncthreads();
+    }
+}
+
+static size_t order_align(size_t v) { return (v + 255) / 256 * 256; }
+static int order_blocks(int N) { return (N + ORDER_BLOCK - 1) / ORDER_BLOCK; }
 
 }  // namespace igs
 
@@ -133,7 +189,9 @@ using namespace igs;
 
 extern "C" size_t igs_spatial_order_workspace_bytes(int B, int N) {
     if (B <= 0 || N <= 0) return 256;
-    return order_hist_bytes(B) + ((size_t)B * N * sizeof(unsigned short) + 255) / 256 * 256;
+    return order_align((size_t)B * ORDER_CELLS * sizeof(int)) +
+           order_align((size_t)B * order_blocks(N) * ORDER_CELLS * sizeof(int)) +
+           order_align((size_t)B * N * sizeof(unsigned short));
 }
 
 extern "C" int igs_spatial_order(const float* positions, const float* x, const int64_t* x_strides, const float* y,
@@ -142,8 +200,8 @@ extern "C" int igs_spatial_order(const float* positions, const float* x, const i
     if (B < 0 || N < 0 || H < 1 || W < 1) return IGS_ERR_ARG;
     if (B == 0 || N == 0) return IGS_OK;
     if (!positions || !x || !y || !x_strides || !y_strides || !order) return IGS_ERR_ARG;
+    if (B > 65535) return IGS_ERR_LIMIT;
     if (!workspace || workspace_bytes < igs_spatial_order_workspace_bytes(B, N)) return IGS_ERR_WORKSPACE;
-    if ((long long)B * N > 0x7fffffffLL * 256) return IGS_ERR_LIMIT;
     DeviceGuard guard(device);
     if (!guard.ok) return IGS_ERR_DEVICE;
     cudaStream_t s = (cudaStream_t)stream;
@@ -156,22 +214,29 @@ extern "C" int igs_spatial_order(const float* positions, const float* x, const i
     a.xs_w = x_strides[2];
     a.ys_b = y_strides[0];
     a.ys_h = y_strides[1];
-    a.hist = reinterpret_cast<int*>(workspace);
-    a.keys = reinterpret_cast<unsigned short*>(reinterpret_cast<unsigned char*>(workspace) + order_hist_bytes(B));
+    a.n_blocks = order_blocks(N);
+    unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+    a.cell_total = reinterpret_cast<int*>(ws);
+    ws += order_align((size_t)B * ORDER_CELLS * sizeof(int));
+    a.block_hist = reinterpret_cast<int*>(ws);
+    ws += order_align((size_t)B * a.n_blocks * ORDER_CELLS * sizeof(int));
+    a.keys = reinterpret_cast<unsigned short*>(ws);
     a.order = order;
     a.B = B;
     a.N = N;
     a.H = H;
     a.W = W;
 
-    cudaError_t e = cudaMemsetAsync(a.hist, 0, (size_t)B * ORDER_CELLS * sizeof(int), s);
+    cudaError_t e = cudaMemsetAsync(a.cell_total, 0, (size_t)B * ORDER_CELLS * sizeof(int), s);
     if (e != cudaSuccess) return (int)e;
-    const unsigned blocks = (unsigned)(((long long)B * N + 255) / 256);
-    order_count_kernel<<<blocks, 256, 0, s>>>(a);
+    const dim3 blocks((unsigned)a.n_blocks, (unsigned)B);
+    order_count_kernel<<<blocks, ORDER_BLOCK, 0, s>>>(a);
     count_launch();
     order_scan_kernel<<<(unsigned)B, ORDER_SCAN_THREADS, 0, s>>>(a);
     count_launch();
-    order_scatter_kernel<<<blocks, 256, 0, s>>>(a);
+    order_block_base_kernel<<<(unsigned)(((long long)B * ORDER_CELLS + 255) / 256), 256, 0, s>>>(a);
+    count_launch();
+    order_scatter_kernel<<<blocks, ORDER_BLOCK, 0, s>>>(a);
     count_launch();
     return (int)cudaGetLastError();
 }

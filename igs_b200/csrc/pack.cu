@@ -14,9 +14,12 @@
 namespace igs {
 
 __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    // `slot` is where the records go, `i` the gaussian they describe: the same unless the
+    // caller asked for the forward records in a given order
+    const long long slot = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     bool narrow = false;
-    if (i < a.M) {
+    if (slot < a.M) {
+        const long long i = a.order ? slot / a.N * a.N + a.order[slot] : slot;
         const ParamLayout& L = a.lay;
         float px = a.pos[(long long)L.pos_s * i], py = a.pos[(long long)L.pos_s * i + 1];
         if (L.pos_off) {
@@ -50,6 +53,11 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             hy = 1.001f * sqrtf(4.0f * CULL_T * (-A) / D);
             if (!(hx == hx) || !(hy == hy)) hx = hy = INFINITY;
         }
+        // 0 * NaN is NaN: a gaussian with a non-finite parameter must reach every pixel, as in
+        // the reference (its weights, or their products with alpha and the colours, are NaN)
+        bool finite = isfinite(px) && isfinite(py) && isfinite(A) && isfinite(B2) && isfinite(Cq) && isfinite(al);
+        for (int c = 0; c < a.C; ++c) finite = finite && isfinite(a.colors[i * L.col_s + c]);
+        if (!finite) hx = hy = INFINITY;
         if (a.narrow_count && a.x && a.W > 1 && a.H > 1) {
             // "narrow" = the box covers less than three quarters of the sampled extent in x or y
             const long long b = i / a.N;
@@ -59,7 +67,7 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
         }
 
         if (a.geo) {
-            float4* g = reinterpret_cast<float4*>(a.geo + i * GEO_FLOATS);
+            float4* g = reinterpret_cast<float4*>(a.geo + slot * GEO_FLOATS);
             g[0] = make_float4(px, py, A, B2);
             g[1] = make_float4(Cq, al, hx, hy);
         }
@@ -68,7 +76,7 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             if (!rec) continue;
             const int ct = a.ch.ct[k], cr = a.ch.cr[k], c0 = a.ch.c0[k];
             const int rs = fwd_rec_floats(ct);
-            float* r = rec + i * rs;
+            float* r = rec + slot * rs;
             r[0] = px; r[1] = py; r[2] = A; r[3] = B2; r[4] = Cq; r[5] = al;
             // colours pre-multiplied by alpha: numerator += e * (alpha * colour)
             for (int c = 0; c < ct; ++c) r[6 + c] = (c < cr) ? al * a.colors[i * L.col_s + c0 + c] : 0.f;
@@ -86,7 +94,7 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
     if (a.grid_flag && a.x) {
         bool bad = false;
         const long long per_b = (long long)a.W + a.H, total = a.B * per_b;
-        for (long long j = i; j < total; j += (long long)gridDim.x * blockDim.x) {
+        for (long long j = slot; j < total; j += (long long)gridDim.x * blockDim.x) {
             const long long b = j / per_b, k = j - b * per_b;
             if (k < a.W - 1) {
                 const float* p = a.x + b * a.xs_b + k * a.xs_w;
@@ -98,6 +106,56 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
         }
         if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.grid_flag, GRID_NOT_MONOTONE);
     }
+}
+
+// Box {x0, x1, y0, y1} around the zero-weight boxes of the gaussians of one forward stage
+// (chunk_g consecutive records), read back from the records pack_kernel wrote.
+__global__ void __launch_bounds__(128) stage_box_kernel(PackArgs a, int n_stages) {
+    __shared__ float s_box[4][4];
+    const int b = blockIdx.y, stage = blockIdx.x;
+    const int ct = a.ch.ct[0], rs = fwd_rec_floats(ct);
+    float u[4] = {INFINITY, -INFINITY, INFINITY, -INFINITY};
+    for (int k = threadIdx.x; k < a.chunk_g; k += blockDim.x) {
+        const int slot = stage * a.chunk_g + k;
+        if (slot >= a.N) break;
+        const float* r = a.frec[0] + ((long long)b * a.N + slot) * rs;
+        const float gx = r[0], gy = r[1], hx = r[6 + ct], hy = r[7 + ct];
+        // a NaN anywhere makes the box NaN-free but infinite: such a stage is never skipped
+        const bool bad = !(gx == gx) || !(gy == gy) || !(hx == hx) || !(hy == hy);
+        u[0] = fminf(u[0], bad ? -INFINITY : gx - hx);
+        u[1] = fmaxf(u[1], bad ? INFINITY : gx + hx);
+        u[2] = fminf(u[2], bad ? -INFINITY : gy - hy);
+        u[3] = fmaxf(u[3], bad ? INFINITY : gy + hy);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        u[0] = fminf(u[0], __shfl_xor_sync(0xffffffffu, u[0], d));
+        u[1] = fmaxf(u[1], __shfl_xor_sync(0xffffffffu, u[1], d));
+        u[2] = fminf(u[2], __shfl_xor_sync(0xffffffffu, u[2], d));
+        u[3] = fmaxf(u[3], __shfl_xor_sync(0xffffffffu, u[3], d));
+    }
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s_box[threadIdx.x >> 5][k] = u[k];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 4; ++w) {
+            u[0] = fminf(u[0], s_box[w][0]);
+            u[1] = fmaxf(u[1], s_box[w][1]);
+            u[2] = fminf(u[2], s_box[w][2]);
+            u[3] = fmaxf(u[3], s_box[w][3]);
+        }
+        reinterpret_cast<float4*>(a.cbox)[(long long)b * n_stages + stage] = make_float4(u[0], u[1], u[2], u[3]);
+    }
+}
+
+cudaError_t launch_stage_boxes(const PackArgs& a, cudaStream_t s) {
+    if (!a.cbox || !a.frec[0] || a.chunk_g <= 0 || a.N <= 0 || a.B <= 0) return cudaSuccess;
+    const int n_stages = (a.N + a.chunk_g - 1) / a.chunk_g;
+    stage_box_kernel<<<dim3((unsigned)n_stages, (unsigned)a.B), 128, 0, s>>>(a, n_stages);
+    count_launch();
+    return cudaGetLastError();
 }
 
 cudaError_t launch_pack(const PackArgs& a, cudaStream_t s) {

@@ -18,6 +18,9 @@ struct PackArgs {
     const float* x;       // sample coordinates (only their extent is read) or nullptr
     const float* y;
     long long xs_b, xs_w, ys_b, ys_h;
+    const int* order;     // [B,N]: record slot -> gaussian (forward records only), or nullptr
+    float* cbox;          // [B, ceil(N / chunk_g), 4]: box around each stage's gaussians, or nullptr
+    int chunk_g;
     int* narrow_count;    // device counter of narrow gaussians, or nullptr
     int* grid_flag;       // receives GRID_NOT_MONOTONE when an axis is not non-decreasing, or nullptr
     int B, N, H, W;       // batch, gaussians per batch element, image size
@@ -31,6 +34,7 @@ struct PackArgs {
 };
 
 cudaError_t launch_pack(const PackArgs& a, cudaStream_t s);
+cudaError_t launch_stage_boxes(const PackArgs& a, cudaStream_t s);  // after launch_pack, when a.cbox is set
 
 // scales, rotation -> inverse-covariance entries (closed form of R S (R S)^T + eps I
 // inverted); shared by the prologue and by the gradient epilogue.

@@ -31,6 +31,7 @@ struct FwdPlan {
     int stages;
     size_t off_frec[MAX_CHUNKS];
     size_t off_partial;  // [n_split][B][C+1][HW] when n_split > 1 or not normalising in-kernel
+    size_t off_cbox;     // [B][ceil(N / chunk_g)][4]: bounding boxes of the stages' gaussians (ordered calls)
     size_t bytes;
 };
 
@@ -76,7 +77,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
                  size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr,
-                 const ParamLayout* layout = nullptr);
+                 const ParamLayout* layout = nullptr, const int* order = nullptr);
 
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);

@@ -201,8 +201,13 @@ class _SplatFromScaleRotation(torch.autograd.Function):
             raise ValueError(f"rotations must be [B,N] = {(B, N)}, got {tuple(rotations.shape)}")
         x3, y3 = _grid_views(x, y, B)
         pos, col, sc, rot, al = (t.contiguous() for t in (positions, colors, scales, rotations, alphas))
-        out, wsum = _lib.forward("sr", pos, sc, rot, None, al, col, x3, y3, eps)
-        ctx.save_for_backward(x, y, pos, col, sc, rot, al, wsum, out)
+        # one spatial order per step (if the policy wants one), shared by forward and backward
+        order, probe = _lib.order_by_policy(pos, None, None, x3, y3)
+        out, wsum, ws = _lib.forward("sr", pos, sc, rot, None, al, col, x3, y3, eps, keep_workspace=True, order=order)
+        if probe is not None:
+            probe.queue(ws)
+        ctx.save_for_backward(x, y, pos, col, sc, rot, al, wsum, out, order if order is not None else wsum.new_empty(0))
+        ctx.has_order = order is not None
         ctx.eps = float(eps)
         ctx.grad_mode = _GRAD_MODES[_grad_mode]
         return out
@@ -210,12 +215,12 @@ class _SplatFromScaleRotation(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, pos, col, sc, rot, al, wsum, out = ctx.saved_tensors
+        x, y, pos, col, sc, rot, al, wsum, out, order = ctx.saved_tensors
         B = pos.shape[0]
         x3, y3 = _grid_views(x, y, B)
         want_xy = ctx.needs_input_grad[5] or ctx.needs_input_grad[6]
         g = _lib.backward("sr", pos, sc, rot, None, al, col, x3, y3, wsum, out, grad_result.contiguous(), ctx.eps,
-                          ctx.grad_mode, want_xy)
+                          ctx.grad_mode, want_xy, order=order if ctx.has_order else None, policy=False)
         gx = _reduce_like(g["x"][:, None], x.shape) if want_xy else None
         gy = _reduce_like(g["y"][:, None], y.shape) if want_xy else None
         return g["positions"], g["colors"], g["scales"], g["rotations"], g["alphas"], gx, gy, None
@@ -245,9 +250,15 @@ class _SplatFromFeature(torch.autograd.Function):
                 raise ValueError(f"the position offsets must be [B,N,2] = {(B, N, 2)}, got {tuple(pos_offset.shape)}")
             off = pos_offset.contiguous()
         x3, y3 = _grid_views(x, y, B)
-        out, wsum = _lib.forward_feature(feat, off, x3, y3, eps)
-        ctx.save_for_backward(x, y, feat, off if off is not None else feat.new_empty(0), wsum, out)
+        order, probe = _lib.order_by_policy(None, feat, off, x3, y3)
+        out, wsum, ws = _lib.forward_feature(feat, off, x3, y3, eps, order=order, keep_workspace=True)
+        if probe is not None:
+            probe.queue(ws)
+        none = feat.new_empty(0)
+        ctx.save_for_backward(x, y, feat, off if off is not None else none, wsum, out,
+                              order if order is not None else none)
         ctx.has_off = off is not None
+        ctx.has_order = order is not None
         ctx.eps = float(eps)
         ctx.grad_mode = _GRAD_MODES[_grad_mode]
         return out
@@ -255,10 +266,11 @@ class _SplatFromFeature(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, feat, off, wsum, out = ctx.saved_tensors
+        x, y, feat, off, wsum, out, order = ctx.saved_tensors
         x3, y3 = _grid_views(x, y, feat.shape[0])
         d_feat = _lib.backward_feature(feat, off if ctx.has_off else None, x3, y3, wsum, out,
-                                       grad_result.contiguous(), ctx.eps, ctx.grad_mode)
+                                       grad_result.contiguous(), ctx.eps, ctx.grad_mode,
+                                       order=order if ctx.has_order else None, policy=False)
         d_off = d_feat[..., :2] if (ctx.has_off and ctx.needs_input_grad[1]) else None
         return d_feat, d_off, None, None, None
 

@@ -68,11 +68,17 @@ int igs_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* f
  *                   planes, then the weight-sum plane), wsum is ignored.  Used when
  *                   gaussians are sharded across GPUs and the sums are all-reduced
  *                   before igs_normalize.
+ *   order: NULL, or a permutation [B,N] (int32; igs_spatial_order makes a good one): the
+ *                   gaussians are summed in that order.  In a spatial order, 128 consecutive
+ *                   gaussians share a patch of the image, and with narrow gaussians a CTA
+ *                   does not even load the groups whose patch misses its pixels.  The image
+ *                   then differs from an order-less call by fp32 rounding (another order
+ *                   of summation); with the same order it is the same bits on every call.
  */
 int igs_forward_sr(const float* positions, const float* scales, const float* rotations,
                    const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
                    const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C,
-                   float eps, int normalize, float* out, float* wsum, void* workspace,
+                   float eps, int normalize, float* out, float* wsum, const int* order, void* workspace,
                    size_t workspace_bytes, int device, void* stream);
 
 /*
@@ -85,7 +91,7 @@ int igs_forward_cov(const float* positions, const float* cov_inv_00, const float
                     const float* cov_inv_11, const float* alphas, const float* colors, const float* x,
                     const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
                     int H, int W, int C, float eps, int normalize, float* out, float* wsum,
-                    void* workspace, size_t workspace_bytes, int device, void* stream);
+                    const int* order, void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
  * igs_forward_sr without a workspace argument, for hosts that cannot allocate device
@@ -171,7 +177,7 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
 int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x,
                         const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
                         int H, int W, int C, float eps, int normalize, float* out, float* wsum,
-                        void* workspace, size_t workspace_bytes, int device, void* stream);
+                        const int* order, void* workspace, size_t workspace_bytes, int device, void* stream);
 int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x,
                          const int64_t* x_strides, const float* y, const int64_t* y_strides,
                          const float* wsum, const float* out, const float* gout, int B, int N, int H,
@@ -206,8 +212,9 @@ int igs_set_culling(int on);
  * order of a 64 x 64 lattice over the sampled extent; x, y and their strides as for the
  * forward, only the first row of x and the first column of y are read).  Worth computing
  * when most gaussians are narrow (igs_read_narrow_count) and the grid is separable: the
- * backward then skips most pixel runs.  The order within a lattice cell may differ from
- * run to run; the gradients computed with it do not.  No counterpart in the reference,
+ * backward then skips most pixel runs.  A stable counting sort: gaussians of one lattice
+ * cell keep their index order and the permutation is the same on every run.  No
+ * counterpart in the reference,
  * whose backward is a dense torch expression (src/igs/gs2d.py:331-436).
  *   workspace: igs_spatial_order_workspace_bytes(B, N) bytes of device memory.
  */

@@ -43,7 +43,7 @@ def test_error_strings_and_argument_errors_without_gpu():
     # argument validation happens before any CUDA call
     assert lib.igs_profile_read(99, None, None) == -1
     assert lib.igs_forward_sr(None, None, None, None, None, None, None, None, None, 1, 1, 4, 4, 0, 1e-6, 1,
-                              None, None, None, 0, 0, None) == -1
+                              None, None, None, None, 0, 0, None) == -1
 
 
 def test_product_package_never_imports_the_oracle():

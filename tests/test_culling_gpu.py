@@ -122,6 +122,12 @@ def test_spatial_order_is_a_permutation_with_neighbours_adjacent():
     order = _lib.spatial_order(d["positions"], x[:, 0], y[:, 0])
     assert order.dtype == torch.int32 and order.shape == (B, N)
     assert torch.equal(order.long().sort(dim=1).values, torch.arange(N, device=dev).expand(B, N))
+    for _ in range(3):  # a stable sort: the same permutation on every run
+        assert torch.equal(_lib.spatial_order(d["positions"], x[:, 0], y[:, 0]), order)
+    # gaussians at one and the same place share a cell and must keep their index order
+    same = d["positions"].clone()
+    same[:] = same[:, :1]
+    assert torch.equal(_lib.spatial_order(same, x[:, 0], y[:, 0]).long(), torch.arange(N, device=dev).expand(B, N))
     # a run of 64 consecutive slots (two warps' gaussians) spans a small patch, not the image
     p = torch.gather(d["positions"], 1, order.long()[..., None].expand(B, N, 2))
     runs = p[:, : N // 64 * 64].reshape(B, -1, 64, 2)
@@ -237,3 +243,106 @@ def test_auto_policy_learns_that_gaussians_are_narrow():
     for _ in range(4):
         _backward_with(d2, gout2, x2, y2, None)
     assert not _lib._probes[(dev.index, B, N, 100, W)].narrow
+
+
+@pytest.mark.parametrize("C", [1, 3, 4])
+def test_ordered_forward_skips_stages_without_changing_a_bit(C):
+    """With an order the forward records are written in that order and a CTA lists the stages
+    (128 consecutive gaussians) whose box meets its pixels.  Same order, culling on / off:
+    the same bits.  Against the order-less forward: equal to rounding (another sequence of
+    additions).  A few image-wide and one NaN-positioned gaussian are mixed in."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 2, 5000, 136, 200
+    d, _, x, y = _case(B, N, H, W, C, 0.004, 0.03, seed=41 + C, dev=dev)
+    d["scales"][:, ::173] = 0.9
+    x3, y3 = x[:, 0], y[:, 0]
+    order = _lib.spatial_order(d["positions"], x3, y3)
+    args = ("sr", d["positions"], d["scales"], d["rotations"], None, d["alphas"], d["colors"], x3, y3, 1e-6)
+    on, wsum_on, ws = _lib.forward(*args, order=order, keep_workspace=True)
+    executed = _lib.read_executed(ws)
+    _lib.set_culling(False)
+    try:
+        off, wsum_off = _lib.forward(*args, order=order)
+    finally:
+        _lib.set_culling(True)
+    plain, wsum_plain = _lib.forward(*args)
+    torch.cuda.synchronize()
+    assert torch.equal(on, off) and torch.equal(wsum_on, wsum_off)
+    assert 0 < executed < 0.5 * B * N * H * W, executed
+    assert _rel(on, plain) < 2e-6 and _rel(wsum_on, wsum_plain) < 2e-6
+    # the same call again: the same bits (the order is deterministic, and so are the sums)
+    again, _ = _lib.forward(*args, order=_lib.spatial_order(d["positions"], x3, y3))
+    assert torch.equal(again, on)
+
+
+def test_ordered_forward_keeps_nan_where_the_reference_has_it():
+    """A NaN position poisons every pixel in the reference (NaN weight); stage boxes must not
+    cull such a gaussian away."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 1000, 64, 96
+    d, _, x, y = _case(B, N, H, W, 3, 0.004, 0.03, seed=51, dev=dev)
+    d["positions"][0, 123, 0] = float("nan")
+    x3, y3 = x[:, 0], y[:, 0]
+    order = _lib.spatial_order(d["positions"], x3, y3)
+    args = ("sr", d["positions"], d["scales"], d["rotations"], None, d["alphas"], d["colors"], x3, y3, 1e-6)
+    with_order, _ = _lib.forward(*args, order=order)
+    without, _ = _lib.forward(*args)
+    assert torch.equal(torch.isnan(with_order), torch.isnan(without))
+    assert bool(torch.isnan(without).all())
+
+
+def _same_with_nans(a, b):
+    return torch.equal(torch.isnan(a), torch.isnan(b)) and torch.equal(torch.nan_to_num(a), torch.nan_to_num(b))
+
+
+@pytest.mark.parametrize("what", ["position", "color", "alpha", "gout"])
+def test_non_finite_values_propagate_as_without_culling(what):
+    """0 * NaN is NaN: skipping a zero weight is only lossless while what it multiplies is
+    finite.  A gaussian with a non-finite parameter therefore reaches every pixel, and a
+    non-finite upstream gradient switches the backward to its dense kernel; either way the
+    NaNs land where the dense kernels (and the reference) put them."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 3000, 96, 160
+    d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.03, seed=61, dev=dev)
+    if what == "position":
+        d["positions"][0, 77, 1] = float("nan")
+    elif what == "color":
+        d["colors"][0, 78, 2] = float("inf")
+    elif what == "alpha":
+        d["alphas"][0, 79] = float("nan")
+    else:
+        gout[0, 1, 40, 50] = float("nan")
+    res = {}
+    for sort in ("off", "on"):
+        for culling in (True, False):
+            _lib.set_backward_sort(sort)
+            _lib.set_culling(culling)
+            try:
+                leaves = {k: v.clone().requires_grad_() for k, v in d.items()}
+                from igs_b200.gs2d import gaussian_splatting_2d
+                out = gaussian_splatting_2d(leaves["positions"], leaves["colors"], leaves["scales"],
+                                            leaves["rotations"], leaves["alphas"], x, y)
+                out.backward(gout)
+                torch.cuda.synchronize()
+                res[(sort, culling)] = (out.detach(), {k: v.grad for k, v in leaves.items()})
+            finally:
+                _lib.set_culling(True)
+                _lib.set_backward_sort("auto")
+    for sort in ("off", "on"):
+        o_on, g_on = res[(sort, True)]
+        o_off, g_off = res[(sort, False)]
+        assert _same_with_nans(o_on, o_off), (what, sort, "image")
+        for k in g_on:
+            assert _same_with_nans(g_on[k], g_off[k]), (what, sort, k)
+    if what in ("position", "alpha"):
+        assert bool(torch.isnan(res[("off", True)][0]).all())  # the reference's image is all NaN here
+    elif what == "color":
+        assert not bool(torch.isfinite(res[("off", True)][0][:, 2]).any())  # ... in the channel that has the inf
+    else:
+        assert bool(torch.isnan(res[("off", True)][1]["positions"]).all())

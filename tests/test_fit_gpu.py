@@ -18,16 +18,24 @@ def _target(H, W, dev, seed=0):
     return img[None].to(dev)
 
 
-def test_fit_reduces_loss_and_graph_matches_eager():
-    from igs_b200 import fit
+@pytest.mark.parametrize("sort", ["off", "on"])
+def test_fit_reduces_loss_and_graph_matches_eager(sort):
+    """(The order policy is pinned: under "auto" the eager run switches to ordered kernels a
+    few steps in, the captured graph keeps what it was captured with, and the two curves
+    then differ by the rounding of two summation orders, amplified over 80 Adam steps.)"""
+    from igs_b200 import _lib, fit
 
     dev = torch.device("cuda", 0)
     tgt = _target(64, 80, dev)
     curves = {}
-    for graph in (False, True):
-        torch.manual_seed(0)
-        model = fit.ImageFitter(400, channels=3).to(dev)
-        curves[graph] = fit.fit(model, tgt, steps=80, lr=1e-2, graph=graph, grad_mode="exact")
+    _lib.set_backward_sort(sort)
+    try:
+        for graph in (False, True):
+            torch.manual_seed(0)
+            model = fit.ImageFitter(400, channels=3).to(dev)
+            curves[graph] = fit.fit(model, tgt, steps=80, lr=1e-2, graph=graph, grad_mode="exact")
+    finally:
+        _lib.set_backward_sort("auto")
     eager, graphed = curves[False], curves[True]
     assert torch.isfinite(eager).all() and torch.isfinite(graphed).all()
     assert eager[-1] < 0.5 * eager[0]
@@ -63,7 +71,7 @@ def test_library_mse_matches_torch(shape):
     ref_out = out.detach().clone().requires_grad_()
     ref = torch.nn.functional.mse_loss(ref_out, tgt)
     (ref * 3.0).backward()
-    assert loss.shape == () and abs(float(loss) - float(ref)) <= 1e-6 * max(1.0, abs(float(ref)))
+    assert loss.shape == () and abs(float(loss.detach()) - float(ref.detach())) <= 1e-6 * max(1.0, abs(float(ref.detach())))
     assert torch.allclose(out.grad, ref_out.grad, rtol=1e-6, atol=1e-12)
     assert torch.equal(fit.mse_loss(out.detach(), tgt), loss.detach())
 

@@ -57,7 +57,7 @@ def _call(lib, static, t, B, N, H, W, C, dev, normalize=1):
         fb, bb = ctypes.c_size_t(0), ctypes.c_size_t(0)
         assert lib.igs_workspace_bytes(B, N, H, W, C, dev.index, ctypes.byref(fb), ctypes.byref(bb)) == 0
         ws = torch.empty(max(fb.value, 256), dtype=torch.uint8, device=dev)
-        rc = lib.igs_forward_sr(*head, _p(ws), ws.numel(), dev.index, stream)
+        rc = lib.igs_forward_sr(*head, None, _p(ws), ws.numel(), dev.index, stream)
     torch.cuda.synchronize(dev)
     return rc, out, wsum
 
