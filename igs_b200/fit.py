@@ -175,3 +175,56 @@ def fit(model, target, steps, lr=1e-2, graph=True, schedule=None, betas=(0.9, 0.
             history[i].copy_(loss)
             i += 1
     return history.cpu()
+
+
+# ---------------------------------------------------------------------------
+# feature -> image experiment with a random number of active features per step
+# ---------------------------------------------------------------------------
+class ProgressiveSplatter(nn.Module):
+    """Learned feature vectors rendered through the module, coarse to fine: the image of the
+    first k features must already resemble the target (the reference's
+    ``ProgressiveGaussianSplatter``, scripts/gs2d_test.py:28-51)."""
+
+    def __init__(self, num_features, feature_dim, gaussians_per_feature, channels=3):
+        super().__init__()
+        self.num_features = int(num_features)
+        self.feature = nn.Parameter(torch.randn(1, num_features, feature_dim))
+        self.gs = GaussianSplatting2D(gaussians_per_feature, feature_dim, channels)
+
+    def forward(self, num_active_features=None, size=None):
+        k = self.num_features if num_active_features is None else min(int(num_active_features), self.num_features)
+        return self.gs(self.feature[:, :k], size)
+
+
+def fit_progressive(model, target, steps, lr=1e-4, chunk=4, ratios=(1 / 16, 1 / 8, 1 / 4, 1 / 2, 1.0),
+                    reg_weight=0.01, clip=0.1, seed=0):
+    """The training loop of the reference's feature -> image experiment
+    (scripts/gs2d_test.py:154-189): every step draws a fraction of the features, renders
+    only those, and steps AdamW on ``reconstruction + reg_weight * koleo(features[:k])``
+    with the gradient norm clipped to ``clip``.  The reconstruction term is L1 + 0.5 MSE
+    (:53-60 without its MS-SSIM term, whose package is not available here).  Returns
+    (losses [steps], the k of every step) on the CPU."""
+    from .reg import koleo_diversity_loss
+
+    if not target.is_cuda:
+        raise RuntimeError("fit_progressive() runs on CUDA tensors only")
+    gen = torch.Generator().manual_seed(seed)
+    opt = torch.optim.AdamW(model.parameters(), lr=lr, eps=EPS)
+    size = target.shape[-2:]
+    n = model.num_features
+    history = torch.zeros(steps, device=target.device)
+    ks = []
+    for i in range(steps):
+        ratio = ratios[int(torch.randint(len(ratios), (1,), generator=gen))]
+        k = int(round(ratio * n / chunk) * chunk)
+        k = max(chunk, min(n, k))
+        ks.append(k)
+        out, _ = model(num_active_features=k, size=size)
+        recon = F.l1_loss(out, target) + 0.5 * mse_loss(out, target)
+        loss = recon + reg_weight * koleo_diversity_loss(model.feature[:, :k])
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
+        opt.step()
+        history[i].copy_(loss.detach())
+    return history.cpu(), ks

@@ -86,3 +86,25 @@ def test_mse_falls_back_to_torch_for_what_the_kernels_do_not_take():
     loss.backward()
     assert torch.allclose(loss, torch.nn.functional.mse_loss(out.detach(), tgt))
     assert out.grad is not None
+
+
+def test_progressive_k_training_loop():
+    """The feature -> image loop with a random number of active features per step: every k
+    of the schedule renders, gradients reach the feature vectors and the projection, and the
+    full-k reconstruction improves."""
+    from igs_b200 import fit
+
+    dev = torch.device("cuda", 0)
+    tgt = _target(64, 64, dev, seed=5)
+    torch.manual_seed(2)
+    model = fit.ProgressiveSplatter(num_features=32, feature_dim=64, gaussians_per_feature=8).to(dev)
+    with torch.no_grad():
+        before = torch.nn.functional.mse_loss(model(size=(64, 64))[0], tgt)
+    hist, ks = fit.fit_progressive(model, tgt, steps=150, lr=2e-3)
+    with torch.no_grad():
+        after = torch.nn.functional.mse_loss(model(size=(64, 64))[0], tgt)
+    assert hist.shape == (150,) and torch.isfinite(hist).all()
+    assert set(ks) <= {4, 8, 16, 32} and len(set(ks)) >= 3
+    assert float(after) < float(before), (float(before), float(after))
+    out, gs_feature = model(num_active_features=8, size=(64, 64))
+    assert out.shape == (1, 3, 64, 64) and gs_feature.shape == (1, 8 * 8, 9)
