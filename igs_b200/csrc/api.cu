@@ -233,6 +233,8 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     }
     p->off_part = off;
     off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
+    p->off_sum = off;
+    off = align_up(off + (size_t)B * p->planes * (size_t)N * sizeof(float), 256);
     p->bytes = off;
     return IGS_OK;
 }
@@ -608,6 +610,15 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     fa.lay = pa.lay;
     fa.B = B; fa.N = N; fa.C = C;
     fa.n_slab = p.n_slab;
+    if (p.n_slab > 4) {
+        // many slabs: add them up with a thread per (plane, gaussian) first -- one thread per
+        // gaussian walking all of them alone keeps too few loads in flight
+        float* sums = reinterpret_cast<float*>(ws + p.off_sum);
+        e = launch_slab_sum(fa.part, sums, p.n_slab, (long long)B * p.planes * N, st);
+        if (e != cudaSuccess) return (int)e;
+        fa.part = sums;
+        fa.n_slab = 1;
+    }
     fa.planes = p.planes;
     fa.n_chunks = p.ch.n;
     fa.kind = kind;

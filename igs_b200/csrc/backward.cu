@@ -425,6 +425,26 @@ __global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
     }
 }
 
+__global__ void __launch_bounds__(256) slab_sum_kernel(const float* __restrict__ part, float* __restrict__ sums,
+                                                       int n_slab, long long per_slab) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= per_slab) return;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n_slab; ++s) acc += part[(long long)s * per_slab + i];
+    sums[i] = acc;
+}
+
+cudaError_t launch_slab_sum(const float* part, float* sums, int n_slab, long long per_slab, cudaStream_t s) {
+    if (per_slab <= 0) return cudaSuccess;
+    {
+        KernelTimer timer(K_FINALIZE, s);
+        slab_sum_kernel<<<(unsigned)((per_slab + 255) / 256), 256, 0, s>>>(part, sums, n_slab, per_slab);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s) {
     const long long n = (long long)a.B * a.N;
     if (n <= 0) return cudaSuccess;

@@ -51,6 +51,7 @@ struct BwdPlan {
     size_t off_geo;
     size_t off_prec[MAX_CHUNKS];
     size_t off_part;       // [n_slab][B][planes][N]
+    size_t off_sum;        // [B][planes][N]: the slab partials added up (when there are many slabs)
     size_t bytes;
 };
 

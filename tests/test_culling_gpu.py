@@ -218,7 +218,7 @@ def test_processing_order_on_general_grid_and_wide_channels():
         assert torch.equal(got[k], want[k]), k
 
 
-def test_auto_policy_learns_that_gaussians_are_narrow():
+def test_auto_policy_learns_that_gaussians_are_narrow(monkeypatch):
     """'auto' starts unsorted, reads the device's narrow count without blocking, and sorts
     from a later call on; from then on the gradients are the same bits call after call, and
     equal to the first call's to rounding."""
@@ -227,6 +227,7 @@ def test_auto_policy_learns_that_gaussians_are_narrow():
     dev = torch.device("cuda", 0)
     B, N, H, W = 1, 4096, 128, 128
     d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.02, seed=31, dev=dev)
+    monkeypatch.setattr(_lib, "AUTO_ORDER_MIN_EVALS", 0)  # small case: lift the size threshold of "auto"
     _lib.set_backward_sort("auto")  # forgets what earlier tests taught it
     first = _backward_with(d, gout, x, y, None)
     probe = _lib._probes[(dev.index, B, N, H, W)]
@@ -243,6 +244,12 @@ def test_auto_policy_learns_that_gaussians_are_narrow():
     for _ in range(4):
         _backward_with(d2, gout2, x2, y2, None)
     assert not _lib._probes[(dev.index, B, N, 100, W)].narrow
+    # and below the size threshold "auto" never orders, whatever the gaussians look like
+    monkeypatch.setattr(_lib, "AUTO_ORDER_MIN_EVALS", 5e8)
+    _lib.set_backward_sort("auto")
+    for _ in range(4):
+        _backward_with(d, gout, x, y, None)
+    assert not _lib._probes
 
 
 @pytest.mark.parametrize("C", [1, 3, 4])
