@@ -46,6 +46,33 @@ def test_error_strings_and_argument_errors_without_gpu():
                               None, None, None, None, 0, 0, None) == -1
 
 
+def test_added_entry_points_validate_arguments_without_gpu():
+    """Null pointers, bad sizes and missing workspaces are refused before any CUDA call."""
+    from igs_b200 import _lib
+
+    lib = _lib.load()
+    strides = (ctypes.c_int64 * 3)(16, 4, 1)
+    one = ctypes.c_void_p(16)  # never dereferenced: every call below fails its argument checks first
+    assert lib.igs_spatial_order(None, one, strides, one, strides, 1, 8, 4, 4, one, one, 1 << 20, 0, None) == -1
+    assert lib.igs_spatial_order(one, one, strides, one, strides, 1, 8, 0, 4, one, one, 1 << 20, 0, None) == -1
+    assert lib.igs_spatial_order(one, one, strides, one, strides, 1, 8, 4, 4, one, None, 0, 0, None) == -2
+    assert lib.igs_spatial_order(one, one, strides, one, strides, 1, 8, 4, 4, one, one, 16, 0, None) == -2
+    assert lib.igs_spatial_order(one, one, strides, one, strides, 0, 8, 4, 4, one, one, 16, 0, None) == 0  # nothing to do
+    assert lib.igs_spatial_order_workspace_bytes(2, 3000) >= 2 * 4096 * 4 + 2 * 3 * 4096 * 4 + 2 * 3000 * 2
+    assert lib.igs_mse_loss(None, one, 10, one, one, 4096, 0, None) == -1
+    assert lib.igs_mse_loss(one, one, 0, one, one, 4096, 0, None) == -1
+    assert lib.igs_mse_loss(one, one, 10, one, one, 16, 0, None) == -2
+    assert lib.igs_mse_grad(one, one, 10, None, None, 0, None) == -1
+    assert lib.igs_read_narrow_count(None, 0, None, None) == -1
+    assert lib.igs_read_executed(None, 0, None, None) == -1
+    assert lib.igs_forward_feature(None, None, one, strides, one, strides, 1, 1, 4, 4, 0, 1e-6, 1, one, one, None,
+                                   one, 1 << 20, 0, None) == -1
+    assert lib.igs_backward_feature(None, None, one, strides, one, strides, one, one, one, 1, 1, 4, 4, 3, 1e-6, 0,
+                                    None, None, one, 1 << 20, 0, None) == -1
+    assert lib.igs_backward_feature(one, None, one, strides, one, strides, one, one, one, 1, 1, 4, 4, 3, 1e-6, 7,
+                                    one, None, one, 1 << 20, 0, None) == -1  # unknown gradient mode
+
+
 def test_product_package_never_imports_the_oracle():
     """The oracle is test infrastructure; nothing under igs_b200/ may reach it."""
     for dirpath, _, files in os.walk(os.path.join(ROOT, "igs_b200")):
