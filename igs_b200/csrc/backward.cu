@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN
         const int slot = a.order ? blockIdx.x * Cfg::GAUSS_PER_CTA + tid * GPT + g
                                  : blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
         n[g] = slot < a.N ? (a.order ? a.order[(long long)b * a.N + slot] : slot) : a.N;
+        if ((unsigned)n[g] > (unsigned)a.N) n[g] = a.N;  // an entry that is no index: the slot stays empty
         const int nn = n[g] < a.N ? n[g] : a.N - 1;
         const float4* gp = reinterpret_cast<const float4*>(a.geo + ((long long)b * a.N + nn) * GEO_FLOATS);
         const float4 g0 = gp[0], g1 = gp[1];

@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
     const long long slot = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     bool narrow = false;
     if (slot < a.M) {
-        const long long i = a.order ? slot / a.N * a.N + a.order[slot] : slot;
+        // (an entry that is no index is clamped: wrong output for a malformed order, never a stray read)
+        const long long i = a.order ? slot / a.N * a.N + min(max(a.order[slot], 0), a.N - 1) : slot;
         const ParamLayout& L = a.lay;
         float px = a.pos[(long long)L.pos_s * i], py = a.pos[(long long)L.pos_s * i + 1];
         if (L.pos_off) {

@@ -139,7 +139,9 @@ int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, floa
  *   finer partition of the rows into slabs (fixed by the shape), so that the few slabs
  *   a patch touches still fill the GPU.  The gradients do not depend on WHICH permutation
  *   is passed, bit for bit; against order == NULL they agree to fp32 rounding (the
- *   per-slab sums associate differently).
+ *   per-slab sums associate differently).  The array must hold a permutation of 0..N-1 per
+ *   batch element; entries outside that range are not followed (that gaussian's gradient
+ *   is then missing), repeated entries make two threads write the same gradient.
  */
 int igs_backward_sr(const float* positions, const float* scales, const float* rotations,
                     const float* alphas, const float* colors, const float* x, const int64_t* x_strides,

@@ -353,3 +353,25 @@ def test_non_finite_values_propagate_as_without_culling(what):
         assert not bool(torch.isfinite(res[("off", True)][0][:, 2]).any())  # ... in the channel that has the inf
     else:
         assert bool(torch.isnan(res[("off", True)][1]["positions"]).all())
+
+
+def test_entries_of_an_order_that_are_no_index_are_not_followed():
+    """A malformed order (entries outside 0..N-1) must not send a kernel outside its arrays:
+    those slots stay empty, every gaussian that is listed still gets its gradient."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 500, 48, 64
+    d, gout, x, y = _case(B, N, H, W, 3, 0.01, 0.2, seed=71, dev=dev)
+    good = _backward_with(d, gout, x, y, _identity(B, N, dev))
+    bad = _identity(B, N, dev).clone()
+    bad[0, 10] = -5
+    bad[0, 20] = N + 3
+    got = _backward_with(d, gout, x, y, bad)
+    keep = torch.ones(N, dtype=torch.bool, device=dev)
+    keep[10] = keep[20] = False
+    for k in good:
+        assert torch.equal(got[k][:, keep], good[k][:, keep]), k
+    out, _, ws = _lib.forward("sr", d["positions"], d["scales"], d["rotations"], None, d["alphas"], d["colors"],
+                              x[:, 0], y[:, 0], 1e-6, order=bad, keep_workspace=True)
+    assert _lib.read_status(ws) == 0 and bool(torch.isfinite(out).all())
