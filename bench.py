@@ -288,15 +288,49 @@ def run_b200(args):
         loss.backward()
         return loss, leaves
 
-    def step_e2e():
-        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        leaves = [d[k].requires_grad_() for k in names]
-        out = gaussian_splatting_2d(*leaves, d["x"], d["y"])
-        loss = torch.nn.functional.mse_loss(out, d["target"])
-        loss.backward()
-        for k, t in zip(names, leaves):
-            grads_host[k].copy_(t.grad, non_blocking=True)
-        loss_host.copy_(loss.detach(), non_blocking=True)
+    # End to end: every step's inputs come from pinned host memory and its gradients and loss
+    # go back there.  The copies of step k+1 are issued on a second stream while step k
+    # computes (two device buffers, events in both directions), the way a training loop with
+    # a prefetching loader runs; the timed region spans the whole loop, first copy included.
+    staged = [{k: torch.empty_like(v) for k, v in on_dev.items()} for _ in range(2)]
+    copy_stream = torch.cuda.Stream(dev)
+    ready = [torch.cuda.Event() for _ in range(2)]
+    free = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[i])  # the step that last used this buffer has finished
+            for k, v in host.items():
+                staged[i][k].copy_(v, non_blocking=True)
+            ready[i].record(copy_stream)
+
+    def run_e2e(n):
+        """n pipelined steps; returns the device time of the whole loop in ms."""
+        main = torch.cuda.current_stream(dev)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        begin.record(main)
+        for ev in free:
+            ev.record(main)  # both buffers are free, and no copy starts before the clock does
+        prefetch(0)
+        for s_ in range(n):
+            i = s_ % 2
+            if s_ + 1 < n:
+                prefetch((s_ + 1) % 2)
+            flush.zero_()
+            main.wait_event(ready[i])
+            d = staged[i]
+            leaves = [d[k].detach().requires_grad_() for k in names]
+            out = gaussian_splatting_2d(*leaves, d["x"], d["y"])
+            loss = torch.nn.functional.mse_loss(out, d["target"])
+            loss.backward()
+            for k, t in zip(names, leaves):
+                grads_host[k].copy_(t.grad, non_blocking=True)
+            loss_host.copy_(loss.detach(), non_blocking=True)
+            free[i].record(main)
+        end.record(main)
+        barrier()
+        return begin.elapsed_time(end)
 
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = sum(v.numel() * v.element_size() for v in grads_host.values()) + 4
@@ -337,8 +371,8 @@ def run_b200(args):
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
     for _ in range(2):
-        step_e2e()
-    e2e_times = timed(step_e2e, steps)
+        run_e2e(1)
+    e2e_total = run_e2e(steps)
 
     # the kernels' bounded waits report through a status word: one more forward, read it
     probe_fwd = _lib.forward("sr", on_dev["positions"], on_dev["scales"], on_dev["rotations"], None, on_dev["alphas"],
@@ -371,7 +405,7 @@ def run_b200(args):
         del probe_bwd
     del probe_fwd
 
-    total_ms = torch.tensor([sum(times), sum(e2e_times)], dtype=torch.float64, device=dev)
+    total_ms = torch.tensor([sum(times), e2e_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = total_ms.tolist()
@@ -453,7 +487,9 @@ def run_b200(args):
             "scaling": "strong" if by_gaussians else "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(cfg, world, by_gaussians),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": total_ms[1] / steps},
+                    "ms_per_step": total_ms[1] / steps,
+                    "timing": "whole loop of `steps` steps incl. the first copy; the inputs of step k+1 are copied "
+                              "on a second stream while step k computes"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roof,
