@@ -379,18 +379,22 @@ def test_headline_identities(headline, dev):
         assert float(unit.max()) <= 1.0 + 1e-6 and float(unit.min()) > 0.99
 
 
+@pytest.mark.parametrize("narrow", [False, True])
+@pytest.mark.parametrize("sort", ["off", "on"])
 @pytest.mark.parametrize("offset", [False, True])
-def test_feature_level_entry_matches_the_parameter_level_one(offset):
+def test_feature_level_entry_matches_the_parameter_level_one(offset, sort, narrow):
     """The module's fused path (kernels read the projection output [B,N,6+C] in place and
     write its whole gradient) against the same computation spelled out with torch ops
     around the parameter-level Function: split, exp + eps, ones, optional offset."""
+    from igs_b200 import _lib
     from igs_b200.gs2d import GaussianSplatting2D, _SplatFromFeature, gaussian_splatting_2d
 
+    _lib.set_backward_sort(sort)  # "on": forward and backward take the gaussians in a spatial order
     dev = torch.device("cuda", 0)
     B, N, C, H, W = 2, 333, 3, 40, 56
     gen = torch.Generator().manual_seed(77)
     feat = torch.randn(B, N, 6 + C, generator=gen) * 0.5
-    feat[..., 2:4] = feat[..., 2:4] - 2.0
+    feat[..., 2:4] = feat[..., 2:4] - (4.5 if narrow else 2.0)  # narrow: the culling kernels run
     off = (torch.rand(B, N, 2, generator=gen) * 0.4 - 0.2) if offset else None
     gout = torch.randn(B, C, H, W, generator=gen).to(dev)
     xg, yg = GaussianSplatting2D.xy_grid((H, W), dev)
@@ -409,6 +413,7 @@ def test_feature_level_entry_matches_the_parameter_level_one(offset):
     out2 = gaussian_splatting_2d(pos, col, torch.exp(log_sc) + 1e-6, rot[..., 0], torch.ones_like(logit[..., 0]), xg, yg)
     out2.backward(gout)
 
+    _lib.set_backward_sort("auto")
     assert_close(_np(out1), _np(out2), 1e-6, "image")
     assert_close(_np(f1.grad), _np(f2.grad), 1e-5, "d_feature")
     assert bool((f1.grad[..., 5] == 0).all())
