@@ -215,7 +215,7 @@ def main():
     module_case(ref, "module_small", 31, 4, 64, 16, 32, 32)
     module_variants_case(ref, "module_variants", 32)
     koleo_case("koleo", 5)
-    # BASELINE config 0 at full size (B=1, N=2048, 256x256, C=3), seed 0
+    # benchmark configuration 0 at full size (B=1, N=2048, 256x256, C=3), seed 0
     render_case(ref, "cfg0_full", 0, 1, 2048, 256, 256, 3, 0.25, 0.75, slim=True)
 
 

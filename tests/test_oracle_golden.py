@@ -62,7 +62,7 @@ def test_kernel_level_entry_both_gradient_modes(dtype):
 
 
 def test_cfg0_full_size():
-    """BASELINE config 0 (B=1, N=2048, 256x256, C=3) against the reference's output."""
+    """Benchmark configuration 0 (B=1, N=2048, 256x256, C=3) against the reference's output."""
     g = load_golden("cfg0_full")
     B, C, H, W = g["out"].shape
     x, y = xy_grid_np(H, W, B)
