@@ -40,6 +40,20 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
     bool bad = false;  // a non-finite upstream term: the skipping kernels must not run
     float ok[2][4], Sp[2][4], gS[2][4];
     long long pp[2][4];
+    // a full block of an image whose rows are a multiple of 4 wide: rows of 4 pixels are
+    // single 16-byte loads (the planes are contiguous, so every such row is aligned)
+    const bool full = (h0 + 1 < a.H) && (w0 + 3 < a.W) && (a.W % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(a.wsum) | reinterpret_cast<uintptr_t>(a.gout) |
+                        reinterpret_cast<uintptr_t>(a.out)) & 15) == 0;
+    auto row4 = [&](const float* plane, int r, float v[4]) {  // plane: [HW] of this batch element / channel
+        if (full) {
+            const float4 t = *reinterpret_cast<const float4*>(plane + pp[r][0]);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = plane[pp[r][k]];
+        }
+    };
 #pragma unroll
     for (int r = 0; r < 2; ++r)
 #pragma unroll
@@ -47,18 +61,31 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
             const bool valid = (h0 + r < a.H) && (w0 + k < a.W);
             ok[r][k] = valid ? 1.f : 0.f;
             pp[r][k] = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + k, a.W - 1);
-            Sp[r][k] = a.wsum[b * HW + pp[r][k]] + a.eps;
-            float acc = 0.f;
-            for (int c = 0; c < a.C; ++c) {
-                const float g = a.gout[(b * a.C + c) * HW + pp[r][k]];
-                if (a.mode == IGS_GRAD_REFERENCE)
-                    acc += g * g;
-                else
-                    acc += (g / Sp[r][k]) * a.out[(b * a.C + c) * HW + pp[r][k]];
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+        row4(a.wsum + b * HW, r, sv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) Sp[r][k] = sv[k] + a.eps;
+        for (int c = 0; c < a.C; ++c) {
+            float g[4], o[4];
+            row4(a.gout + (b * a.C + c) * HW, r, g);
+            if (a.mode == IGS_GRAD_REFERENCE) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] += g[k] * g[k];
+            } else {
+                row4(a.out + (b * a.C + c) * HW, r, o);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] += (g[k] / Sp[r][k]) * o[k];
             }
-            gS[r][k] = ok[r][k] * ((a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp[r][k] * Sp[r][k]) : -acc);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            gS[r][k] = ok[r][k] * ((a.mode == IGS_GRAD_REFERENCE) ? -acc[k] / (Sp[r][k] * Sp[r][k]) : -acc[k]);
             bad |= !isfinite(gS[r][k]);
         }
+    }
 
     for (int q = 0; q < a.ch.n; ++q) {
         const int ct = a.ch.ct[q], cr = a.ch.cr[q], c0 = a.ch.c0[q];
@@ -67,25 +94,30 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
         reinterpret_cast<float4*>(rec)[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
         reinterpret_cast<float4*>(rec)[1] = make_float4(yv[0], yv[1], 0.f, 0.f);
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < 2; ++r) {
+            float* pr0 = rec + 8 + (r * 2) * pf;  // pixel pairs (columns 0,1) and (2,3) of this row
+            float* pr1 = pr0 + pf;
+            pr0[0] = q == 0 ? gS[r][0] : 0.f;
+            pr0[1] = q == 0 ? gS[r][1] : 0.f;
+            pr1[0] = q == 0 ? gS[r][2] : 0.f;
+            pr1[1] = q == 0 ? gS[r][3] : 0.f;
+            for (int c = 0; c < pf / 2 - 1; ++c) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (c < cr) {
+                    float g[4];
+                    row4(a.gout + (b * a.C + c0 + c) * HW, r, g);
 #pragma unroll
-            for (int cp = 0; cp < 2; ++cp) {
-                float* pr = rec + 8 + (r * 2 + cp) * pf;
-                pr[0] = q == 0 ? gS[r][2 * cp] : 0.f;
-                pr[1] = q == 0 ? gS[r][2 * cp + 1] : 0.f;
-                for (int c = 0; c < pf / 2 - 1; ++c) {
-#pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        float v = 0.f;
-                        if (c < cr) {
-                            const int kk = 2 * cp + k;
-                            v = ok[r][kk] * (a.gout[(b * a.C + c0 + c) * HW + pp[r][kk]] / Sp[r][kk]);
-                            bad |= !isfinite(v);
-                        }
-                        pr[2 + 2 * c + k] = v;
+                    for (int k = 0; k < 4; ++k) {
+                        v[k] = ok[r][k] * (g[k] / Sp[r][k]);
+                        bad |= !isfinite(v[k]);
                     }
                 }
+                pr0[2 + 2 * c] = v[0];
+                pr0[3 + 2 * c] = v[1];
+                pr1[2 + 2 * c] = v[2];
+                pr1[3 + 2 * c] = v[3];
             }
+        }
     }
     if (bad && a.flags) atomicOr(a.flags, UPSTREAM_NOT_FINITE);
 }

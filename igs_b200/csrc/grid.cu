@@ -7,17 +7,41 @@
 namespace igs {
 
 __global__ void __launch_bounds__(256) grid_check_kernel(GridCheckArgs a) {
-    const long long HW = (long long)a.H * a.W;
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*HW
+    // a thread checks four consecutive pixels of one row (one 16-byte load per array when the
+    // rows are contiguous and aligned, which is the materialised-grid case this kernel exists for)
+    const long long quads_w = (a.W + 3) / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*H*quads_w
     bool bad = false;
-    if (i < (long long)a.B * HW) {
-        const long long b = i / HW, p = i - b * HW;
-        const long long h = p / a.W, w = p - h * a.W;
-        const float xv = a.x[b * a.xs_b + h * a.xs_h + w * a.xs_w];
-        const float yv = a.y[b * a.ys_b + h * a.ys_h + w * a.ys_w];
+    if (i < (long long)a.B * a.H * quads_w) {
+        const long long b = i / (a.H * quads_w), r = i - b * a.H * quads_w;
+        const long long h = r / quads_w, w0 = (r - h * quads_w) * 4;
+        const float* xr = a.x + b * a.xs_b + h * a.xs_h;  // this row
+        const float* yr = a.y + b * a.ys_b + h * a.ys_h;
+        const float* x0 = a.x + b * a.xs_b;               // row 0
+        const float y0 = yr[0];                            // column 0 of this row
+        float xv[4], yv[4], xf[4];
+        const bool vec = a.xs_w == 1 && a.ys_w == 1 && w0 + 3 < a.W &&
+                         ((reinterpret_cast<uintptr_t>(xr + w0) | reinterpret_cast<uintptr_t>(yr + w0) |
+                           reinterpret_cast<uintptr_t>(x0 + w0)) & 15) == 0;
+        if (vec) {
+            const float4 vx = *reinterpret_cast<const float4*>(xr + w0), vy = *reinterpret_cast<const float4*>(yr + w0);
+            const float4 vf = *reinterpret_cast<const float4*>(x0 + w0);
+            xv[0] = vx.x; xv[1] = vx.y; xv[2] = vx.z; xv[3] = vx.w;
+            yv[0] = vy.x; yv[1] = vy.y; yv[2] = vy.z; yv[3] = vy.w;
+            xf[0] = vf.x; xf[1] = vf.y; xf[2] = vf.z; xf[3] = vf.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const long long w = w0 + k < a.W ? w0 + k : a.W - 1;
+                xv[k] = xr[w * a.xs_w];
+                yv[k] = yr[w * a.ys_w];
+                xf[k] = x0[w * a.xs_w];
+            }
+        }
         // bit comparison: the separable kernels must see exactly the values the general
         // one would (a NaN coordinate simply selects the general kernel)
-        bad = (xv != a.x[b * a.xs_b + w * a.xs_w]) || (yv != a.y[b * a.ys_b + h * a.ys_h]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bad |= (xv[k] != xf[k]) || (yv[k] != y0);
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.flag, GRID_NOT_SEPARABLE);
 }
@@ -31,7 +55,7 @@ GridKind classify_grid(long long xs_h, long long ys_w, int H, int W, bool kernel
 }
 
 cudaError_t launch_grid_check(const GridCheckArgs& a, cudaStream_t s) {
-    const long long n = (long long)a.B * a.H * a.W;
+    const long long n = (long long)a.B * a.H * ((a.W + 3) / 4);
     cudaError_t e = cudaMemsetAsync(a.flag, 0, sizeof(int), s);
     if (e != cudaSuccess || n <= 0) return e;
     {
