@@ -23,8 +23,14 @@ namespace igs {
 __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
     if (a.grid_sel && (*a.grid_sel & GRID_NOT_SEPARABLE)) return;
     const long long per_b = (long long)a.nrp * a.ncb;
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*nrp*ncb
-    if (i >= (long long)a.B * per_b) return;
+    // Records are built in shared memory and written out by the whole CTA in consecutive
+    // 16-byte pieces: a thread storing its own 160-byte record leaves every store instruction
+    // of the warp scattered over 32 half-used sectors.
+    extern __shared__ __align__(16) float s_rec[];  // [blockDim.x][record floats]
+    const long long total = (long long)a.B * per_b;
+    const long long i_raw = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*nrp*ncb
+    const bool in_range = i_raw < total;
+    const long long i = in_range ? i_raw : total - 1;  // threads past the end redo the last block, and store nothing
     const long long b = i / per_b, blk = i - b * per_b;
     const int rp = (int)(blk / a.ncb), cbk = (int)(blk - (long long)rp * a.ncb);
     const long long HW = (long long)a.H * a.W;
@@ -90,7 +96,8 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
     for (int q = 0; q < a.ch.n; ++q) {
         const int ct = a.ch.ct[q], cr = a.ch.cr[q], c0 = a.ch.c0[q];
         const int pf = bwd_sep_pair_floats(ct);
-        float* rec = a.prec[q] + i * bwd_sep_rec_floats(ct);
+        const int rs = bwd_sep_rec_floats(ct);
+        float* rec = s_rec + (size_t)threadIdx.x * rs;
         reinterpret_cast<float4*>(rec)[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
         reinterpret_cast<float4*>(rec)[1] = make_float4(yv[0], yv[1], 0.f, 0.f);
 #pragma unroll
@@ -118,6 +125,15 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
                 pr1[3 + 2 * c] = v[3];
             }
         }
+        __syncthreads();
+        {
+            const long long first = (long long)blockIdx.x * blockDim.x;
+            const long long n_here = total - first < (long long)blockDim.x ? total - first : (long long)blockDim.x;
+            float4* dst = reinterpret_cast<float4*>(a.prec[q] + first * rs);
+            const float4* src4 = reinterpret_cast<const float4*>(s_rec);
+            for (long long j = threadIdx.x; j < n_here * (rs / 4); j += blockDim.x) dst[j] = src4[j];
+        }
+        __syncthreads();
     }
     if (bad && a.flags) atomicOr(a.flags, UPSTREAM_NOT_FINITE);
 }
@@ -127,7 +143,9 @@ cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s) {
     if (n <= 0) return cudaSuccess;
     {
         KernelTimer timer(K_PIXEL_TERMS, s);
-        pixel_terms_sep_kernel<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(a);
+        int max_rs = 0;
+        for (int q = 0; q < a.ch.n; ++q) max_rs = max(max_rs, bwd_sep_rec_floats(a.ch.ct[q]));
+        pixel_terms_sep_kernel<<<(unsigned)((n + 127) / 128), 128, (size_t)128 * max_rs * sizeof(float), s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
