@@ -237,6 +237,18 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
     p->off_sum = off;
     off = align_up(off + (size_t)B * p->planes * (size_t)N * sizeof(float), 256);
+    p->part_bytes = (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float);
+    p->off_tasks = off;
+    p->task_capacity = 0;
+    if (p->sep_ok) {
+        const long long groups32 = ((long long)N + 31) / 32;
+        const long long cap = (long long)B * groups32 * n_slab_max;
+        if (cap <= 0x7fffffffLL / 2) {
+            p->task_capacity = (int)cap;
+            off = align_up(off + (size_t)cap * sizeof(int4), 256);
+            off = align_up(off + (size_t)B * groups32 * sizeof(int4), 256);
+        }
+    }
     p->bytes = off;
     return IGS_OK;
 }
@@ -580,13 +592,30 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.moment_plane0 = N_MOMENTS * k;
         ba.color_plane0 = N_MOMENTS * p.ch.n;
         if (grid_kind != GRID_GENERAL) {
+            const bool queued = order && p.task_capacity > 0 && ba.cull_sel;
+            if (queued) {
+                // The ordered skipping path writes partial sums only for the (group, slab) pairs
+                // that have a task; the others are exact zeros.  Cleared before ANY of the
+                // kernels below runs: whichever one the device selects writes after this.
+                e = cudaMemsetAsync(ba.part, 0, p.part_bytes, st);
+                if (e != cudaSuccess) return (int)e;
+            }
             e = launch_backward_chunk(p.ch.ct[k], true, false, ba, p, st);
             if (e != cudaSuccess) return (int)e;
             if (ba.cull_sel) {
                 // the skipping kernel: with a processing order, the one whose warps each follow
                 // their own gaussians' reach; without, the one that skips per CTA
-                e = order ? launch_backward_warp_chunk(p.ch.ct[k], ba, p, st)
-                          : launch_backward_chunk(p.ch.ct[k], true, true, ba, p, st);
+                if (queued) {
+                    ba.tasks = reinterpret_cast<int4*>(ws + p.off_tasks);
+                    ba.group_rect = reinterpret_cast<int4*>(
+                        ws + align_up(p.off_tasks + (size_t)p.task_capacity * sizeof(int4), 256));
+                    ba.task_count = reinterpret_cast<int*>(ws) + TASK_COUNT_WORD;
+                    ba.task_next = reinterpret_cast<int*>(ws) + TASK_NEXT_WORD;
+                    ba.task_capacity = p.task_capacity;
+                    e = launch_backward_warp_chunk(p.ch.ct[k], ba, p, sm_count(device), st);
+                } else {
+                    e = launch_backward_chunk(p.ch.ct[k], true, true, ba, p, st);
+                }
                 if (e != cudaSuccess) return (int)e;
             }
         }

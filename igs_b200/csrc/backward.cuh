@@ -36,6 +36,12 @@ struct BwdArgs {
     // unless the word picks it.
     const int* grid_sel;   // grid word: bit 0 = not a separable grid -> general / separable kernel
     unsigned long long* exec_count;  // skipping kernel: evaluations it did not skip (may be null)
+    // task list of the ordered skipping path (backward_warp.cu); nullptr elsewhere
+    int4* tasks;        // [task_capacity]: {batch element, group of 32 slots, slab, -}
+    int4* group_rect;   // [B, ceil(N/32)]: rows lo..hi and column blocks lo..hi the group's box meets
+    int* task_count;    // tasks on the list
+    int* task_next;     // next task to hand out
+    int task_capacity;
     const int* cull_sel;   // count of narrow gaussians: at least one in eight (and monotone axes,
     const int* grid_word;  //   bit 1 of the grid word clear) -> skipping / plain separable kernel
     long long npairs, pairs_per_slab;
@@ -89,7 +95,7 @@ cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const Bw
 bool backward_has_separable(int ct);
 cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
 cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
-cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
+cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, int sm_count, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
 // sums[i] = part[0][i] + part[1][i] + ... (in that order), i over per_slab elements
 cudaError_t launch_slab_sum(const float* part, float* sums, int n_slab, long long per_slab, cudaStream_t s);

@@ -38,6 +38,8 @@ constexpr int STATUS_WORD = 0;       // kernels: a bounded wait gave up
 constexpr int GRID_FLAG_WORD = 1;    // bit 0 = grid not separable, bit 1 = axes not monotone, bit 2 = upstream not finite
 constexpr int NARROW_COUNT_WORD = 2; // pack: gaussians whose reach is well inside the image
 constexpr int EXEC_COUNT_WORD = 4;   // (64 bits) culling kernels: (gaussian, pixel) evaluations not skipped
+constexpr int TASK_COUNT_WORD = 6;   // ordered backward: tasks on its list ...
+constexpr int TASK_NEXT_WORD = 7;    // ... and the next one to hand out
 constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2;
 // Skipping a term w * t because w is exactly zero is only lossless while t is finite
 // (0 * NaN and 0 * inf are NaN).  Gaussians with a non-finite parameter get an infinite box

@@ -52,6 +52,9 @@ struct BwdPlan {
     size_t off_prec[MAX_CHUNKS];
     size_t off_part;       // [n_slab][B][planes][N]
     size_t off_sum;        // [B][planes][N]: the slab partials added up (when there are many slabs)
+    size_t off_tasks;      // ordered skipping path: [task_capacity] int4, then [B][ceil(N/32)] int4
+    int task_capacity;     // B * ceil(N/32) * (most slabs either partition has); 0 without separable kernels
+    size_t part_bytes;     // size of the partial sums of the partition in use
     size_t bytes;
 };
 
