@@ -185,16 +185,20 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     const long long slots = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
     const long long base = groups * (B > 0 ? B : 1);
     const int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);
-    // Fine partition: slabs of 8 row pairs (16 above 32768 gaussians, 32 above 262144: with
-    // more gaussian groups there are enough tasks already, and every (group, slab) pair that
-    // turns out idle still costs a CTA launch), at most 96 of them, never fewer than the plain
+    // Fine partition: slabs of 8 row pairs, at most 96 of them, never fewer than the plain
     // partition has.  A function of the shape alone, like the plain one, so the result's bits
     // depend on whether an order was passed but not on the order or on the gaussians.
-    // Measured, narrow gaussians at 1024 x 1024: N = 16384: 0.54 / 0.55 / 0.64 ms for 4 / 8 / 16
-    // row pairs; N = 65536: 0.72 / 0.65 / 0.68 ms for 8 / 16 / 32.
+    // (Group, slab) pairs without work cost nothing -- the ordered path hands out tasks from a
+    // list -- so short slabs only add partial sums to add up.  Measured, narrow gaussians at
+    // 1024 x 1024, skipping kernel: N = 16384: 0.43 / 0.44 / 0.50 ms for 4 / 8 / 16 row pairs;
+    // N = 65536: 0.47 / 0.48 / 0.51 ms, the step as a whole being fastest at 8.
     int ns_fine = ns;
     if (p->sep_ok) {
-        const int rp_fine = N <= 32768 ? 8 : (N <= 262144 ? 16 : 32);
+#ifdef IGS_FINE_RP
+        const int rp_fine = IGS_FINE_RP;
+#else
+        const int rp_fine = 8;
+#endif
         const int want = (p->nrp + rp_fine - 1) / rp_fine;
         ns_fine = want < 96 ? want : 96;
         if (ns_fine < ns) ns_fine = ns;

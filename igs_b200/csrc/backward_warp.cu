@@ -38,10 +38,10 @@ namespace igs {
 #define IGS_BWDW_THREADS 64
 #endif
 #ifndef IGS_BWDW_MINCTAS
-#define IGS_BWDW_MINCTAS 10
+#define IGS_BWDW_MINCTAS 8  // 16 warps per SM at 126 registers (10: 96 registers and a spill, slower)
 #endif
 #ifndef IGS_BWDW_STAGE
-#define IGS_BWDW_STAGE 16
+#define IGS_BWDW_STAGE 32
 #endif
 
 template <int CT>
