@@ -323,10 +323,12 @@ def order_by_policy(pos, feat, pos_off, x3, y3):
     dev = x3.device
     probe = None
     if _BACKWARD_SORT == "auto":
-        if B * N * H * W < AUTO_ORDER_MIN_EVALS:
-            return None, None
         probe = _probes.setdefault((dev.index, B, N, H, W), _NarrowProbe())
         if not probe.poll(B * N):
+            return None, probe
+        # small problems: ordering costs an eager step more on the host than it saves on the
+        # device; inside a graph capture the host cost is paid once, so there it always pays
+        if B * N * H * W < AUTO_ORDER_MIN_EVALS and not torch.cuda.is_current_stream_capturing():
             return None, probe
     if pos is None:
         pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off

@@ -244,12 +244,14 @@ def test_auto_policy_learns_that_gaussians_are_narrow(monkeypatch):
     for _ in range(4):
         _backward_with(d2, gout2, x2, y2, None)
     assert not _lib._probes[(dev.index, B, N, 100, W)].narrow
-    # and below the size threshold "auto" never orders, whatever the gaussians look like
+    # below the size threshold "auto" still learns, but orders only inside a graph capture
     monkeypatch.setattr(_lib, "AUTO_ORDER_MIN_EVALS", 5e8)
     _lib.set_backward_sort("auto")
     for _ in range(4):
         _backward_with(d, gout, x, y, None)
-    assert not _lib._probes
+    assert _lib._probes[(dev.index, B, N, H, W)].narrow
+    order, _ = _lib.order_by_policy(d["positions"], None, None, x[:, 0], y[:, 0])
+    assert order is None
 
 
 @pytest.mark.parametrize("C", [1, 3, 4])
