@@ -277,13 +277,13 @@ static Strides get_strides(const int64_t* s, int H, int W) {
 // ---- lossless culling switch (igs_set_culling) ----
 static std::atomic<int> g_culling{1};
 
-// Classifies the sample grid (GridKind) and initialises the status area's grid word:
-// launches the separability check when the strides do not settle the question.
+// Classifies the sample grid (GridKind); launches the separability check when the strides do
+// not settle the question.  The caller has cleared the status area (grid word included).
 static cudaError_t prepare_grid(unsigned char* ws, const float* x, const float* y, const Strides& sx, const Strides& sy,
                                 int B, int H, int W, bool separable_available, GridKind* kind, cudaStream_t st) {
     int* flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
     *kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && separable_available);
-    if (*kind != GRID_CHECK_ON_DEVICE) return cudaMemsetAsync(flag, 0, sizeof(int), st);
+    if (*kind != GRID_CHECK_ON_DEVICE) return cudaSuccess;
     GridCheckArgs ga;
     ga.x = x; ga.y = y;
     ga.xs_b = sx.b; ga.xs_h = sx.h; ga.xs_w = sx.w;

@@ -51,6 +51,14 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
     const bool full = (h0 + 1 < a.H) && (w0 + 3 < a.W) && (a.W % 4 == 0) &&
                       ((reinterpret_cast<uintptr_t>(a.wsum) | reinterpret_cast<uintptr_t>(a.gout) |
                         reinterpret_cast<uintptr_t>(a.out)) & 15) == 0;
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const bool valid = (h0 + r < a.H) && (w0 + k < a.W);
+            ok[r][k] = valid ? 1.f : 0.f;
+            pp[r][k] = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + k, a.W - 1);
+        }
     auto row4 = [&](const float* plane, int r, float v[4]) {  // plane: [HW] of this batch element / channel
         if (full) {
             const float4 t = *reinterpret_cast<const float4*>(plane + pp[r][0]);
@@ -60,14 +68,6 @@ __global__ void __launch_bounds__(128) pixel_terms_sep_kernel(PixelTermArgs a) {
             for (int k = 0; k < 4; ++k) v[k] = plane[pp[r][k]];
         }
     };
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const bool valid = (h0 + r < a.H) && (w0 + k < a.W);
-            ok[r][k] = valid ? 1.f : 0.f;
-            pp[r][k] = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + k, a.W - 1);
-        }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float sv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};

@@ -163,10 +163,7 @@ cudaError_t launch_pack(const PackArgs& a, cudaStream_t s) {
     if (a.M <= 0) return cudaSuccess;
     const int threads = 256;
     const long long blocks = (a.M + threads - 1) / threads;
-    if (a.narrow_count) {
-        cudaError_t e = cudaMemsetAsync(a.narrow_count, 0, sizeof(int), s);
-        if (e != cudaSuccess) return e;
-    }
+    // (a.narrow_count and a.grid_flag are words of the status area, which the caller cleared)
     {
         KernelTimer timer(K_PACK, s);
         pack_kernel<<<(unsigned)blocks, threads, 0, s>>>(a);
