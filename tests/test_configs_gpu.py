@@ -188,3 +188,22 @@ def test_module_optional_inputs_match_reference_fixture(tag, dev):
     assert_close(_np(m.proj.weight.grad), g[f"{tag}_g_weight"], TOL, f"{tag} d_weight")
     assert_close(_np(m.proj.bias.grad), g[f"{tag}_g_bias"], TOL, f"{tag} d_bias")
     assert_close(_np(feat.grad), g[f"{tag}_g_feature"], TOL, f"{tag} d_feature")
+
+
+@pytest.mark.parametrize("name", ["narrow", "narrow64k"])
+def test_narrow_workloads_ordered_culling_path_against_the_oracle(name, dev):
+    """The image-compression regime at full size (16384 / 65536 narrow gaussians on a
+    1024x1024 grid), forward and backward taking the gaussians in a spatial order: stage
+    lists in the forward, the task queue in the backward, 97-99 % of the pairs skipped.
+    Image at sampled pixels and gradients of sampled gaussians against the fp64 oracle,
+    which skips nothing."""
+    from igs_b200 import _lib, workloads
+
+    cfg = workloads.CONFIGS[name]
+    d = workloads.draw(cfg, device=dev)
+    _lib.set_backward_sort("on")
+    try:
+        out, gout, grads, _ = _render_and_backward(d, lambda o: torch.nn.functional.mse_loss(o, d["target"]))
+    finally:
+        _lib.set_backward_sort("auto")
+    subset_check(d, out, gout, grads, n_pix=128, n_gauss=16, seed=7)
