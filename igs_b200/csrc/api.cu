@@ -102,10 +102,17 @@ int make_chunks(int C, Chunks* out) {
 }
 
 // Picks the count (1..max_parts) of equal parts along the streamed axis that wastes the
-// fewest CTA slots in the last wave; ties go to the smaller count.
-static int pick_parts(long long base_ctas, long long slots, long long axis_len, long long min_len, int max_parts) {
-    int best = 1;
-    double best_eff = -1.0;
+// fewest CTA slots in the last wave (ties go to the smaller count).  `run_slots` are the CTA
+// slots of the kernel that will actually run: if the choice gives it fewer than four waves,
+// a deeper one (eight to sixteen waves) is taken instead -- CTAs do not finish in lockstep,
+// so with one or two waves the slowest SM sets the time (measured on B=1, N=16384, 512 x 512,
+// backward: 2.47 / 2.45 / 2.29 / 2.24 / 2.23 ms at 1 / 2 / 3 / 4 / 8 waves; at seven waves and
+// more the count no longer matters: 4.39-4.44 ms for 8 to 32 slabs on B=16, N=8192, 256 x 256).
+static int pick_parts(long long base_ctas, long long slots, long long axis_len, long long min_len, int max_parts,
+                      long long run_slots = 0) {
+    if (run_slots <= 0) run_slots = slots;
+    int best = 1, best_deep = 0;
+    double best_eff = -1.0, best_deep_eff = -1.0;
     for (int s = 1; s <= max_parts; ++s) {
         if (s > 1 && axis_len / s < min_len) break;
         const long long ctas = base_ctas * s;
@@ -115,7 +122,14 @@ static int pick_parts(long long base_ctas, long long slots, long long axis_len, 
             best_eff = eff;
             best = s;
         }
+        const long long run_waves = (ctas + run_slots - 1) / run_slots;
+        const double run_eff = (double)ctas / (double)(run_waves * run_slots);
+        if (run_waves >= 8 && run_waves <= 16 && run_eff > best_deep_eff + 0.02) {
+            best_deep_eff = run_eff;
+            best_deep = s;
+        }
     }
+    if (best_deep && base_ctas * best < 4 * run_slots) return best_deep;
     return best;
 }
 
@@ -165,7 +179,7 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
     return IGS_OK;
 }
 
-int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs) {
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs, bool separable_grid) {
     if (B < 0 || N < 0 || H < 0 || W < 0) return IGS_ERR_ARG;
     if (B > 65535) return IGS_ERR_LIMIT;
     int rc = make_chunks(C, &p->ch);
@@ -182,9 +196,21 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     p->sep_ok = (p->ch.n == 1 && backward_has_separable(ct)) ? 1 : 0;
     const long long per_cta = (long long)p->threads * p->gauss_per_thread;
     const long long groups = ((long long)N + per_cta - 1) / per_cta;
-    const long long slots = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
     const long long base = groups * (B > 0 ? B : 1);
-    const int ns = pick_parts(base > 0 ? base : 1, slots, p->npairs, 2LL * p->chunk_pairs, 256);
+    // The slab count is chosen for the general kernel's occupancy; when the separable kernel
+    // will run (it holds fewer CTAs per SM: more registers) and would get fewer than four
+    // waves, a deeper count is taken.  The workspace covers both.
+    const long long slots_gen = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
+    const int ns_gen = pick_parts(base > 0 ? base : 1, slots_gen, p->npairs, 2LL * p->chunk_pairs, 256);
+    int ns_sep = ns_gen;
+    if (p->sep_ok) {
+        const int per_sm = backward_sep_ctas_per_sm(ct, device);
+        if (per_sm > 0)
+            ns_sep = pick_parts(base > 0 ? base : 1, slots_gen, p->npairs, 2LL * p->chunk_pairs, 256,
+                                (long long)sm_count(device) * per_sm);
+    }
+    const int ns = (separable_grid && p->sep_ok) ? ns_sep : ns_gen;
+    const int ns_other = (separable_grid && p->sep_ok) ? ns_gen : ns_sep;  // covered by the workspace size
     // Fine partition: slabs of 8 row pairs, at most 96 of them, never fewer than the plain
     // partition has.  A function of the shape alone, like the plain one, so the result's bits
     // depend on whether an order was passed but not on the order or on the gaussians.
@@ -218,7 +244,11 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     const bool fine = fine_slabs && ns_fine > n_plain;
     p->pairs_per_slab = fine ? per_fine : per_plain;
     p->n_slab = fine ? ns_fine : n_plain;
-    const int n_slab_max = ns_fine > n_plain ? ns_fine : n_plain;
+    // the most slabs any of the partitions can have, whichever kernel the grid selects: the
+    // workspace size must not depend on that choice
+    int n_slab_max = ns_gen > ns_sep ? ns_gen : ns_sep;
+    if (ns_fine > n_slab_max) n_slab_max = ns_fine;
+    (void)ns_other;
     p->planes = N_MOMENTS * p->ch.n + C;
     // separable variant: same slab count, slabs are ranges of whole row pairs
     p->rp_per_slab = (p->nrp + p->n_slab - 1) / p->n_slab;
@@ -508,15 +538,18 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         return (int)e;
     }
 
+    // which kernel family will (probably) run is known from the strides, or assumed separable
+    // when the data has to be checked on the device (a materialised xy_grid)
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    const bool likely_separable = classify_grid(sx.h, sy.w, H, W, separable_enabled()) != GRID_GENERAL;
     BwdPlan p;
-    rc = plan_backward(B, N, H, W, C, device, &p, order != nullptr);
+    rc = plan_backward(B, N, H, W, C, device, &p, order != nullptr, likely_separable);
     if (rc) return rc;
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
     if (e != cudaSuccess) return (int)e;
 
-    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
     // separable grid?  (same decision procedure as the forward)
     int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
     GridKind grid_kind;

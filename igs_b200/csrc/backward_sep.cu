@@ -558,6 +558,35 @@ static cudaError_t launch_sep_one(const BwdArgs& a, const BwdPlan& p, cudaStream
     return cudaGetLastError();
 }
 
+template <int CT>
+static int sep_occ(int device) {
+    using Cfg = BwdSepCfg<CT>;
+    static int cached[64];
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
+    cudaFuncSetAttribute(splat_backward_sep_kernel<CT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)Cfg::SMEM);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, splat_backward_sep_kernel<CT, false>, Cfg::THREADS,
+                                                      Cfg::SMEM) != cudaSuccess ||
+        n <= 0) {
+        cudaGetLastError();
+        n = Cfg::MIN_CTAS;
+    }
+    if (device >= 0 && device < 64) cached[device] = n;
+    return n;
+}
+
+// CTAs of the plain separable kernel an SM holds (the plan sizes its slab count by it)
+int backward_sep_ctas_per_sm(int ct, int device) {
+    switch (ct) {
+        case 1: return sep_occ<1>(device);
+        case 2: return sep_occ<2>(device);
+        case 3: return sep_occ<3>(device);
+        case 4: return sep_occ<4>(device);
+    }
+    return 0;
+}
+
 // instantiations exist for single-chunk channel counts up to 4, two gaussians per thread
 bool backward_has_separable(int ct) { return ct <= 4 && backward_gauss_per_thread(ct) == BwdSepCfg<3>::GPT; }
 

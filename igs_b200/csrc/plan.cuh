@@ -63,7 +63,10 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p);
 // fine_slabs: the partition used when the caller passes a spatial order (many short slabs, so
 // that the few slabs each gaussian group reaches still fill the machine).  The workspace
 // size covers both partitions.
-int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs = false);
+// separable_grid: size the plain slab count for the separable kernel's occupancy (the kernel
+// that will run) instead of the general kernel's.
+int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, bool fine_slabs = false,
+                  bool separable_grid = false);
 
 // Where the per-gaussian parameters live.  The default is the reference's separate
 // contiguous tensors; the feature-level entry points point all of them into the rows of one
@@ -86,6 +89,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);
 int backward_ctas_per_sm(int ct, int device);
+int backward_sep_ctas_per_sm(int ct, int device);
 int forward_px_per_thread(int ct);
 int forward_threads(int ct);
 int forward_chunk_g(int ct);
