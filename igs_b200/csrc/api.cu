@@ -227,6 +227,10 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
 #endif
         const int want = (p->nrp + rp_fine - 1) / rp_fine;
         ns_fine = want < 96 ? want : 96;
+        // the partial sums grow with slabs x gaussians: keep them under half a gigabyte
+        const long long per_slab_bytes = (long long)(B > 0 ? B : 1) * (N_MOMENTS * p->ch.n + C) * (long long)N * 4;
+        const long long fit = per_slab_bytes > 0 ? (512LL << 20) / per_slab_bytes : ns_fine;
+        if (fit < ns_fine) ns_fine = (int)(fit > 1 ? fit : 1);
         if (ns_fine < ns) ns_fine = ns;
     }
     auto slabs_for = [&](int parts, long long* per_out) {
