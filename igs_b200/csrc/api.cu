@@ -391,7 +391,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     const bool culling_on = g_culling.load(std::memory_order_relaxed);
     if (order && culling_on && !use_plan && p.tiles_sep > 0 && (long long)p.tiles_sep * B >= sm_count(device) &&
-        (N + p.chunk_g - 1) / p.chunk_g <= 1024 /* what a CTA can list */) {
+        (N + p.chunk_g - 1) / p.chunk_g <= 8192 /* what a CTA can list */) {
         // A caller that passes an order expects narrow gaussians: a CTA then streams a few
         // stages only, and splitting the gaussians over several CTAs per tile would just add
         // partial sums to write and add up.  (A function of the shape and of whether an order

@@ -54,15 +54,15 @@ struct FwdCfg {
     // The culling kernel spends little time per stage (most gaussians are skipped), so the
     // latency of a stage's copy shows unless more copies are in flight.
     static constexpr int STAGES_CULL = 4;
-    static constexpr int LIST_CAP = 1024;  // stages a CTA can list (ordered calls): 131072 gaussians per split
+    static constexpr int LIST_CAP = 8192;  // stages a CTA can list (ordered calls): 2^20 gaussians per split
     // stages | mbarriers | flags (16 B) | surviving-gaussian list of the current stage | per-warp scratch |
     // list of the stages whose box meets the CTA's pixels
-    static constexpr size_t smem_bytes(int stages) {
+    static constexpr size_t smem_bytes(int stages, int list_cap) {
         return (size_t)stages * CHUNK_G * RS * sizeof(float) + stages * sizeof(uint64_t) + 16 +
-               CHUNK_G * sizeof(unsigned short) + 8 * 4 * sizeof(float) + LIST_CAP * sizeof(unsigned short);
+               CHUNK_G * sizeof(unsigned short) + 8 * 4 * sizeof(float) + list_cap * sizeof(unsigned short);
     }
-    static constexpr size_t SMEM = smem_bytes(STAGES);
-    static constexpr size_t SMEM_CULL = smem_bytes(STAGES_CULL);
+    static constexpr size_t SMEM = smem_bytes(STAGES, 1024);  // (the plain kernels never list)
+    static constexpr size_t SMEM_CULL = smem_bytes(STAGES_CULL, LIST_CAP);
 };
 
 // Separable tiles: 16 rows x 64 columns per CTA, 2 rows x 4 columns per thread.
