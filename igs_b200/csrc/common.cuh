@@ -113,7 +113,7 @@ __device__ __forceinline__ f2 ex2_2(f2 q) {
 }
 
 // ---------------------------------------------------------------------------
-// mbarrier + bulk copy (global -> shared, no multicast), every wait bounded
+// mbarrier + bulk copy (global -> shared, this CTA only), every wait bounded
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
