@@ -11,15 +11,19 @@ import ctypes
 import functools
 import os
 import threading
+import weakref
 
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# IGS_B200_LIB: development override, a differently tuned build of the same library
-LIB_PATH = os.environ.get("IGS_B200_LIB") or os.path.join(_HERE, "libigs_b200.so")
+LIB_PATH = os.path.join(_HERE, "libigs_b200.so")
 
 GRAD_REFERENCE = 0
 GRAD_EXACT = 1
+# `hints` of the forward / backward entry points (include/igs_b200.h)
+HINT_WIDE_GAUSSIANS = 1
+HINT_GENERAL_GRID = 2
+STATUS_WORDS = 8
 
 _lock = threading.Lock()
 _lib = None
@@ -34,16 +38,21 @@ SIGNATURES = {
     "igs_strerror": (ctypes.c_char_p, [_i]),
     "igs_launch_count": (ctypes.c_longlong, []),
     "igs_workspace_bytes": (_i, [_i] * 6 + [ctypes.POINTER(_sz)] * 2),
-    "igs_forward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "igs_forward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "igs_forward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _i, _vp, _sz, _i, _vp]),
+    "igs_forward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _i, _vp, _sz, _i, _vp]),
     "igs_forward_sr_static": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _i, _vp]),
     "igs_normalize": (_i, [_vp] + [_i] * 4 + [_f, _vp, _vp, _i, _vp]),
-    "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9 + [_sz, _i, _vp]),
-    "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 10 + [_sz, _i, _vp]),
-    "igs_forward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "igs_backward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 3
-                             + [_sz, _i, _vp]),
+    "igs_backward_sr": (_i, [_vp] * 6 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 8
+                        + [_i, _vp, _sz, _i, _vp]),
+    "igs_backward_cov": (_i, [_vp] * 7 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 9
+                         + [_i, _vp, _sz, _i, _vp]),
+    "igs_forward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_i] * 5 + [_f, _i, _vp, _vp, _vp, _i, _vp, _sz, _i,
+                                                                           _vp]),
+    "igs_backward_feature": (_i, [_vp] * 3 + [_I64, _vp, _I64] + [_vp] * 3 + [_i] * 5 + [_f, _i] + [_vp] * 2
+                             + [_i, _vp, _sz, _i, _vp]),
     "igs_read_status": (_i, [_vp, _i, _vp, ctypes.POINTER(_i)]),
+    "igs_read_status_static": (_i, [_i, _vp, ctypes.POINTER(_i)]),
+    "igs_read_status_words": (_i, [_vp, _i, _vp, _vp]),
     "igs_set_culling": (_i, [_i]),
     "igs_spatial_order_workspace_bytes": (_sz, [_i, _i]),
     "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
@@ -55,9 +64,7 @@ SIGNATURES = {
     "igs_profile_reset": (_i, []),
     "igs_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
     "igs_describe_plan": (_i, [_i] * 6 + [ctypes.POINTER(_i)] * 4),
-    "igs_probe_fp32_rate": (_i, [_i, _i, ctypes.POINTER(ctypes.c_double)]),
-    "igs_probe_ex2_rate": (_i, [_i, ctypes.POINTER(ctypes.c_double)]),
-    "igs_probe_mix_rate": (_i, [_i, _i, ctypes.POINTER(ctypes.c_double)]),
+    "igs_describe_kernels": (_i, [_i] + [ctypes.POINTER(_i)] * 2),
 }
 
 
@@ -70,28 +77,27 @@ class IgsError(RuntimeError):
 
 
 def load() -> ctypes.CDLL:
-    """Loads (building first if the source tree is newer) the shared object."""
+    """Loads the shared object, building it first when it is missing or was built from
+    other sources than the tree holds now (``build.is_stale``: a hash of the sources)."""
     global _lib
     if _lib is not None:
         return _lib
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(LIB_PATH):
-            try:
-                from . import build as _build
+        from . import build as _build
 
+        if _build.is_stale():
+            try:
                 _build.build()
             except Exception as exc:  # noqa: BLE001 - surfaced verbatim below
                 raise ImportError(
-                    f"igs_b200: {LIB_PATH} is missing and could not be built ({exc}). "
+                    f"igs_b200: {LIB_PATH} is missing or out of date and could not be built ({exc}). "
                     "Run `python -m igs_b200.build`; there is no CPU or PyTorch fallback.") from exc
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name, None)
             if fn is None:
-                if os.environ.get("IGS_B200_LIB"):
-                    continue  # an older development build without this entry point
                 raise AttributeError(f"{LIB_PATH} does not export {name}: header and library out of sync")
             fn.restype = res
             fn.argtypes = args
@@ -140,6 +146,13 @@ def describe_plan(B, N, H, W, C, device: torch.device):
             "bwd_slabs": v[3].value}
 
 
+def separable_kernels(C: int):
+    """(forward, backward): whether separable-grid kernels exist for C channels."""
+    f, b = _i(0), _i(0)
+    check("igs_describe_kernels", load().igs_describe_kernels(int(C), ctypes.byref(f), ctypes.byref(b)))
+    return bool(f.value), bool(b.value)
+
+
 def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
     return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
 
@@ -161,11 +174,206 @@ def read_executed(ws: torch.Tensor) -> int:
     return int(host.value)
 
 
-def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, keep_workspace=False, order=None):
+# ---------------------------------------------------------------------------
+# What earlier calls found out about the data
+# ---------------------------------------------------------------------------
+# Without help the library decides on the device which kernel instantiations the data calls
+# for (separable grid or not, narrow gaussians or not) and launches all candidates; those
+# not chosen return at once.  The facts end up in the workspace's status words.  Here they
+# are read back WITHOUT ever blocking (a 32-byte copy into pinned memory plus an event,
+# picked up by a later call once the event has completed) and remembered, so that later
+# calls pass hints and launch only what will run:
+#   * per (device, B, N, H, W): whether at least one gaussian in eight is narrow -- looked at
+#     during the first calls and every 32nd after that; "not narrow" becomes
+#     HINT_WIDE_GAUSSIANS, "narrow" lets the set_backward_sort policy order the gaussians.
+#     A stale answer costs time only: the plain kernels are correct for any data.
+#   * per pair of grid tensors (the very same tensor objects, unmodified: weak references
+#     and torch's version counters): whether the library's device check found them
+#     separable.  If so, later calls hand the library stride-0 views (first row of x, first
+#     column of y), which are separable by construction; if not, HINT_GENERAL_GRID.
+#   * word 0, a kernel that gave up on a bounded wait: raised as IgsError by the next call.
+_memo_lock = threading.Lock()
+_pending = []       # reads in flight: _PendingRead
+_free_hosts = []    # pinned int32[STATUS_WORDS] buffers to reuse
+_shape_memos = {}   # (device index, B, N, H, W) -> _ShapeMemo
+_grid_memos = {}    # (id(x), id(y)) -> _GridMemo
+GRID_CHECKED_BIT = 8
+GRID_NOT_SEPARABLE_BIT = 1
+
+
+class _ShapeMemo:
+    EVERY = 32  # after the first few calls, look again every this many
+
+    __slots__ = ("total", "narrow", "calls", "pending")
+
+    def __init__(self, total):
+        self.total = total
+        self.narrow = None  # unknown until the first read has come back
+        self.calls = 0
+        self.pending = False
+
+
+class _GridMemo:
+    __slots__ = ("xref", "yref", "xv", "yv", "kind", "pending")
+
+    def __init__(self, x, y):
+        self.xref, self.yref = weakref.ref(x), weakref.ref(y)
+        self.xv, self.yv = x._version, y._version
+        self.kind = None  # None = not known yet; "separable", "general", "unchecked"
+        self.pending = False
+
+    def matches(self, x, y):
+        return self.xref() is x and self.yref() is y and self.xv == x._version and self.yv == y._version
+
+
+class _PendingRead:
+    __slots__ = ("host", "event", "shape", "grid")
+
+
+def _drain_reads():
+    """Folds every status read whose copy has completed into the memos."""
+    if not _pending or torch.cuda.is_current_stream_capturing():
+        return
+    failed = False
+    with _memo_lock:
+        keep = []
+        for r in _pending:
+            if not r.event.query():
+                keep.append(r)
+                continue
+            words = r.host.tolist()
+            _free_hosts.append(r.host)
+            failed |= words[0] != 0
+            if r.shape is not None:
+                r.shape.pending = False
+                r.shape.narrow = words[2] * 8 >= r.shape.total
+            if r.grid is not None:
+                r.grid.pending = False
+                if r.grid.kind is None:
+                    if words[1] & GRID_CHECKED_BIT:
+                        r.grid.kind = "general" if words[1] & GRID_NOT_SEPARABLE_BIT else "separable"
+                    else:
+                        r.grid.kind = "unchecked"  # the call did not have to look: nothing learnt
+        _pending[:] = keep
+    if failed:
+        raise IgsError("igs_read_status_words", -5, "an earlier call's kernel gave up on a bounded wait; its result "
+                                                    "is invalid")
+
+
+def _queue_read(ws, shape, grid):
+    """After a forward / backward on workspace ws: queue a status read if a memo wants one."""
+    if shape is not None:
+        shape.calls += 1
+    want_shape = shape is not None and not shape.pending and (shape.calls <= 4 or shape.calls % shape.EVERY == 0)
+    want_grid = grid is not None and grid.kind is None and not grid.pending
+    if not (want_shape or want_grid) or torch.cuda.is_current_stream_capturing():
+        return
+    dev = ws.device
+    with _memo_lock:
+        host = _free_hosts.pop() if _free_hosts else torch.zeros(STATUS_WORDS, dtype=torch.int32, pin_memory=True)
+        r = _PendingRead()
+        r.host, r.shape, r.grid = host, (shape if want_shape else None), (grid if want_grid else None)
+        check("igs_read_status_words",
+              load().igs_read_status_words(_ptr(ws), dev.index, _stream(dev), ctypes.c_void_p(host.data_ptr())))
+        r.event = torch.cuda.Event()
+        r.event.record(torch.cuda.current_stream(dev))
+        if want_shape:
+            shape.pending = True
+        if want_grid:
+            grid.pending = True
+        _pending.append(r)
+
+
+def _shape_memo(dev, B, N, H, W):
+    key = (dev.index, B, N, H, W)
+    m = _shape_memos.get(key)
+    if m is None:
+        if len(_shape_memos) > 256:
+            _shape_memos.clear()
+        m = _shape_memos[key] = _ShapeMemo(B * N)
+    return m
+
+
+def forget_what_calls_learnt() -> None:
+    """Drops every remembered fact (tests; after changing the culling switch)."""
+    with _memo_lock:
+        _shape_memos.clear()
+        _grid_memos.clear()
+
+
+def grid_for_call(x, y, B):
+    """x, y [B,1,H,W] or [1,1,H,W] -> (x3, y3, hints, memo): [B,H,W] views without a copy,
+    the grid part of the call's hints, and the memo entry that wants to learn from this call
+    (or None).  Grids remembered as separable come back as stride-0 views."""
+    if x.dim() != 4 or y.dim() != 4 or x.shape[1] != 1 or y.shape[1] != 1:
+        raise ValueError(f"x and y must be [B,1,H,W]; got {tuple(x.shape)} and {tuple(y.shape)}")
+    if x.shape != y.shape:
+        raise ValueError(f"x {tuple(x.shape)} and y {tuple(y.shape)} differ")
+    if x.shape[0] not in (B, 1):
+        raise ValueError(f"x/y batch {x.shape[0]} does not match the gaussians' batch {B}")
+    H, W = x.shape[2], x.shape[3]
+    x3, y3 = x[:, 0].expand(B, H, W), y[:, 0].expand(B, H, W)
+    if H < 4 or W < 16 or ((x3.stride(1) == 0 or H == 1) and (y3.stride(2) == 0 or W == 1)):
+        return x3, y3, 0, None  # tiny, or separable by construction: the library needs no help
+    key = (id(x), id(y))
+    entry = _grid_memos.get(key)
+    if entry is None or not entry.matches(x, y):
+        if torch.cuda.is_current_stream_capturing():
+            return x3, y3, 0, None
+        with _memo_lock:
+            if len(_grid_memos) > 64:  # forget grids that are gone (or everything, if none is)
+                dead = [k for k, e in _grid_memos.items() if e.xref() is None or e.yref() is None]
+                for k in dead or list(_grid_memos):
+                    del _grid_memos[k]
+            entry = _grid_memos[key] = _GridMemo(x, y)
+        return x3, y3, 0, entry
+    if entry.kind == "separable":
+        return x3[:, :1].expand(B, H, W), y3[:, :, :1].expand(B, H, W), 0, None
+    if entry.kind == "general":
+        return x3, y3, HINT_GENERAL_GRID, None
+    return x3, y3, 0, (entry if entry.kind is None else None)
+
+
+def grid_views(x, y, B, as_separable=False):
+    """[B,1,H,W] (or [1,1,H,W]) sample coordinates -> [B,H,W] views, no copy; as_separable:
+    the stride-0 views of a grid known to be separable (first row of x, first column of y)."""
+    H, W = x.shape[2], x.shape[3]
+    if as_separable:
+        return x[:, 0, :1].expand(B, H, W), y[:, 0, :, :1].expand(B, H, W)
+    return x[:, 0].expand(B, H, W), y[:, 0].expand(B, H, W)
+
+
+class CallInfo:
+    """What one forward decided, kept for its backward: the grid views (as_separable says
+    which kind), the hints, the processing order, and the memos that learn from the call."""
+    __slots__ = ("x3", "y3", "as_separable", "hints", "order", "shape", "grid")
+
+
+def prepare_call(x, y, pos, feat=None, pos_off=None):
+    """Everything a forward (and the backward after it) needs beyond the tensors: grid views,
+    hints from what earlier calls learnt, and the processing order the set_backward_sort
+    policy wants, if any.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off)."""
+    _drain_reads()
+    B, N = (pos if pos is not None else feat).shape[:2]
+    info = CallInfo()
+    info.x3, info.y3, info.hints, info.grid = grid_for_call(x, y, B)
+    info.as_separable = info.x3.stride(1) == 0 and info.y3.stride(2) == 0
+    _, H, W = info.x3.shape
+    info.shape = _shape_memo(x.device, B, N, H, W) if B * N * H * W > 0 else None
+    info.order = None
+    if info.shape is not None:
+        if info.shape.narrow is False and _BACKWARD_SORT != "on":
+            info.hints |= HINT_WIDE_GAUSSIANS
+        info.order = order_by_policy(info.shape, pos, feat, pos_off, info.x3, info.y3)
+    return info
+
+
+def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, keep_workspace=False, order=None,
+            hints=0, info=None):
     """kind 'sr': s0 = scales, s1 = rotations; kind 'cov': s0, s1, s2 = cov_inv_00/01/11.
     x3, y3 are [B,H,W] views (any strides).  Returns (out, wsum) or, with
     normalize=False, (sums [B,C+1,H,W], None).  order: [B,N] int32 permutation in which the
-    gaussians are summed, or None."""
+    gaussians are summed, or None.  info: a CallInfo whose memos learn from this call."""
     dev = pos.device
     B, N, C = colors.shape
     _, H, W = x3.shape
@@ -178,19 +386,21 @@ def forward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, eps, normalize=True, 
         out = torch.empty(B, C + 1, H, W, dtype=torch.float32, device=dev)
         wsum = None
     tail = (_ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N, H, W, C, float(eps), int(bool(normalize)),
-            _ptr(out), _ptr(wsum), _ptr(order), _ptr(ws), ws.numel(), dev.index, _stream(dev))
+            _ptr(out), _ptr(wsum), _ptr(order), int(hints), _ptr(ws), ws.numel(), dev.index, _stream(dev))
     lib = load()
     if kind == "sr":
         check("igs_forward_sr", lib.igs_forward_sr(_ptr(pos), _ptr(s0), _ptr(s1), _ptr(alphas), _ptr(colors), *tail))
     else:
         check("igs_forward_cov",
               lib.igs_forward_cov(_ptr(pos), _ptr(s0), _ptr(s1), _ptr(s2), _ptr(alphas), _ptr(colors), *tail))
+    if info is not None and N > 0:
+        _queue_read(ws, info.shape, info.grid)
     if keep_workspace:
         return out, wsum, ws
     return out, wsum
 
 
-def forward_feature(feat, pos_off, x3, y3, eps, order=None, keep_workspace=False):
+def forward_feature(feat, pos_off, x3, y3, eps, order=None, keep_workspace=False, hints=0, info=None):
     """The forward on the module's projection output feat [B,N,6+C] (contiguous); pos_off
     [B,N,2] or None.  Returns (out, wsum)."""
     dev = feat.device
@@ -203,32 +413,31 @@ def forward_feature(feat, pos_off, x3, y3, eps, order=None, keep_workspace=False
     wsum = torch.empty(B, H, W, dtype=torch.float32, device=dev)
     check("igs_forward_feature",
           load().igs_forward_feature(_ptr(feat), _ptr(pos_off), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N,
-                                     H, W, C, float(eps), 1, _ptr(out), _ptr(wsum), _ptr(order), _ptr(ws), ws.numel(),
-                                     dev.index, _stream(dev)))
+                                     H, W, C, float(eps), 1, _ptr(out), _ptr(wsum), _ptr(order), int(hints), _ptr(ws),
+                                     ws.numel(), dev.index, _stream(dev)))
+    if info is not None and N > 0:
+        _queue_read(ws, info.shape, info.grid)
     if keep_workspace:
         return out, wsum, ws
     return out, wsum
 
 
-def backward_feature(feat, pos_off, x3, y3, wsum, out, gout, eps, grad_mode, order=None, policy=True):
-    """Gradient with respect to feat, [B,N,6+C] (the unused column gets zeros).  order /
-    policy as for backward()."""
+def backward_feature(feat, pos_off, x3, y3, wsum, out, gout, eps, grad_mode, order=None, hints=0, info=None):
+    """Gradient with respect to feat, [B,N,6+C] (the unused column gets zeros)."""
     dev = feat.device
     B, N, per = feat.shape
     C = per - 6
     _, H, W = x3.shape
-    probe = None
-    if order is None and policy:
-        order, probe = order_by_policy(None, feat, pos_off, x3, y3)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     d_feat = torch.empty_like(feat)
     check("igs_backward_feature",
           load().igs_backward_feature(_ptr(feat), _ptr(pos_off), _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3),
                                       _ptr(wsum), _ptr(out), _ptr(gout), B, N, H, W, C, float(eps), int(grad_mode),
-                                      _ptr(d_feat), _ptr(order), _ptr(ws), ws.numel(), dev.index, _stream(dev)))
-    if probe is not None:
-        probe.queue(ws)
+                                      _ptr(d_feat), _ptr(order), int(hints), _ptr(ws), ws.numel(), dev.index,
+                                      _stream(dev)))
+    if info is not None and N > 0 and H * W > 0:
+        _queue_read(ws, info.shape, None)
     return d_feat
 
 
@@ -245,7 +454,7 @@ def normalize(sums: torch.Tensor, eps: float):
 
 def spatial_order(pos, x3, y3):
     """[B,N] int32 permutation putting spatial neighbours next to each other (the `order`
-    argument of the backward)."""
+    argument of the forward and the backward)."""
     dev = pos.device
     B, N, _ = pos.shape
     _, H, W = x3.shape
@@ -258,41 +467,7 @@ def spatial_order(pos, x3, y3):
     return order
 
 
-class _NarrowProbe:
-    """Host-side memory of whether a shape's gaussians were narrow at its recent backward
-    calls, learnt without ever blocking: now and then a backward queues a copy of the
-    device's narrow-gaussian count into pinned memory, and a later call picks the value up
-    once the copy's event has completed."""
-
-    EVERY = 32  # after the first few calls, look again every this many
-
-    def __init__(self):
-        self.host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-        self.event = None
-        self.calls = 0
-        self.narrow = False
-
-    def poll(self, total):
-        if self.event is not None and not torch.cuda.is_current_stream_capturing() and self.event.query():
-            self.narrow = int(self.host[0]) * 8 >= total
-            self.event = None
-        return self.narrow
-
-    def queue(self, ws):
-        self.calls += 1
-        if self.event is not None or not (self.calls <= 4 or self.calls % self.EVERY == 0):
-            return
-        dev = ws.device
-        if torch.cuda.is_current_stream_capturing():
-            return
-        check("igs_read_narrow_count",
-              load().igs_read_narrow_count(_ptr(ws), dev.index, _stream(dev), ctypes.c_void_p(self.host.data_ptr())))
-        self.event = torch.cuda.Event()
-        self.event.record(torch.cuda.current_stream(dev))
-
-
 _BACKWARD_SORT = "auto"
-_probes = {}
 # Below this many gaussian x pixel pairs per call, "auto" does not order: the half dozen
 # extra launches cost an eager step more host time than the skipping saves on the device
 # (measured: 2.7e8 pairs, 4096 gaussians at 256x256: 0.61 ms ordered against 0.51 ms; 1.1e9
@@ -301,50 +476,43 @@ AUTO_ORDER_MIN_EVALS = 5e8
 
 
 def set_backward_sort(mode: str) -> None:
-    """'auto' (default): the backward takes its gaussians in spatial order once the shape's
-    recent calls have shown mostly narrow gaussians; 'on' / 'off': always / never.  The
-    gradients are the same bit for bit in every mode; only the time differs."""
+    """'auto' (default): forward and backward take their gaussians in spatial order once the
+    shape's recent calls have shown mostly narrow gaussians; 'on' / 'off': always / never.
+    The gradients are the same bit for bit in every mode; only the time differs."""
     global _BACKWARD_SORT
     if mode not in ("auto", "on", "off"):
         raise ValueError("mode must be 'auto', 'on' or 'off'")
     _BACKWARD_SORT = mode
-    _probes.clear()
+    forget_what_calls_learnt()
 
 
-def order_by_policy(pos, feat, pos_off, x3, y3):
-    """(order or None, probe or None) for one forward / backward under the set_backward_sort
-    policy.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off) to take the positions
-    from.  The caller hands the probe the workspace of a call it made (probe.queue(ws)), so
-    that later calls learn how narrow the gaussians are."""
+def order_by_policy(shape, pos, feat, pos_off, x3, y3):
+    """The processing order one forward + backward should use under the set_backward_sort
+    policy, or None.  shape: the call's _ShapeMemo; pos [B,N,2], or None with feat
+    [B,N,6+C] (+ pos_off) to take the positions from."""
     B, N = (pos if pos is not None else feat).shape[:2]
     _, H, W = x3.shape
     if B * N == 0 or _BACKWARD_SORT == "off":
-        return None, None
-    dev = x3.device
-    probe = None
+        return None
     if _BACKWARD_SORT == "auto":
-        probe = _probes.setdefault((dev.index, B, N, H, W), _NarrowProbe())
-        if not probe.poll(B * N):
-            return None, probe
+        if not shape.narrow:
+            return None
         # small problems: ordering costs an eager step more on the host than it saves on the
         # device; inside a graph capture the host cost is paid once, so there it always pays
         if B * N * H * W < AUTO_ORDER_MIN_EVALS and not torch.cuda.is_current_stream_capturing():
-            return None, probe
+            return None
     if pos is None:
         pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off
-    return spatial_order(pos.contiguous(), x3, y3), probe
+    return spatial_order(pos.contiguous(), x3, y3)
 
 
 def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps, grad_mode, want_xy,
-             keep_workspace=False, order=None, policy=True):
+             keep_workspace=False, order=None, hints=0, info=None):
     """Returns dict of gradients; d_x / d_y only when want_xy.  order: an explicit [B,N] int32
-    permutation, or None: then by the set_backward_sort policy if ``policy``, else none."""
+    permutation or None."""
     dev = pos.device
     B, N, C = colors.shape
     _, H, W = x3.shape
-    probe = None
-    if order is None and policy:
-        order, probe = order_by_policy(pos, None, None, x3, y3)
     _, bb = workspace_bytes(B, N, H, W, C, dev)
     ws = _workspace(bb, dev)
     f32 = dict(dtype=torch.float32, device=dev)
@@ -355,8 +523,8 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     d_y = torch.empty(B, H, W, **f32) if want_xy else None
     head = (_ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), _ptr(wsum), _ptr(out), _ptr(gout), B, N, H, W, C,
             float(eps), int(grad_mode))
-    tail = (_ptr(d_alpha), _ptr(d_col), _ptr(d_x), _ptr(d_y), _ptr(order), _ptr(ws), ws.numel(), dev.index,
-            _stream(dev))
+    tail = (_ptr(d_alpha), _ptr(d_col), _ptr(d_x), _ptr(d_y), _ptr(order), int(hints), _ptr(ws), ws.numel(),
+            dev.index, _stream(dev))
     lib = load()
     if kind == "sr":
         d_s0 = torch.empty(B, N, 2, **f32)
@@ -371,8 +539,8 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
               lib.igs_backward_cov(_ptr(pos), _ptr(s0), _ptr(s1), _ptr(s2), _ptr(alphas), _ptr(colors), *head,
                                    _ptr(d_pos), _ptr(d_s0), _ptr(d_s1), _ptr(d_s2), *tail))
         res = {"positions": d_pos, "c00": d_s0, "c01": d_s1, "c11": d_s2, "alphas": d_alpha, "colors": d_col}
-    if probe is not None:
-        probe.queue(ws)
+    if info is not None and N > 0 and H * W > 0:
+        _queue_read(ws, info.shape, None)
     if want_xy:
         res["x"], res["y"] = d_x, d_y
     if keep_workspace:
@@ -408,6 +576,7 @@ KERNEL_NAMES = ("pack", "forward", "reduce_normalize", "pixel_terms", "backward"
 def set_culling(on: bool) -> None:
     """Process-wide switch of the lossless (gaussian, pixel tile) culling; default on."""
     check("igs_set_culling", load().igs_set_culling(int(bool(on))))
+    forget_what_calls_learnt()
 
 
 def profile_enable(on: bool) -> None:
@@ -426,21 +595,3 @@ def profile_read():
         check("igs_profile_read", load().igs_profile_read(k, ctypes.byref(ms), ctypes.byref(n)))
         res[name] = (ms.value, int(n.value))
     return res
-
-
-def probe_rates(device: torch.device):
-    """Measured issue rates of the FP32 FMA pipe (scalar, packed) and of MUFU ex2."""
-    lib = load()
-    vals = {}
-    for key, packed in (("fp32_scalar_lane_instr_per_s", 0), ("fp32_packed_lane_instr_per_s", 1)):
-        d = ctypes.c_double(0)
-        check("igs_probe_fp32_rate", lib.igs_probe_fp32_rate(device.index, packed, ctypes.byref(d)))
-        vals[key] = d.value
-    d = ctypes.c_double(0)
-    check("igs_probe_ex2_rate", lib.igs_probe_ex2_rate(device.index, ctypes.byref(d)))
-    vals["ex2_results_per_s"] = d.value
-    for key, bwd in (("fp32_forward_mix_lane_instr_per_s", 0), ("fp32_backward_mix_lane_instr_per_s", 1)):
-        d = ctypes.c_double(0)
-        check("igs_probe_mix_rate", lib.igs_probe_mix_rate(device.index, bwd, ctypes.byref(d)))
-        vals[key] = d.value
-    return vals

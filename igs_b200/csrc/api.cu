@@ -20,17 +20,41 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 static std::atomic<int> g_profile_on{0};
 static std::mutex g_profile_mu;
 struct EventPair {
-    int id;
+    int id, dev;
     cudaEvent_t start, stop;
 };
 static std::vector<EventPair> g_pending;
+// events that have been read are kept, per device, for the next timed launches: creating a
+// pair per launch costs the host more than the launch itself
+static std::vector<cudaEvent_t> g_free_events[64];
 static double g_total_ms[K_COUNT];
 static long long g_timed_launches[K_COUNT];
 
+static cudaEvent_t take_event(int dev) {
+    {
+        std::lock_guard<std::mutex> lock(g_profile_mu);
+        if (dev >= 0 && dev < 64 && !g_free_events[dev].empty()) {
+            cudaEvent_t e = g_free_events[dev].back();
+            g_free_events[dev].pop_back();
+            return e;
+        }
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return e;
+}
+
 KernelTimer::KernelTimer(int id_, cudaStream_t s) : id(id_), stream(s) {
     if (!g_profile_on.load(std::memory_order_relaxed)) return;
-    if (cudaEventCreate(&start) != cudaSuccess || cudaEventCreate(&stop) != cudaSuccess) {
-        cudaGetLastError();
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    start = take_event(dev);
+    stop = take_event(dev);
+    if (!start || !stop) {
+        if (start) cudaEventDestroy(start);
+        if (stop) cudaEventDestroy(stop);
         start = stop = nullptr;
         return;
     }
@@ -40,7 +64,7 @@ KernelTimer::~KernelTimer() {
     if (!start || !stop) return;
     cudaEventRecord(stop, stream);
     std::lock_guard<std::mutex> lock(g_profile_mu);
-    g_pending.push_back({id, start, stop});
+    g_pending.push_back({id, dev, start, stop});
 }
 
 // waits for every pending pair and folds it into the totals
@@ -57,21 +81,16 @@ static cudaError_t profile_drain() {
         } else if (first == cudaSuccess) {
             first = e;
         }
-        cudaEventDestroy(p.start);
-        cudaEventDestroy(p.stop);
+        if (p.dev >= 0 && p.dev < 64 && g_free_events[p.dev].size() < 4096) {
+            g_free_events[p.dev].push_back(p.start);
+            g_free_events[p.dev].push_back(p.stop);
+        } else {
+            cudaEventDestroy(p.start);
+            cudaEventDestroy(p.stop);
+        }
     }
     g_pending.clear();
     return first;
-}
-
-// IGS_B200_NO_SEPARABLE=1 (development knob) keeps every call on the general kernels.
-static bool separable_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("IGS_B200_NO_SEPARABLE");
-        v = (e && e[0] == '1') ? 0 : 1;
-    }
-    return v != 0;
 }
 
 int sm_count(int device) {
@@ -220,11 +239,7 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     // N = 65536: 0.47 / 0.48 / 0.51 ms, the step as a whole being fastest at 8.
     int ns_fine = ns;
     if (p->sep_ok) {
-#ifdef IGS_FINE_RP
-        const int rp_fine = IGS_FINE_RP;
-#else
         const int rp_fine = 8;
-#endif
         const int want = (p->nrp + rp_fine - 1) / rp_fine;
         ns_fine = want < 96 ? want : 96;
         // the partial sums grow with slabs x gaussians: keep them under half a gigabyte
@@ -273,8 +288,6 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     }
     p->off_part = off;
     off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
-    p->off_sum = off;
-    off = align_up(off + (size_t)B * p->planes * (size_t)N * sizeof(float), 256);
     p->part_bytes = (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float);
     p->off_tasks = off;
     p->task_capacity = 0;
@@ -314,9 +327,10 @@ static std::atomic<int> g_culling{1};
 // Classifies the sample grid (GridKind); launches the separability check when the strides do
 // not settle the question.  The caller has cleared the status area (grid word included).
 static cudaError_t prepare_grid(unsigned char* ws, const float* x, const float* y, const Strides& sx, const Strides& sy,
-                                int B, int H, int W, bool separable_available, GridKind* kind, cudaStream_t st) {
+                                int B, int H, int W, bool separable_available, int hints, GridKind* kind,
+                                cudaStream_t st) {
     int* flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
-    *kind = classify_grid(sx.h, sy.w, H, W, separable_enabled() && separable_available);
+    *kind = classify_grid(sx.h, sy.w, H, W, separable_available && !(hints & IGS_HINT_GENERAL_GRID));
     if (*kind != GRID_CHECK_ON_DEVICE) return cudaSuccess;
     GridCheckArgs ga;
     ga.x = x; ga.y = y;
@@ -354,8 +368,9 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
                  size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan, const ParamLayout* layout,
-                 const int* order) {
+                 const int* order, int hints) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    if (hints & ~(IGS_HINT_WIDE_GAUSSIANS | IGS_HINT_GENERAL_GRID)) return IGS_ERR_ARG;
     if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
     if (B == 0 || HW == 0) return IGS_OK;
@@ -389,7 +404,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         if (rc) return rc;
     }
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
-    const bool culling_on = g_culling.load(std::memory_order_relaxed);
+    const bool culling_on = g_culling.load(std::memory_order_relaxed) && !(hints & IGS_HINT_WIDE_GAUSSIANS);
     if (order && culling_on && !use_plan && p.tiles_sep > 0 && (long long)p.tiles_sep * B >= sm_count(device) &&
         (N + p.chunk_g - 1) / p.chunk_g <= 8192 /* what a CTA can list */) {
         // A caller that passes an order expects narrow gaussians: a CTA then streams a few
@@ -407,7 +422,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     // separable grid (x by column, y by row)?  known from the strides, or checked on the device
     int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
     GridKind grid_kind;
-    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.tiles_sep > 0, &grid_kind, st);
+    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.tiles_sep > 0, hints, &grid_kind, st);
     if (e != cudaSuccess) return (int)e;
 
     PackArgs pa;
@@ -465,7 +480,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         if (gk != GRID_GENERAL) {
             // the separable kernel comes as a plain and a culling instantiation; both are
             // launched and the count of narrow gaussians picks one (the other returns at once)
-            fa.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
+            fa.cull_sel = culling_on ? pa.narrow_count : nullptr;
             fa.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
             fa.cbox = pa.cbox;
             fa.chunks_per_b = (N + p.chunk_g - 1) / p.chunk_g;
@@ -503,10 +518,11 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
                          const int64_t* ys, const float* wsum, const float* out, const float* gout, int B, int N,
                          int H, int W, int C, float eps, int mode, float* d_pos, float* d_s0, float* d_s1,
                          float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, const int* order,
-                         void* workspace, size_t workspace_bytes, int device, void* stream,
+                         int hints, void* workspace, size_t workspace_bytes, int device, void* stream,
                          const ParamLayout* layout = nullptr) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
+    if (hints & ~(IGS_HINT_WIDE_GAUSSIANS | IGS_HINT_GENERAL_GRID)) return IGS_ERR_ARG;
     if (layout && (d_x || d_y)) return IGS_ERR_ARG;  // coordinate gradients: separate tensors only
     if ((d_x == nullptr) != (d_y == nullptr)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
@@ -545,7 +561,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     // which kernel family will (probably) run is known from the strides, or assumed separable
     // when the data has to be checked on the device (a materialised xy_grid)
     const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
-    const bool likely_separable = classify_grid(sx.h, sy.w, H, W, separable_enabled()) != GRID_GENERAL;
+    const bool likely_separable = !(hints & IGS_HINT_GENERAL_GRID) && classify_grid(sx.h, sy.w, H, W, true) != GRID_GENERAL;
     BwdPlan p;
     rc = plan_backward(B, N, H, W, C, device, &p, order != nullptr, likely_separable);
     if (rc) return rc;
@@ -557,7 +573,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     // separable grid?  (same decision procedure as the forward)
     int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
     GridKind grid_kind;
-    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.sep_ok != 0, &grid_kind, st);
+    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.sep_ok != 0, hints, &grid_kind, st);
     if (e != cudaSuccess) return (int)e;
 
     PackArgs pa;
@@ -622,7 +638,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.rp_per_slab = p.rp_per_slab;
         ba.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
         ba.grid_word = grid_flag;
-        ba.cull_sel = g_culling.load(std::memory_order_relaxed) ? pa.narrow_count : nullptr;
+        ba.cull_sel = (g_culling.load(std::memory_order_relaxed) && !(hints & IGS_HINT_WIDE_GAUSSIANS)) ? pa.narrow_count : nullptr;
         ba.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
         ba.pairs_per_slab = p.pairs_per_slab;
         ba.B = B; ba.N = N;
@@ -683,15 +699,6 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     fa.lay = pa.lay;
     fa.B = B; fa.N = N; fa.C = C;
     fa.n_slab = p.n_slab;
-    if (p.n_slab > 4) {
-        // many slabs: add them up with a thread per (plane, gaussian) first -- one thread per
-        // gaussian walking all of them alone keeps too few loads in flight
-        float* sums = reinterpret_cast<float*>(ws + p.off_sum);
-        e = launch_slab_sum(fa.part, sums, p.n_slab, (long long)B * p.planes * N, st);
-        if (e != cudaSuccess) return (int)e;
-        fa.part = sums;
-        fa.n_slab = 1;
-    }
     fa.planes = p.planes;
     fa.n_chunks = p.ch.n;
     fa.kind = kind;
@@ -750,7 +757,7 @@ using namespace igs;
 
 extern "C" {
 
-int igs_version(void) { return 100; }
+int igs_version(void) { return 110; }
 
 const char* igs_strerror(int code) {
     switch (code) {
@@ -802,24 +809,33 @@ int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_ti
     return IGS_OK;
 }
 
+int igs_describe_kernels(int C, int* forward_separable, int* backward_separable) {
+    Chunks ch;
+    int rc = make_chunks(C, &ch);
+    if (rc) return rc;
+    if (forward_separable) *forward_separable = forward_has_separable(ch.ct[0]) ? 1 : 0;
+    if (backward_separable) *backward_separable = (ch.n == 1 && backward_has_separable(ch.ct[0])) ? 1 : 0;
+    return IGS_OK;
+}
+
 int igs_forward_sr(const float* positions, const float* scales, const float* rotations, const float* alphas,
                    const float* colors, const float* x, const int64_t* x_strides, const float* y,
                    const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
-                   float* wsum, const int* order, void* workspace, size_t workspace_bytes, int device,
+                   float* wsum, const int* order, int hints, void* workspace, size_t workspace_bytes, int device,
                    void* stream) {
     return forward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
                         y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream,
-                        nullptr, nullptr, order);
+                        nullptr, nullptr, order, hints);
 }
 
 int igs_forward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01, const float* cov_inv_11,
                     const float* alphas, const float* colors, const float* x, const int64_t* x_strides, const float* y,
                     const int64_t* y_strides, int B, int N, int H, int W, int C, float eps, int normalize, float* out,
-                    float* wsum, const int* order, void* workspace, size_t workspace_bytes, int device,
-                   void* stream) {
+                    float* wsum, const int* order, int hints, void* workspace, size_t workspace_bytes, int device,
+                    void* stream) {
     return forward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
                         y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes, device, stream,
-                        nullptr, nullptr, order);
+                        nullptr, nullptr, order, hints);
 }
 
 int igs_normalize(const float* sums, int B, int H, int W, int C, float eps, float* out, float* wsum, int device,
@@ -832,10 +848,11 @@ int igs_backward_sr(const float* positions, const float* scales, const float* ro
                     const int64_t* y_strides, const float* wsum, const float* out, const float* gout, int B, int N,
                     int H, int W, int C, float eps, int grad_mode, float* d_positions, float* d_scales,
                     float* d_rotations, float* d_alphas, float* d_colors, float* d_x, float* d_y, const int* order,
-                    void* workspace, size_t workspace_bytes, int device, void* stream) {
+                    int hints, void* workspace, size_t workspace_bytes, int device, void* stream) {
     return backward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_scales, d_rotations,
-                         nullptr, d_alphas, d_colors, d_x, d_y, order, workspace, workspace_bytes, device, stream);
+                         nullptr, d_alphas, d_colors, d_x, d_y, order, hints, workspace, workspace_bytes, device,
+                         stream);
 }
 
 int igs_backward_cov(const float* positions, const float* cov_inv_00, const float* cov_inv_01,
@@ -843,12 +860,12 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                      const int64_t* x_strides, const float* y, const int64_t* y_strides, const float* wsum,
                      const float* out, const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
                      float* d_positions, float* d_cov_inv_00, float* d_cov_inv_01, float* d_cov_inv_11,
-                     float* d_alphas, float* d_colors, float* d_x, float* d_y, const int* order, void* workspace,
-                     size_t workspace_bytes, int device, void* stream) {
+                     float* d_alphas, float* d_colors, float* d_x, float* d_y, const int* order, int hints,
+                     void* workspace, size_t workspace_bytes, int device, void* stream) {
     return backward_impl(SHAPE_COV_INV, positions, cov_inv_00, cov_inv_01, cov_inv_11, alphas, colors, x, x_strides, y,
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_cov_inv_00,
-                         d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, order, workspace, workspace_bytes,
-                         device, stream);
+                         d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, order, hints, workspace,
+                         workspace_bytes, device, stream);
 }
 
 int igs_set_culling(int on) {
@@ -895,22 +912,21 @@ static ParamLayout feature_layout(int C, const float* pos_offset, float* d_featu
 
 int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,
                         const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C, float eps,
-                        int normalize, float* out, float* wsum, const int* order, void* workspace,
-                        size_t workspace_bytes, int device,
-                        void* stream) {
+                        int normalize, float* out, float* wsum, const int* order, int hints, void* workspace,
+                        size_t workspace_bytes, int device, void* stream) {
     if (C < 1) return IGS_ERR_ARG;
     const ParamLayout l = feature_layout(C, pos_offset, nullptr);
     return forward_impl(SHAPE_SCALE_ROT, gs_feature, gs_feature ? gs_feature + 2 : nullptr,
                         gs_feature ? gs_feature + 4 : nullptr, nullptr, nullptr, gs_feature ? gs_feature + 6 : nullptr, x,
                         x_strides, y, y_strides, B, N, H, W, C, eps, normalize, out, wsum, workspace, workspace_bytes,
-                        device, stream, nullptr, &l, order);
+                        device, stream, nullptr, &l, order, hints);
 }
 
 int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x, const int64_t* x_strides,
                          const float* y, const int64_t* y_strides, const float* wsum, const float* out,
                          const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
-                         float* d_feature, const int* order, void* workspace, size_t workspace_bytes, int device,
-                         void* stream) {
+                         float* d_feature, const int* order, int hints, void* workspace, size_t workspace_bytes,
+                         int device, void* stream) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (B == 0 || N == 0) return IGS_OK;
     if (!gs_feature || !d_feature) return IGS_ERR_ARG;
@@ -925,8 +941,8 @@ int igs_backward_feature(const float* gs_feature, const float* pos_offset, const
     const ParamLayout l = feature_layout(C, pos_offset, d_feature);
     return backward_impl(SHAPE_SCALE_ROT, gs_feature, gs_feature + 2, gs_feature + 4, nullptr, nullptr, gs_feature + 6, x,
                          x_strides, y, y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_feature,
-                         d_feature + 2, d_feature + 4, nullptr, nullptr, d_feature + 6, nullptr, nullptr, order, workspace,
-                         workspace_bytes, device, stream, &l);
+                         d_feature + 2, d_feature + 4, nullptr, nullptr, d_feature + 6, nullptr, nullptr, order, hints,
+                         workspace, workspace_bytes, device, stream, &l);
 }
 
 int igs_read_status(const void* workspace, int device, void* stream, int* host_status) {
@@ -940,6 +956,16 @@ int igs_read_status(const void* workspace, int device, void* stream, int* host_s
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     return *host_status ? IGS_ERR_STATUS : IGS_OK;
+}
+
+int igs_read_status_words(const void* workspace, int device, void* stream, int* host_words) {
+    if (!workspace || !host_words) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    return (int)cudaMemcpyAsync(host_words, workspace, IGS_STATUS_WORDS * sizeof(int), cudaMemcpyDeviceToHost,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int igs_read_executed(const void* workspace, int device, void* stream, unsigned long long* host_count) {

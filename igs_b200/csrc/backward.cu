@@ -103,12 +103,10 @@ cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStrea
 // for four cycles per warp, so with GPT = 1 the 3 reads per pixel pair (C = 3) need
 // more return-path cycles than the 22 f32x2 instructions need FMA-pipe cycles; GPT = 2
 // halves the reads per evaluation and makes the FMA pipe the limiter again.
-#ifndef IGS_BWD_GPT
-#define IGS_BWD_GPT 2
-#endif
-#ifndef IGS_BWD_GPT_16  // gaussians per thread in the 16-channel instantiation (165 registers,
-#define IGS_BWD_GPT_16 2  // 12 warps per SM: 248.8 ms against 254.7 ms with one, B=8 N=65536 512x512)
-#endif
+constexpr int BWD_GPT = 2;
+// gaussians per thread in the 16-channel instantiation (165 registers, 12 warps per SM:
+// 248.8 ms against 254.7 ms with one, B=8 N=65536 512x512)
+constexpr int BWD_GPT_16 = 2;
 
 template <int CT, int GPT>
 struct BwdCfg {
@@ -116,16 +114,8 @@ struct BwdCfg {
     static constexpr int GAUSS_PER_CTA = THREADS * GPT;
     static constexpr int CHUNK_PAIRS = CT <= 4 ? 256 : 128;
     static constexpr int STAGES = 2;
-#ifdef IGS_BWD_MINCTAS
-    static constexpr int MIN_CTAS = IGS_BWD_MINCTAS;
-#else
     static constexpr int MIN_CTAS = CT <= 4 ? 5 : (CT <= 8 ? 4 : 3);
-#endif
-#ifdef IGS_BWD_UNROLL
-    static constexpr int UNROLL = IGS_BWD_UNROLL;
-#else
     static constexpr int UNROLL = CT > 4 ? (GPT >= 2 ? 1 : 2) : (GPT >= 2 ? 4 : 2);
-#endif
     static constexpr bool TWO_LEVEL = (CT <= 4 && GPT == 1);
     static constexpr int RS = bwd_rec_floats(CT);
     static constexpr int NACC = N_MOMENTS + CT;
@@ -315,12 +305,12 @@ cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const Bw
     if (separable) return launch_backward_sep_chunk(ct, culling, a, p, s);
     const bool two = p.gauss_per_thread >= 2;
     switch (ct) {
-        case 1: return two ? launch_one<1, IGS_BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);
-        case 2: return two ? launch_one<2, IGS_BWD_GPT>(a, p, s) : launch_one<2, 1>(a, p, s);
-        case 3: return two ? launch_one<3, IGS_BWD_GPT>(a, p, s) : launch_one<3, 1>(a, p, s);
-        case 4: return two ? launch_one<4, IGS_BWD_GPT>(a, p, s) : launch_one<4, 1>(a, p, s);
+        case 1: return two ? launch_one<1, BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);
+        case 2: return two ? launch_one<2, BWD_GPT>(a, p, s) : launch_one<2, 1>(a, p, s);
+        case 3: return two ? launch_one<3, BWD_GPT>(a, p, s) : launch_one<3, 1>(a, p, s);
+        case 4: return two ? launch_one<4, BWD_GPT>(a, p, s) : launch_one<4, 1>(a, p, s);
         case 8: return launch_one<8, 1>(a, p, s);
-        case 16: return launch_one<16, IGS_BWD_GPT_16>(a, p, s);
+        case 16: return launch_one<16, BWD_GPT_16>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -343,17 +333,17 @@ static int occ(int device) {
 }
 
 // two gaussians per thread where the registers allow it (up to 4 channels per chunk)
-int backward_gauss_per_thread(int ct) { return ct > 8 ? IGS_BWD_GPT_16 : (ct > 4 ? 1 : IGS_BWD_GPT); }
+int backward_gauss_per_thread(int ct) { return ct > 8 ? BWD_GPT_16 : (ct > 4 ? 1 : BWD_GPT); }
 
 int backward_ctas_per_sm(int ct, int device) {
     const bool two = backward_gauss_per_thread(ct) >= 2;
     switch (ct) {
-        case 1: return two ? occ<1, IGS_BWD_GPT>(device) : occ<1, 1>(device);
-        case 2: return two ? occ<2, IGS_BWD_GPT>(device) : occ<2, 1>(device);
-        case 3: return two ? occ<3, IGS_BWD_GPT>(device) : occ<3, 1>(device);
-        case 4: return two ? occ<4, IGS_BWD_GPT>(device) : occ<4, 1>(device);
+        case 1: return two ? occ<1, BWD_GPT>(device) : occ<1, 1>(device);
+        case 2: return two ? occ<2, BWD_GPT>(device) : occ<2, 1>(device);
+        case 3: return two ? occ<3, BWD_GPT>(device) : occ<3, 1>(device);
+        case 4: return two ? occ<4, BWD_GPT>(device) : occ<4, 1>(device);
         case 8: return occ<8, 1>(device);
-        default: return occ<16, IGS_BWD_GPT_16>(device);
+        default: return occ<16, BWD_GPT_16>(device);
     }
 }
 int backward_threads(int) { return 128; }
@@ -362,26 +352,37 @@ int backward_chunk_pairs(int ct) { return ct <= 4 ? 256 : 128; }
 // ---------------------------------------------------------------------------
 // per-gaussian epilogue: slab partials -> gradients
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*N
-    if (i >= (long long)a.B * a.N) return;
+// One CTA finalises FIN_G consecutive gaussians.  First every warp adds up the slab partials
+// of some of the planes (in slab order; a warp's loads are 32 consecutive gaussians of one
+// plane, and the eight warps keep eight planes' worth of loads in flight), then the first
+// warp turns the sums into gradients, one gaussian per lane.
+constexpr int FIN_G = 32, FIN_THREADS = 256;
+
+__global__ void __launch_bounds__(FIN_THREADS) finalize_kernel(FinalizeArgs a) {
+    extern __shared__ float s_sum[];  // [planes][FIN_G]
+    const int lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
+    const long long total = (long long)a.B * a.N;
+    const long long i_raw = (long long)blockIdx.x * FIN_G + lane;  // over B*N
+    const long long i = i_raw < total ? i_raw : total - 1;
     const long long b = i / a.N, n = i - b * a.N;
-    float M[N_MOMENTS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const long long plane = a.N;
-    for (int s = 0; s < a.n_slab; ++s) {
-        const float* src = a.part + ((long long)s * a.B + b) * a.planes * plane + n;
-        for (int q = 0; q < a.n_chunks; ++q)
-#pragma unroll
-            for (int k = 0; k < N_MOMENTS; ++k) M[k] += src[(long long)(q * N_MOMENTS + k) * plane];
+    const long long slab_stride = (long long)a.B * a.planes * plane;
+    for (int p = wq; p < a.planes; p += FIN_THREADS / 32) {
+        const float* src = a.part + (b * a.planes + p) * plane + n;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < a.n_slab; ++s) acc += src[(long long)s * slab_stride];
+        s_sum[p * FIN_G + lane] = acc;
     }
+    __syncthreads();
+    if (wq != 0 || i_raw >= total) return;
+    float M[N_MOMENTS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int q = 0; q < a.n_chunks; ++q)
+#pragma unroll
+        for (int k = 0; k < N_MOMENTS; ++k) M[k] += s_sum[(q * N_MOMENTS + k) * FIN_G + lane];
     const ParamLayout& L = a.lay;
     const float al = a.alpha ? a.alpha[i] : 1.0f;
-    for (int c = 0; c < a.C; ++c) {
-        float e = 0.f;
-        for (int s = 0; s < a.n_slab; ++s)
-            e += a.part[(((long long)s * a.B + b) * a.planes + a.n_chunks * N_MOMENTS + c) * plane + n];
-        a.d_colors[i * L.col_s + c] = al * e;
-    }
+    for (int c = 0; c < a.C; ++c) a.d_colors[i * L.col_s + c] = al * s_sum[(a.n_chunks * N_MOMENTS + c) * FIN_G + lane];
     float c00, c01, c11;
     CovInv ci;
     float sx = 0.f, sy = 0.f, ex = 1.f, ey = 1.f;  // ex, ey: d scale / d (what the caller stores)
@@ -426,32 +427,13 @@ __global__ void __launch_bounds__(256) finalize_kernel(FinalizeArgs a) {
     }
 }
 
-__global__ void __launch_bounds__(256) slab_sum_kernel(const float* __restrict__ part, float* __restrict__ sums,
-                                                       int n_slab, long long per_slab) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= per_slab) return;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < n_slab; ++s) acc += part[(long long)s * per_slab + i];
-    sums[i] = acc;
-}
-
-cudaError_t launch_slab_sum(const float* part, float* sums, int n_slab, long long per_slab, cudaStream_t s) {
-    if (per_slab <= 0) return cudaSuccess;
-    {
-        KernelTimer timer(K_FINALIZE, s);
-        slab_sum_kernel<<<(unsigned)((per_slab + 255) / 256), 256, 0, s>>>(part, sums, n_slab, per_slab);
-    }
-    count_launch();
-    return cudaGetLastError();
-}
-
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s) {
     const long long n = (long long)a.B * a.N;
     if (n <= 0) return cudaSuccess;
     {
         KernelTimer timer(K_FINALIZE, s);
-        finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
+        // (planes <= 6 * 16 + 256: at most 45 KB, within the default dynamic limit)
+        finalize_kernel<<<(unsigned)((n + FIN_G - 1) / FIN_G), FIN_THREADS, (size_t)a.planes * FIN_G * sizeof(float), s>>>(a);
     }
     count_launch();
     return cudaGetLastError();

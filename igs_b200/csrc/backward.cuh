@@ -97,8 +97,6 @@ cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
 cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, int sm_count, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
-// sums[i] = part[0][i] + part[1][i] + ... (in that order), i over per_slab elements
-cudaError_t launch_slab_sum(const float* part, float* sums, int n_slab, long long per_slab, cudaStream_t s);
 cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
 
 }  // namespace igs

@@ -34,23 +34,17 @@
 
 namespace igs {
 
-#ifndef IGS_BWDW_THREADS
-#define IGS_BWDW_THREADS 64
-#endif
-#ifndef IGS_BWDW_MINCTAS
-#define IGS_BWDW_MINCTAS 8  // 16 warps per SM at 126 registers (10: 96 registers and a spill, slower)
-#endif
-#ifndef IGS_BWDW_STAGE
-#define IGS_BWDW_STAGE 32
-#endif
+constexpr int BWDW_THREADS = 64;
+constexpr int BWDW_MINCTAS = 8;  // 16 warps per SM at 126 registers (10: 96 registers and a spill, slower)
+constexpr int BWDW_STAGE = 32;
 
 template <int CT>
 struct BwdWarpCfg {
-    static constexpr int THREADS = IGS_BWDW_THREADS;
+    static constexpr int THREADS = BWDW_THREADS;
     static constexpr int WARPS = THREADS / 32;
-    static constexpr int STAGE_BLOCKS = IGS_BWDW_STAGE;  // 2x4-pixel blocks per warp-private stage
+    static constexpr int STAGE_BLOCKS = BWDW_STAGE;  // 2x4-pixel blocks per warp-private stage
     static constexpr int STAGES = 2;
-    static constexpr int MIN_CTAS = IGS_BWDW_MINCTAS;
+    static constexpr int MIN_CTAS = BWDW_MINCTAS;
     static constexpr int RS = bwd_sep_rec_floats(CT);
     static constexpr int PF = bwd_sep_pair_floats(CT);
     static constexpr size_t SMEM =
@@ -371,7 +365,7 @@ cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& 
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const int n_ctas = sm_count * IGS_BWDW_MINCTAS;  // as many warps as stay resident; each pulls tasks until none is left
+    const int n_ctas = sm_count * BWDW_MINCTAS;  // as many warps as stay resident; each pulls tasks until none is left
     switch (ct) {
         case 1: return launch_queue_one<1>(a, n_ctas, s);
         case 2: return launch_queue_one<2>(a, n_ctas, s);

@@ -35,12 +35,13 @@ constexpr float CULL_T = 130.0f;
 
 // Words of the workspace's 256-byte status area.
 constexpr int STATUS_WORD = 0;       // kernels: a bounded wait gave up
-constexpr int GRID_FLAG_WORD = 1;    // bit 0 = grid not separable, bit 1 = axes not monotone, bit 2 = upstream not finite
+constexpr int GRID_FLAG_WORD = 1;    // bit 0 = grid not separable, bit 1 = axes not monotone, bit 2 = upstream not finite,
+                                     // bit 3 = the separability check ran (bit 0 is an answer, not a default)
 constexpr int NARROW_COUNT_WORD = 2; // pack: gaussians whose reach is well inside the image
 constexpr int EXEC_COUNT_WORD = 4;   // (64 bits) culling kernels: (gaussian, pixel) evaluations not skipped
 constexpr int TASK_COUNT_WORD = 6;   // ordered backward: tasks on its list ...
 constexpr int TASK_NEXT_WORD = 7;    // ... and the next one to hand out
-constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2;
+constexpr int GRID_NOT_SEPARABLE = 1, GRID_NOT_MONOTONE = 2, GRID_CHECKED = 8;
 // Skipping a term w * t because w is exactly zero is only lossless while t is finite
 // (0 * NaN and 0 * inf are NaN).  Gaussians with a non-finite parameter get an infinite box
 // (pack.cu); a non-finite upstream value (gout / weight sum) sets this bit, and the backward
@@ -171,6 +172,7 @@ enum KernelId { K_PACK = 0, K_FORWARD, K_REDUCE, K_PIXEL_TERMS, K_BACKWARD, K_FI
 // otherwise does nothing.
 struct KernelTimer {
     int id;
+    int dev = -1;
     cudaStream_t stream;
     cudaEvent_t start = nullptr, stop = nullptr;
     KernelTimer(int id, cudaStream_t s);

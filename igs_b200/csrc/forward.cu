@@ -40,16 +40,8 @@ struct FwdCfg {
     static constexpr int PX = PX_;
     static constexpr int CHUNK_G = 128;  // gaussians per stage
     static constexpr int STAGES = 2;
-#ifdef IGS_FWD_MINCTAS
-    static constexpr int MIN_CTAS = IGS_FWD_MINCTAS;
-#else
     static constexpr int MIN_CTAS = (PX_ * (CT + 3) >= 128) ? 2 : ((PX_ * (CT + 3) >= 64) ? 3 : 4);
-#endif
-#ifdef IGS_FWD_UNROLL
-    static constexpr int UNROLL = IGS_FWD_UNROLL;
-#else
     static constexpr int UNROLL = CT <= 3 ? 4 : 2;
-#endif
     static constexpr int RS = fwd_rec_floats(CT);
     // The culling kernel spends little time per stage (most gaussians are skipped), so the
     // latency of a stage's copy shows unless more copies are in flight.
@@ -433,13 +425,12 @@ static cudaError_t launch_one(const FwdArgs& a, const FwdPlan& p, cudaStream_t s
     return cudaGetLastError();
 }
 
-#ifndef IGS_FWD_WIDE_PX
-#define IGS_FWD_WIDE_PX 8  // pixels per thread of the 8- and 16-channel instantiations (4: fewer registers, measured 6 % slower at C = 16)
-#endif
-int forward_px_per_thread(int ct) { return ct > 4 ? IGS_FWD_WIDE_PX : 8; }
+// 8 pixels per thread at every channel count (4 for the 8- and 16-channel instantiations
+// needs fewer registers but measured 6 % slower at C = 16)
+int forward_px_per_thread(int) { return 8; }
 
-// separable instantiations exist where the general one uses 8 pixels per thread
-bool forward_has_separable(int ct) { return ct <= 4 || IGS_FWD_WIDE_PX == 8; }
+// every channel count has a separable instantiation
+bool forward_has_separable(int) { return true; }
 
 cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const FwdArgs& a, const FwdPlan& p,
                                  cudaStream_t s) {
@@ -449,10 +440,8 @@ cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const Fwd
             case 2: return launch_one<2, 8, true, true>(a, p, s);
             case 3: return launch_one<3, 8, true, true>(a, p, s);
             case 4: return launch_one<4, 8, true, true>(a, p, s);
-#if IGS_FWD_WIDE_PX == 8
             case 8: return launch_one<8, 8, true, true>(a, p, s);
             case 16: return launch_one<16, 8, true, true>(a, p, s);
-#endif
         }
         return cudaErrorInvalidValue;
     }
@@ -462,10 +451,8 @@ cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const Fwd
             case 2: return launch_one<2, 8, true, false>(a, p, s);
             case 3: return launch_one<3, 8, true, false>(a, p, s);
             case 4: return launch_one<4, 8, true, false>(a, p, s);
-#if IGS_FWD_WIDE_PX == 8
             case 8: return launch_one<8, 8, true, false>(a, p, s);
             case 16: return launch_one<16, 8, true, false>(a, p, s);
-#endif
         }
         return cudaErrorInvalidValue;
     }
@@ -474,8 +461,8 @@ cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const Fwd
         case 2: return launch_one<2, 8, false, false>(a, p, s);
         case 3: return launch_one<3, 8, false, false>(a, p, s);
         case 4: return launch_one<4, 8, false, false>(a, p, s);
-        case 8: return launch_one<8, IGS_FWD_WIDE_PX, false, false>(a, p, s);
-        case 16: return launch_one<16, IGS_FWD_WIDE_PX, false, false>(a, p, s);
+        case 8: return launch_one<8, 8, false, false>(a, p, s);
+        case 16: return launch_one<16, 8, false, false>(a, p, s);
     }
     return cudaErrorInvalidValue;
 }
@@ -515,8 +502,8 @@ int forward_ctas_per_sm(int ct, int device) {
         case 2: return occ<2, 8>(device);
         case 3: return occ<3, 8>(device);
         case 4: return occ<4, 8>(device);
-        case 8: return occ<8, IGS_FWD_WIDE_PX>(device);
-        default: return occ<16, IGS_FWD_WIDE_PX>(device);
+        case 8: return occ<8, 8>(device);
+        default: return occ<16, 8>(device);
     }
 }
 int forward_threads(int) { return 128; }

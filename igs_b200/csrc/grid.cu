@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(256) grid_check_kernel(GridCheckArgs a) {
         for (int k = 0; k < 4; ++k) bad |= (xv[k] != xf[k]) || (yv[k] != y0);
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(a.flag, GRID_NOT_SEPARABLE);
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(a.flag, GRID_CHECKED);  // for hosts that remember the answer
 }
 
 GridKind classify_grid(long long xs_h, long long ys_w, int H, int W, bool kernels_available) {

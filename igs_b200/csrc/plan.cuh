@@ -51,7 +51,6 @@ struct BwdPlan {
     size_t off_geo;
     size_t off_prec[MAX_CHUNKS];
     size_t off_part;       // [n_slab][B][planes][N]
-    size_t off_sum;        // [B][planes][N]: the slab partials added up (when there are many slabs)
     size_t off_tasks;      // ordered skipping path: [task_capacity] int4, then [B][ceil(N/32)] int4
     int task_capacity;     // B * ceil(N/32) * (most slabs either partition has); 0 without separable kernels
     size_t part_bytes;     // size of the partial sums of the partition in use
@@ -84,7 +83,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
                  size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr,
-                 const ParamLayout* layout = nullptr, const int* order = nullptr);
+                 const ParamLayout* layout = nullptr, const int* order = nullptr, int hints = 0);
 
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);

@@ -22,12 +22,15 @@
 // different streams) would write the same bytes at the same time: the caller must
 // order them on one stream.
 //
-// First call.  The array's name is a host-side handle, not a device address; the
-// device address is looked up with cudaGetSymbolAddress the first time the entry point
-// runs on a device (with that device current) and remembered.  Make that first call
-// during start-up, before any stream capture is begun on that device.
-#include <mutex>
-
+// Address.  The array's name is a host-side handle, not a device address; every call
+// looks the device address up with cudaGetSymbolAddress while its device is current (a
+// cheap host-side lookup once the library's device code is loaded, and it stays right if
+// the application tears the device's context down and brings it up again).  The very
+// first lookup on a device may load the device code: make the first call during start-up,
+// before any stream capture is begun on that device.
+//
+// Status.  A kernel that gives up on a bounded wait sets the first word of the array, which
+// the caller cannot reach through a workspace pointer: igs_read_status_static reads it.
 #include "pack.cuh"
 #include "plan.cuh"
 
@@ -35,21 +38,22 @@ namespace igs {
 
 static __device__ __align__(256) unsigned char g_static_scratch[IGS_STATIC_SCRATCH_BYTES];
 
-static std::mutex g_scratch_mu;
-static void* g_scratch_addr[64];
+// Device address of the array on the current device.
+static int static_scratch_address(void** out) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return IGS_ERR_DEVICE;
+    *out = p;
+    return IGS_OK;
+}
 
-// Device address of the array on `device`, which must be the current device.
-static int static_scratch_address(int device, void** out) {
-    if (device < 0 || device >= 64) return IGS_ERR_DEVICE;
-    std::lock_guard<std::mutex> lock(g_scratch_mu);
-    if (!g_scratch_addr[device]) {
-        void* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (e != cudaSuccess) return (int)e;
-        if (!p) return IGS_ERR_DEVICE;
-        g_scratch_addr[device] = p;
+static int check_device_index(int device) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return IGS_ERR_DEVICE;
     }
-    *out = g_scratch_addr[device];
     return IGS_OK;
 }
 
@@ -63,11 +67,13 @@ extern "C" int igs_forward_sr_static(const float* positions, const float* scales
                                      int H, int W, int C, float eps, int normalize, float* out, float* wsum, int device,
                                      void* stream) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
+    int rc = check_device_index(device);
+    if (rc) return rc;
     DeviceGuard guard(device);
     if (!guard.ok) return IGS_ERR_DEVICE;
 
     FwdPlan p;
-    int rc = plan_forward(B, N, H, W, C, device, &p);
+    rc = plan_forward(B, N, H, W, C, device, &p);
     if (rc) return rc;
     if (p.bytes > IGS_STATIC_SCRATCH_BYTES) {
         // fall back to a single gaussian split: no partial sums, only the records
@@ -79,9 +85,21 @@ extern "C" int igs_forward_sr_static(const float* positions, const float* scales
     if (p.bytes > IGS_STATIC_SCRATCH_BYTES) return IGS_ERR_LIMIT;
 
     void* scratch = nullptr;
-    rc = static_scratch_address(device, &scratch);
+    rc = static_scratch_address(&scratch);
     if (rc) return rc;
     return forward_impl(SHAPE_SCALE_ROT, positions, scales, rotations, nullptr, alphas, colors, x, x_strides, y,
                         y_strides, B, N, H, W, C, eps, normalize, out, wsum, scratch, IGS_STATIC_SCRATCH_BYTES, device,
                         stream, &p);
+}
+
+extern "C" int igs_read_status_static(int device, void* stream, int* host_status) {
+    if (!host_status) return IGS_ERR_ARG;
+    int rc = check_device_index(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    return igs_read_status(scratch, device, stream, host_status);
 }

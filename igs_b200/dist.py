@@ -12,9 +12,12 @@ the batch / gaussian structure of ``src/igs/gs2d.py:275-337`` allows):
   rank normalises, and the backward is local: a rank produces the gradients of its own
   gaussians only.  ``sharded_gaussian_splatting_2d`` does this.
 
-Before the collective the ranks compare shapes on the host (``check_consistent``), so a
-rank that was handed a different image size raises on every rank instead of hanging or
-corrupting the reduction.
+Before a group's first collective on a given shape the ranks compare shapes on the host
+(``check_consistent``), so a rank that was handed a different image size raises on every
+rank instead of hanging or corrupting the reduction.  The comparison costs a collective of
+its own and a device-to-host read, so it runs once per (group, shape), not per step: it
+catches a job that was set up inconsistently, not a rank whose shape changes later while
+the others' stay.
 """
 from __future__ import annotations
 
@@ -39,6 +42,18 @@ def gaussian_range(N: int, world: int, rank: int):
     return batch_range(N, world, rank)
 
 
+_checked = set()  # (id of the group, the values) that have passed check_consistent
+
+
+def check_consistent_once(values, group=None):
+    """check_consistent the first time this process sees `values` for `group`; nothing after."""
+    key = (id(group) if group is not None else 0, tuple(int(v) for v in values))
+    if key in _checked:
+        return
+    check_consistent(values, group)
+    _checked.add(key)
+
+
 def check_consistent(values, group=None):
     """All ranks must pass the same integers (image size, channels, batch): gathers them on
     the host side of the collective and raises ValueError on every rank if they differ."""
@@ -54,13 +69,21 @@ def check_consistent(values, group=None):
 
 
 class CudaSplatBackend:
-    """The three device calls the sharded op is built from (libigs_b200.so)."""
+    """The three device calls the sharded op is built from (libigs_b200.so).  `info` is what
+    `prepare` returned for the step: grid views, hints and the memos of the call layer."""
 
     @staticmethod
-    def forward_sums(pos, col, sc, rot, al, x3, y3, eps):
+    def prepare(x, y, pos):
         from . import _lib
 
-        sums, _ = _lib.forward("sr", pos, sc, rot, None, al, col, x3, y3, eps, normalize=False)
+        return _lib.prepare_call(x, y, pos)
+
+    @staticmethod
+    def forward_sums(pos, col, sc, rot, al, x3, y3, eps, info=None):
+        from . import _lib
+
+        sums, _ = _lib.forward("sr", pos, sc, rot, None, al, col, x3, y3, eps, normalize=False,
+                               order=info.order if info else None, hints=info.hints if info else 0, info=info)
         return sums
 
     @staticmethod
@@ -70,23 +93,38 @@ class CudaSplatBackend:
         return _lib.normalize(sums, eps)
 
     @staticmethod
-    def backward(pos, col, sc, rot, al, x3, y3, wsum, out, gout, eps, grad_mode):
+    def backward(pos, col, sc, rot, al, x3, y3, wsum, out, gout, eps, grad_mode, info=None, order=None):
         from . import _lib
 
-        return _lib.backward("sr", pos, sc, rot, None, al, col, x3, y3, wsum, out, gout, eps, grad_mode, False)
+        return _lib.backward("sr", pos, sc, rot, None, al, col, x3, y3, wsum, out, gout, eps, grad_mode, False,
+                             order=order, hints=info.hints if info else 0, info=info)
+
+
+def _plain_views(x, y, B):
+    H, W = x.shape[2], x.shape[3]
+    return x[:, 0].expand(B, H, W), y[:, 0].expand(B, H, W)
 
 
 class _ShardedSplat(torch.autograd.Function):
     @staticmethod
     def forward(ctx, positions, colors, scales, rotations, alphas, x, y, eps, group, backend):
         B = positions.shape[0]
-        x3, y3 = gs2d._grid_views(x, y, B)
         pos, col, sc, rot, al = (t.contiguous() for t in (positions, colors, scales, rotations, alphas))
-        check_consistent((B, col.shape[2], x3.shape[1], x3.shape[2]), group)
-        sums = backend.forward_sums(pos, col, sc, rot, al, x3, y3, eps)
+        check_consistent_once((B, col.shape[2], x.shape[2], x.shape[3]), group)
+        if hasattr(backend, "prepare"):
+            info = backend.prepare(x, y, pos)
+            sums = backend.forward_sums(pos, col, sc, rot, al, info.x3, info.y3, eps, info=info)
+        else:
+            info = None
+            x3, y3 = _plain_views(x, y, B)
+            sums = backend.forward_sums(pos, col, sc, rot, al, x3, y3, eps)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
         out, wsum = backend.normalize(sums, eps)
-        ctx.save_for_backward(x, y, pos, col, sc, rot, al, wsum, out)
+        if info is not None:
+            gs2d._save_call(ctx, info, x, y, pos, col, sc, rot, al, wsum, out)
+        else:
+            ctx.save_for_backward(x, y, pos, col, sc, rot, al, wsum, out)
+            ctx.call_info = None
         ctx.eps, ctx.backend = float(eps), backend
         ctx.grad_mode = gs2d._GRAD_MODES[gs2d.get_grad_mode()]
         return out
@@ -94,12 +132,17 @@ class _ShardedSplat(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, pos, col, sc, rot, al, wsum, out = ctx.saved_tensors
         if ctx.needs_input_grad[5] or ctx.needs_input_grad[6]:
             raise NotImplementedError("gradients of x_grid / y_grid are not available in the gaussian-sharded op")
-        x3, y3 = gs2d._grid_views(x, y, pos.shape[0])
-        g = ctx.backend.backward(pos, col, sc, rot, al, x3, y3, wsum, out, grad_result.contiguous(), ctx.eps,
-                                 ctx.grad_mode)
+        if ctx.call_info is not None:
+            (x, y, pos, col, sc, rot, al, wsum, out), x3, y3, order = gs2d._saved_call(ctx)
+            g = ctx.backend.backward(pos, col, sc, rot, al, x3, y3, wsum, out, grad_result.contiguous(), ctx.eps,
+                                     ctx.grad_mode, info=ctx.call_info, order=order)
+        else:
+            x, y, pos, col, sc, rot, al, wsum, out = ctx.saved_tensors
+            x3, y3 = _plain_views(x, y, pos.shape[0])
+            g = ctx.backend.backward(pos, col, sc, rot, al, x3, y3, wsum, out, grad_result.contiguous(), ctx.eps,
+                                     ctx.grad_mode)
         return (g["positions"], g["colors"], g["scales"], g["rotations"], g["alphas"], None, None, None, None, None)
 
 

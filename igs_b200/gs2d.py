@@ -94,16 +94,24 @@ def _require_cuda_f32(name, t):
         raise TypeError(f"{name} must be float32 (the reference computes in fp32), got {t.dtype}")
 
 
-def _grid_views(x, y, B):
-    """[B,1,H,W] (or [1,1,H,W]) sample coordinates -> [B,H,W] views, no copy."""
-    if x.dim() != 4 or y.dim() != 4 or x.shape[1] != 1 or y.shape[1] != 1:
-        raise ValueError(f"x and y must be [B,1,H,W]; got {tuple(x.shape)} and {tuple(y.shape)}")
-    if x.shape != y.shape:
-        raise ValueError(f"x {tuple(x.shape)} and y {tuple(y.shape)} differ")
-    if x.shape[0] not in (B, 1):
-        raise ValueError(f"x/y batch {x.shape[0]} does not match the gaussians' batch {B}")
-    H, W = x.shape[2], x.shape[3]
-    return x[:, 0].expand(B, H, W), y[:, 0].expand(B, H, W)
+def _save_call(ctx, info, x, y, *tensors):
+    """Saves a forward's tensors plus what the call decided (grid views' kind, hints,
+    processing order) so that the backward runs the same kernels on the same views."""
+    ctx.save_for_backward(x, y, *tensors, info.order if info.order is not None else x.new_empty(0))
+    ctx.has_order = info.order is not None
+    ctx.as_separable = info.as_separable
+    ctx.hints = info.hints
+    info.x3 = info.y3 = info.order = None  # only the memos stay on the context
+    ctx.call_info = info
+
+
+def _saved_call(ctx):
+    """-> (the saved tensors without the order, x3, y3, order or None)."""
+    *tensors, order = ctx.saved_tensors
+    x, y = tensors[0], tensors[1]
+    B = tensors[2].shape[0]
+    x3, y3 = _lib.grid_views(x, y, B, ctx.as_separable)
+    return tensors, x3, y3, (order if ctx.has_order else None)
 
 
 def _check_gaussians(position, alphas, colors):
@@ -152,15 +160,16 @@ class GaussianSplatting2DKernel(torch.autograd.Function):
             _require_cuda_f32(n, t)
         _same_device(*tensors)
         B, N, C = _check_gaussians(position, alphas, colors)
-        x3, y3 = _grid_views(x, y, B)
         cov = []
         for n, t in zip(names[3:6], tensors[3:6]):
             if t.numel() != B * N:
                 raise ValueError(f"{n} must hold B*N = {B * N} values, got shape {tuple(t.shape)}")
             cov.append(t.reshape(B, N).contiguous())
         pos, al, col = position.contiguous(), alphas.contiguous(), colors.contiguous()
-        out, wsum = _lib.forward("cov", pos, cov[0], cov[1], cov[2], al, col, x3, y3, eps)
-        ctx.save_for_backward(x, y, pos, cov[0], cov[1], cov[2], al, col, wsum, out)
+        info = _lib.prepare_call(x, y, pos)
+        out, wsum = _lib.forward("cov", pos, cov[0], cov[1], cov[2], al, col, info.x3, info.y3, eps,
+                                 order=info.order, hints=info.hints, info=info)
+        _save_call(ctx, info, x, y, pos, cov[0], cov[1], cov[2], al, col, wsum, out)
         ctx.eps = float(eps)
         ctx.grad_mode = _GRAD_MODES[_grad_mode]
         ctx.cov_shapes = tuple(t.shape for t in tensors[3:6])
@@ -169,12 +178,10 @@ class GaussianSplatting2DKernel(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, pos, c00, c01, c11, al, col, wsum, out = ctx.saved_tensors
-        B = pos.shape[0]
-        x3, y3 = _grid_views(x, y, B)
+        (x, y, pos, c00, c01, c11, al, col, wsum, out), x3, y3, order = _saved_call(ctx)
         want_xy = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
         g = _lib.backward("cov", pos, c00, c01, c11, al, col, x3, y3, wsum, out, grad_result.contiguous(),
-                          ctx.eps, ctx.grad_mode, want_xy)
+                          ctx.eps, ctx.grad_mode, want_xy, order=order, hints=ctx.hints, info=ctx.call_info)
         gx = _reduce_like(g["x"][:, None], x.shape) if want_xy else None
         gy = _reduce_like(g["y"][:, None], y.shape) if want_xy else None
         s00, s01, s11 = ctx.cov_shapes
@@ -199,15 +206,13 @@ class _SplatFromScaleRotation(torch.autograd.Function):
             raise ValueError(f"scales must be [B,N,2] = {(B, N, 2)}, got {tuple(scales.shape)}")
         if rotations.shape != (B, N):
             raise ValueError(f"rotations must be [B,N] = {(B, N)}, got {tuple(rotations.shape)}")
-        x3, y3 = _grid_views(x, y, B)
         pos, col, sc, rot, al = (t.contiguous() for t in (positions, colors, scales, rotations, alphas))
-        # one spatial order per step (if the policy wants one), shared by forward and backward
-        order, probe = _lib.order_by_policy(pos, None, None, x3, y3)
-        out, wsum, ws = _lib.forward("sr", pos, sc, rot, None, al, col, x3, y3, eps, keep_workspace=True, order=order)
-        if probe is not None:
-            probe.queue(ws)
-        ctx.save_for_backward(x, y, pos, col, sc, rot, al, wsum, out, order if order is not None else wsum.new_empty(0))
-        ctx.has_order = order is not None
+        # grid views, hints and one spatial order per step (if the policy wants one), shared by
+        # forward and backward
+        info = _lib.prepare_call(x, y, pos)
+        out, wsum = _lib.forward("sr", pos, sc, rot, None, al, col, info.x3, info.y3, eps, order=info.order,
+                                 hints=info.hints, info=info)
+        _save_call(ctx, info, x, y, pos, col, sc, rot, al, wsum, out)
         ctx.eps = float(eps)
         ctx.grad_mode = _GRAD_MODES[_grad_mode]
         return out
@@ -215,12 +220,10 @@ class _SplatFromScaleRotation(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, pos, col, sc, rot, al, wsum, out, order = ctx.saved_tensors
-        B = pos.shape[0]
-        x3, y3 = _grid_views(x, y, B)
+        (x, y, pos, col, sc, rot, al, wsum, out), x3, y3, order = _saved_call(ctx)
         want_xy = ctx.needs_input_grad[5] or ctx.needs_input_grad[6]
         g = _lib.backward("sr", pos, sc, rot, None, al, col, x3, y3, wsum, out, grad_result.contiguous(), ctx.eps,
-                          ctx.grad_mode, want_xy, order=order if ctx.has_order else None, policy=False)
+                          ctx.grad_mode, want_xy, order=order, hints=ctx.hints, info=ctx.call_info)
         gx = _reduce_like(g["x"][:, None], x.shape) if want_xy else None
         gy = _reduce_like(g["y"][:, None], y.shape) if want_xy else None
         return g["positions"], g["colors"], g["scales"], g["rotations"], g["alphas"], gx, gy, None
@@ -249,16 +252,11 @@ class _SplatFromFeature(torch.autograd.Function):
             if pos_offset.shape != (B, N, 2):
                 raise ValueError(f"the position offsets must be [B,N,2] = {(B, N, 2)}, got {tuple(pos_offset.shape)}")
             off = pos_offset.contiguous()
-        x3, y3 = _grid_views(x, y, B)
-        order, probe = _lib.order_by_policy(None, feat, off, x3, y3)
-        out, wsum, ws = _lib.forward_feature(feat, off, x3, y3, eps, order=order, keep_workspace=True)
-        if probe is not None:
-            probe.queue(ws)
-        none = feat.new_empty(0)
-        ctx.save_for_backward(x, y, feat, off if off is not None else none, wsum, out,
-                              order if order is not None else none)
+        info = _lib.prepare_call(x, y, None, feat, off)
+        out, wsum = _lib.forward_feature(feat, off, info.x3, info.y3, eps, order=info.order, hints=info.hints,
+                                         info=info)
+        _save_call(ctx, info, x, y, feat, off if off is not None else feat.new_empty(0), wsum, out)
         ctx.has_off = off is not None
-        ctx.has_order = order is not None
         ctx.eps = float(eps)
         ctx.grad_mode = _GRAD_MODES[_grad_mode]
         return out
@@ -266,11 +264,10 @@ class _SplatFromFeature(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_result):
-        x, y, feat, off, wsum, out, order = ctx.saved_tensors
-        x3, y3 = _grid_views(x, y, feat.shape[0])
+        (x, y, feat, off, wsum, out), x3, y3, order = _saved_call(ctx)
         d_feat = _lib.backward_feature(feat, off if ctx.has_off else None, x3, y3, wsum, out,
-                                       grad_result.contiguous(), ctx.eps, ctx.grad_mode,
-                                       order=order if ctx.has_order else None, policy=False)
+                                       grad_result.contiguous(), ctx.eps, ctx.grad_mode, order=order, hints=ctx.hints,
+                                       info=ctx.call_info)
         d_off = d_feat[..., :2] if (ctx.has_off and ctx.needs_input_grad[1]) else None
         return d_feat, d_off, None, None, None
 

@@ -1,7 +1,10 @@
 // Micro-benchmarks that give the roofline its denominators on the GPU at hand:
 // the issue rate of the FP32 FMA pipe (scalar FFMA and packed f32x2 FMA) and of the
-// MUFU ex2 unit, each from a kernel that does nothing else.
-#include "common.cuh"
+// MUFU ex2 unit, each from a kernel that does nothing else.  Bench tooling: built into
+// its own small library (libigs_probes.so), not into the splat library.  Each entry point
+// synchronises and writes a rate to a HOST double; return 0 = ok, -1 = bad argument,
+// -4 = device cannot be selected, positive = cudaError_t.
+#include "../csrc/common.cuh"
 
 namespace igs {
 
@@ -116,6 +119,15 @@ static double best_time(F launch, cudaError_t* err) {
     return best;
 }
 
+static int probe_sm_count(int device) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 148;
+    }
+    return n;
+}
+
 }  // namespace igs
 
 using namespace igs;
@@ -126,7 +138,7 @@ int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s) {
     if (!lane_instr_per_s) return IGS_ERR_ARG;
     DeviceGuard guard(device);
     if (!guard.ok) return IGS_ERR_DEVICE;
-    const int blocks = sm_count(device) * 16;
+    const int blocks = probe_sm_count(device) * 16;
     cudaError_t err;
     const double t = best_time(
         [&] {
@@ -134,7 +146,6 @@ int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s) {
                 probe_ffma2_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
             else
                 probe_ffma_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
-            count_launch();
         },
         &err);
     if (err != cudaSuccess) return (int)err;
@@ -149,7 +160,7 @@ int igs_probe_mix_rate(int device, int backward_mix, double* lane_instr_per_s) {
     if (!guard.ok) return IGS_ERR_DEVICE;
     // 96 KB of (unused) dynamic shared memory per CTA holds residency at 2 CTAs of 256
     // threads per SM: the splat kernels' own 16 warps per SM
-    const int blocks = sm_count(device) * 8;
+    const int blocks = probe_sm_count(device) * 8;
     cudaError_t err = backward_mix ? cudaFuncSetAttribute(probe_mix_kernel<22>,
                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)
                                    : cudaFuncSetAttribute(probe_mix_kernel<11>,
@@ -161,7 +172,6 @@ int igs_probe_mix_rate(int device, int backward_mix, double* lane_instr_per_s) {
                 probe_mix_kernel<22><<<blocks, PROBE_THREADS, 96 * 1024>>>(nullptr, 0.999f, 0.001f);
             else
                 probe_mix_kernel<11><<<blocks, PROBE_THREADS, 96 * 1024>>>(nullptr, 0.999f, 0.001f);
-            count_launch();
         },
         &err);
     if (err != cudaSuccess) return (int)err;
@@ -175,12 +185,11 @@ int igs_probe_ex2_rate(int device, double* results_per_s) {
     if (!results_per_s) return IGS_ERR_ARG;
     DeviceGuard guard(device);
     if (!guard.ok) return IGS_ERR_DEVICE;
-    const int blocks = sm_count(device) * 16;
+    const int blocks = probe_sm_count(device) * 16;
     cudaError_t err;
     const double t = best_time(
         [&] {
             probe_ex2_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.5f);
-            count_launch();
         },
         &err);
     if (err != cudaSuccess) return (int)err;

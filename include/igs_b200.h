@@ -11,7 +11,8 @@
  *   - every pointer is a DEVICE pointer on `device` unless stated otherwise; all
  *     tensors are fp32 and contiguous except x / y, which carry element strides;
  *   - `stream` is a cudaStream_t passed as void*; nothing synchronises the stream
- *     except igs_read_status and igs_probe_*;
+ *     except igs_read_status, igs_read_status_static,
+ *     igs_read_executed and igs_profile_read;
  *   - the library never allocates: scratch comes in through `workspace`, whose
  *     size igs_workspace_bytes reports; the first 256 bytes of a workspace hold a
  *     status word the kernels set if one of their bounded waits gives up;
@@ -44,6 +45,23 @@ extern "C" {
 /* gradient of the per-pixel normalisation term, see igs_backward_* */
 #define IGS_GRAD_REFERENCE 0  /* gS = -sum_c g_c^2 / S^2, src/igs/gs2d.py:370 (and :176) */
 #define IGS_GRAD_EXACT 1      /* gS = -sum_c (g_c/S) out_c, autograd of src/igs/gs2d.py:24-44 */
+
+/*
+ * `hints` of igs_forward_* / igs_backward_*: what the caller already knows about its data,
+ * OR-ed together; 0 = nothing.  Without a hint the library finds both facts out on the
+ * device and launches every kernel instantiation that could apply (those the data does
+ * not call for return at once); a hint only removes launches.  Both hints name the
+ * instantiation that is correct for any data, so a wrong hint costs time, never a bit of
+ * the result.
+ *   IGS_HINT_WIDE_GAUSSIANS: few gaussians are narrow (igs_read_status_words, word 2): only
+ *                            the plain kernels are launched, not the culling ones;
+ *   IGS_HINT_GENERAL_GRID:   x / y are not a separable grid (x by column, y by row): only
+ *                            the general kernels are launched, and the grid is not checked.
+ * A caller that knows its grid IS separable says so through the strides: row stride 0 for
+ * x and column stride 0 for y (then nothing is checked and only the separable kernels run).
+ */
+#define IGS_HINT_WIDE_GAUSSIANS 1
+#define IGS_HINT_GENERAL_GRID 2
 
 int igs_version(void);
 const char* igs_strerror(int code);
@@ -78,8 +96,8 @@ int igs_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* f
 int igs_forward_sr(const float* positions, const float* scales, const float* rotations,
                    const float* alphas, const float* colors, const float* x, const int64_t* x_strides,
                    const float* y, const int64_t* y_strides, int B, int N, int H, int W, int C,
-                   float eps, int normalize, float* out, float* wsum, const int* order, void* workspace,
-                   size_t workspace_bytes, int device, void* stream);
+                   float eps, int normalize, float* out, float* wsum, const int* order, int hints,
+                   void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
  * Forward from inverse-covariance entries.  Replaces
@@ -91,15 +109,18 @@ int igs_forward_cov(const float* positions, const float* cov_inv_00, const float
                     const float* cov_inv_11, const float* alphas, const float* colors, const float* x,
                     const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
                     int H, int W, int C, float eps, int normalize, float* out, float* wsum,
-                    const int* order, void* workspace, size_t workspace_bytes, int device, void* stream);
+                    const int* order, int hints, void* workspace, size_t workspace_bytes, int device,
+                    void* stream);
 
 /*
  * igs_forward_sr without a workspace argument, for hosts that cannot allocate device
  * memory (a plug-in inside another application's memory budget, a loop that must stay
  * off the driver's allocator).  No counterpart in the reference: it is an addition of
- * this library.  Same arguments, results and return codes as igs_forward_sr; the
- * scratch is a fixed array of IGS_STATIC_SCRATCH_BYTES inside the library's device
- * image (held on every GPU that loads the library until the process exits).
+ * this library.  Same arguments and return codes as igs_forward_sr (minus order, hints and
+ * the workspace) and the same results up to the order of summation (the gaussian splits
+ * may differ, see below); the scratch is a fixed array of IGS_STATIC_SCRATCH_BYTES inside
+ * the library's device image (held on every GPU that loads the library until the process
+ * exits).
  *   - returns IGS_ERR_LIMIT when the shape needs more scratch than that: with C <= 4
  *     the records take 48 bytes per gaussian (B*N*48 <= 8 MiB, about 170k gaussians);
  *     gaussian splits are dropped first if their partial sums would not fit;
@@ -107,8 +128,11 @@ int igs_forward_cov(const float* positions, const float* cov_inv_00, const float
  *     profiling, igs_profile_enable, must stay off: it creates events);
  *   - all calls on a device share the one array: calls whose kernels could overlap on
  *     the GPU must be ordered on one stream by the caller;
- *   - the first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress); make it at start-up, before any stream capture begins.
+ *   - every call looks up the array's device address (cudaGetSymbolAddress, with `device`
+ *     current); the first such call on a device may load the library's device code, so
+ *     make it at start-up, before any stream capture begins;
+ *   - a kernel that gave up on a bounded wait reports through the array's status word:
+ *     igs_read_status_static reads it.
  */
 #define IGS_STATIC_SCRATCH_BYTES (8u << 20)
 int igs_forward_sr_static(const float* positions, const float* scales, const float* rotations,
@@ -148,7 +172,7 @@ int igs_backward_sr(const float* positions, const float* scales, const float* ro
                     const float* y, const int64_t* y_strides, const float* wsum, const float* out,
                     const float* gout, int B, int N, int H, int W, int C, float eps, int grad_mode,
                     float* d_positions, float* d_scales, float* d_rotations, float* d_alphas,
-                    float* d_colors, float* d_x, float* d_y, const int* order, void* workspace,
+                    float* d_colors, float* d_x, float* d_y, const int* order, int hints, void* workspace,
                     size_t workspace_bytes, int device, void* stream);
 
 /*
@@ -162,8 +186,8 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                      const float* wsum, const float* out, const float* gout, int B, int N, int H, int W,
                      int C, float eps, int grad_mode, float* d_positions, float* d_cov_inv_00,
                      float* d_cov_inv_01, float* d_cov_inv_11, float* d_alphas, float* d_colors,
-                     float* d_x, float* d_y, const int* order, void* workspace, size_t workspace_bytes,
-                     int device, void* stream);
+                     float* d_x, float* d_y, const int* order, int hints, void* workspace,
+                     size_t workspace_bytes, int device, void* stream);
 
 /*
  * The splat driven directly by the module's projection output.  Replaces what
@@ -179,12 +203,13 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
 int igs_forward_feature(const float* gs_feature, const float* pos_offset, const float* x,
                         const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
                         int H, int W, int C, float eps, int normalize, float* out, float* wsum,
-                        const int* order, void* workspace, size_t workspace_bytes, int device, void* stream);
+                        const int* order, int hints, void* workspace, size_t workspace_bytes, int device,
+                        void* stream);
 int igs_backward_feature(const float* gs_feature, const float* pos_offset, const float* x,
                          const int64_t* x_strides, const float* y, const int64_t* y_strides,
                          const float* wsum, const float* out, const float* gout, int B, int N, int H,
                          int W, int C, float eps, int grad_mode, float* d_feature, const int* order,
-                         void* workspace, size_t workspace_bytes, int device, void* stream);
+                         int hints, void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
  * Synchronises `stream`, copies the workspace's status word to *host_status
@@ -193,11 +218,40 @@ int igs_backward_feature(const float* gs_feature, const float* pos_offset, const
 int igs_read_status(const void* workspace, int device, void* stream, int* host_status);
 
 /*
+ * The same check for igs_forward_sr_static, whose caller has no workspace pointer: reads
+ * the status word of the library's fixed scratch array on `device` (what the last
+ * igs_forward_sr_static call on that device left).  Synchronises `stream`.
+ */
+int igs_read_status_static(int device, void* stream, int* host_status);
+
+/*
+ * Asynchronous read of what the last forward or backward on this workspace found out about
+ * its data: queues on `stream` a copy of the first IGS_STATUS_WORDS words of the status
+ * area into host_words (HOST pointer to IGS_STATUS_WORDS ints, pinned for a copy that does
+ * not block) and returns at once; the values are there when the stream has reached that
+ * point.  Never synchronises.
+ *   word 0: non-zero if a kernel gave up on a bounded wait (the result is then invalid);
+ *   word 1: bit 0 = the grid is NOT separable (only set when the library had to check),
+ *           bit 1 = an axis is not non-decreasing, bit 2 = a non-finite upstream value;
+ *   word 2: the number of narrow gaussians (see igs_read_narrow_count).
+ * A host remembers these to pass `hints` (or stride-0 grid views) on later calls.
+ */
+#define IGS_STATUS_WORDS 8
+int igs_read_status_words(const void* workspace, int device, void* stream, int* host_words);
+
+/*
  * Launch geometry the library would use (for reports): pixels per forward CTA,
  * gaussian splits, backward threads per CTA and pixel slabs.  Any pointer may be NULL.
  */
 int igs_describe_plan(int B, int N, int H, int W, int C, int device, int* fwd_tile_pixels,
                       int* fwd_splits, int* bwd_threads, int* bwd_slabs);
+
+/*
+ * For reports: whether kernels specialised for separable grids (x by column, y by row; what
+ * xy_grid makes) exist for C channels, forward and backward (1 / 0).  They issue fewer
+ * FMA-pipe instructions per evaluation than the general kernels.  Either pointer may be NULL.
+ */
+int igs_describe_kernels(int C, int* forward_separable, int* backward_separable);
 
 /*
  * Lossless culling, on by default.  A weight ex2(q) is exactly zero once its exponent is
@@ -279,17 +333,6 @@ int igs_mse_grad(const float* out, const float* target, long long n, const float
 int igs_profile_enable(int on);
 int igs_profile_reset(void);
 int igs_profile_read(int kernel_id, double* total_ms, long long* launches);
-
-/*
- * Micro-benchmarks used as roofline denominators; each synchronises and writes a
- * rate to a HOST double: fp32 lane-instructions per second of the FMA pipe
- * (packed = with f32x2 instructions) and MUFU ex2 results per second.
- */
-int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s);
-int igs_probe_ex2_rate(int device, double* results_per_s);
-/* FMA-pipe rate reached by the kernels' instruction mix with all dependencies removed
- * (11 f32x2 FMA : 2 ex2 forward, 22 : 2 backward), at the kernels' occupancy. */
-int igs_probe_mix_rate(int device, int backward_mix, double* lane_instr_per_s);
 
 #ifdef __cplusplus
 }

@@ -43,7 +43,10 @@ def test_error_strings_and_argument_errors_without_gpu():
     # argument validation happens before any CUDA call
     assert lib.igs_profile_read(99, None, None) == -1
     assert lib.igs_forward_sr(None, None, None, None, None, None, None, None, None, 1, 1, 4, 4, 0, 1e-6, 1,
-                              None, None, None, None, 0, 0, None) == -1
+                              None, None, None, 0, None, 0, 0, None) == -1
+    one = ctypes.c_void_p(16)  # never dereferenced: the unknown hint bit is refused first
+    assert lib.igs_forward_sr(one, one, one, one, one, one, None, one, None, 1, 1, 4, 4, 3, 1e-6, 1,
+                              one, one, None, 64, one, 1 << 20, 0, None) == -1
 
 
 def test_added_entry_points_validate_arguments_without_gpu():
@@ -65,12 +68,14 @@ def test_added_entry_points_validate_arguments_without_gpu():
     assert lib.igs_mse_grad(one, one, 10, None, None, 0, None) == -1
     assert lib.igs_read_narrow_count(None, 0, None, None) == -1
     assert lib.igs_read_executed(None, 0, None, None) == -1
-    assert lib.igs_forward_feature(None, None, one, strides, one, strides, 1, 1, 4, 4, 0, 1e-6, 1, one, one, None,
+    assert lib.igs_forward_feature(None, None, one, strides, one, strides, 1, 1, 4, 4, 0, 1e-6, 1, one, one, None, 0,
                                    one, 1 << 20, 0, None) == -1
     assert lib.igs_backward_feature(None, None, one, strides, one, strides, one, one, one, 1, 1, 4, 4, 3, 1e-6, 0,
-                                    None, None, one, 1 << 20, 0, None) == -1
+                                    None, None, 0, one, 1 << 20, 0, None) == -1
     assert lib.igs_backward_feature(one, None, one, strides, one, strides, one, one, one, 1, 1, 4, 4, 3, 1e-6, 7,
-                                    one, None, one, 1 << 20, 0, None) == -1  # unknown gradient mode
+                                    one, None, 0, one, 1 << 20, 0, None) == -1  # unknown gradient mode
+    assert lib.igs_read_status_words(None, 0, None, None) == -1
+    assert lib.igs_read_status_static(0, None, None) == -1
 
 
 def test_product_package_never_imports_the_oracle():

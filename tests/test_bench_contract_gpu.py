@@ -26,6 +26,7 @@ def test_b200_arm_line():
               "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks", "roofline"):
         assert k in d, k
     assert d["n_gpus"] == 1 and d["steps"] == 3 and d["warmup"] == 3 and d["higher_is_better"] is True
+    assert d["scaling"] == "strong" and d["config"]["global_batch"] == 4
     assert d["value"] > 0 and d["ms_per_step"] > 0 and d["gpu_launches"] > 0 and d["dtype"] == "f32"
     assert "workload" in d["config"]
     e = d["e2e"]
@@ -40,5 +41,6 @@ def test_b200_arm_line():
 def test_reference_arm_line():
     d = _run("--impl", "reference", "--workload", "cfg2_small", "--steps", "1", "--warmup", "0")
     assert d["impl"] == "reference" and d["value"] > 0
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["cpu_sample_N"] >= 32 and d["scaling"] == "strong"
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0

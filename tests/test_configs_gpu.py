@@ -90,6 +90,19 @@ def test_cfg3_single_image_fit_shape(dev):
     subset_check(d, out, gout, grads, seed=3)
 
 
+def _sinusoid_target(x, y, seed=33):
+    """The fit protocol's target: per channel a sum of 64 random sinusoids over the sample
+    grid (x, y: [H,W] CPU tensors), min-max normalised; [1,3,H,W]."""
+    gen = torch.Generator().manual_seed(seed)
+    a = torch.rand(3, 64, generator=gen)
+    f = torch.rand(3, 64, 2, generator=gen) * 16 - 8
+    ph = torch.rand(3, 64, generator=gen) * 2 * math.pi
+    tgt = (a[:, :, None, None] * torch.sin(math.pi * (f[:, :, 0, None, None] * x + f[:, :, 1, None, None] * y)
+                                           + ph[:, :, None, None])).sum(1)
+    tgt = (tgt - tgt.amin((1, 2), keepdim=True)) / (tgt.amax((1, 2), keepdim=True) - tgt.amin((1, 2), keepdim=True))
+    return tgt[None].contiguous()
+
+
 def test_cfg3_adam_steps_reduce_the_loss(dev):
     """The fit protocol: Adam (lr 1e-2) on the five parameter tensors against a smooth
     target (sum of 64 random sinusoids per channel, min-max normalised); the loss must go
@@ -99,15 +112,7 @@ def test_cfg3_adam_steps_reduce_the_loss(dev):
 
     cfg = workloads.CONFIGS["cfg3"]
     d = workloads.draw(cfg, device=dev, with_target=False)
-    gen = torch.Generator().manual_seed(33)
-    a = torch.rand(3, 64, generator=gen)
-    f = torch.rand(3, 64, 2, generator=gen) * 16 - 8
-    ph = torch.rand(3, 64, generator=gen) * 2 * math.pi
-    x, y = d["x"][0, 0].cpu(), d["y"][0, 0].cpu()
-    tgt = (a[:, :, None, None] * torch.sin(math.pi * (f[:, :, 0, None, None] * x + f[:, :, 1, None, None] * y)
-                                           + ph[:, :, None, None])).sum(1)
-    tgt = (tgt - tgt.amin((1, 2), keepdim=True)) / (tgt.amax((1, 2), keepdim=True) - tgt.amin((1, 2), keepdim=True))
-    tgt = tgt[None].to(dev)
+    tgt = _sinusoid_target(d["x"][0, 0].cpu(), d["y"][0, 0].cpu()).to(dev)
     names = ("positions", "colors", "scales", "rotations", "alphas")
     params = [d[k].clone().requires_grad_() for k in names]
     opt = torch.optim.Adam(params, lr=1e-2)
@@ -122,6 +127,155 @@ def test_cfg3_adam_steps_reduce_the_loss(dev):
     assert all(math.isfinite(v) for v in losses)
     assert losses[-1] < 0.5 * losses[0], (losses[0], losses[-1])
     assert all(bool(torch.isfinite(p).all()) for p in params)
+
+
+NAMES = ("positions", "colors", "scales", "rotations", "alphas")
+
+
+def _oracle_loss_and_grads(P, x, y, tgt):
+    """MSE loss and its gradients from the fp64 oracle alone; P: dict of numpy parameters."""
+    from oracle import splat_oracle as so
+
+    out, _, grads = so.render_with_grads(P["positions"], P["colors"], P["scales"], P["rotations"], P["alphas"], x, y,
+                                         lambda o: 2 * (o - tgt) / o.size, 1e-6, dtype=np.float64)
+    return float(((out - tgt) ** 2).mean()), out, grads
+
+
+class _NumpyAdam:
+    """torch.optim.Adam's update (no weight decay, no amsgrad) in float64 on float32 parameters."""
+
+    def __init__(self, params, lr=1e-2, b1=0.9, b2=0.999, eps=1e-8):
+        self.lr, self.b1, self.b2, self.eps, self.t = lr, b1, b2, eps, 0
+        self.m = {k: np.zeros(v.shape) for k, v in params.items()}
+        self.v = {k: np.zeros(v.shape) for k, v in params.items()}
+
+    def step(self, params, grads):
+        self.t += 1
+        for k in params:
+            g = np.asarray(grads[k], np.float64)
+            self.m[k] = self.b1 * self.m[k] + (1 - self.b1) * g
+            self.v[k] = self.b2 * self.v[k] + (1 - self.b2) * g * g
+            denom = np.sqrt(self.v[k]) / math.sqrt(1 - self.b2 ** self.t) + self.eps
+            params[k] = (params[k].astype(np.float64) - self.lr / (1 - self.b1 ** self.t) * self.m[k] / denom
+                         ).astype(np.float32)
+
+
+def _assert_grads(got, want, what):
+    from tests._util import assert_close
+
+    ref_scale = max(float(np.abs(w).max()) for w in want.values())
+    for k, w in want.items():
+        if float(np.abs(w).max()) < 1e-9 * ref_scale:  # a gradient that is zero but for rounding
+            assert float(np.abs(got[k]).max()) <= 1e-6 * ref_scale, f"{what} d_{k}"
+        else:
+            assert_close(got[k], w, TOL, f"{what} d_{k}")
+
+
+def test_fit_protocol_first_adam_steps_against_an_oracle_driven_adam(dev):
+    """The single-image fit protocol at a reduced size (N=1024, 64x64; same distributions,
+    target and optimiser as the full one): three Adam steps of gaussian_splatting_2d on the
+    device against Adam driven by the CPU oracle alone.  At every step the loss and all five
+    gradients are compared at the device's current parameters, and the independent oracle
+    trajectory's losses and parameters must stay with the device's."""
+    from igs_b200 import workloads
+    from igs_b200.gs2d import gaussian_splatting_2d
+
+    cfg = workloads.SplatConfig("cfg3_small", 1, 1024, 64, 64, 3, 0.05, 0.30, seed=3)
+    d = workloads.draw(cfg, device="cpu", with_target=False)
+    tgt = _sinusoid_target(d["x"][0, 0], d["y"][0, 0])
+    x, y, tgt_np = _np(d["x"])[:, 0], _np(d["y"])[:, 0], _np(tgt)
+    params = [d[k].to(dev).clone().requires_grad_() for k in NAMES]
+    opt = torch.optim.Adam(params, lr=1e-2)
+    oracle_params = {k: _np(d[k]).copy() for k in NAMES}
+    oracle_adam = _NumpyAdam(oracle_params)
+    xd, yd, tgt_d = d["x"].to(dev), d["y"].to(dev), tgt.to(dev)
+    for step in range(3):
+        opt.zero_grad(set_to_none=True)
+        out = gaussian_splatting_2d(*params, xd, yd)
+        loss = torch.nn.functional.mse_loss(out, tgt_d)
+        loss.backward()
+        here = {k: _np(p) for k, p in zip(NAMES, params)}
+        o_loss, o_out, o_grads = _oracle_loss_and_grads(here, x, y, tgt_np)
+        assert abs(float(loss) - o_loss) <= 1e-5 * o_loss, (step, float(loss), o_loss)
+        _assert_grads({k: _np(p.grad) for k, p in zip(NAMES, params)}, o_grads, f"step {step}")
+        # the oracle's own trajectory: its gradients at ITS parameters, its Adam
+        t_loss, _, t_grads = _oracle_loss_and_grads(oracle_params, x, y, tgt_np)
+        assert abs(float(loss) - t_loss) <= 1e-4 * t_loss, (step, float(loss), t_loss)
+        oracle_adam.step(oracle_params, t_grads)
+        opt.step()
+    for k, p in zip(NAMES, params):
+        diff = np.abs(_np(p) - oracle_params[k])
+        # Adam divides by |g|: the few parameters whose gradient is ~1e-8 may step differently
+        assert float(np.percentile(diff, 99)) <= 1e-5, (k, float(np.percentile(diff, 99)), float(diff.max()))
+
+
+def test_image_fitter_steps_against_an_oracle_driven_adam(dev):
+    """igs_b200.fit: three steps of ImageFitter + Adam (the loop fit() runs, eager) against
+    the oracle-driven Adam in the fitter's own parametrisation (scales = exp(log_scale) + eps,
+    opacities one): per-step loss and the gradients of position, log-scale, rotation, colour."""
+    from igs_b200 import fit
+
+    N, H, W = 1024, 64, 64
+    gen = torch.Generator().manual_seed(5)
+    model = fit.ImageFitter(N, 3, init_log_scale=-3.0)
+    with torch.no_grad():  # generic starting values: no two gaussians alike, none isotropic
+        model.position.add_(torch.randn(1, N, 2, generator=gen) * 0.02)
+        model.log_scale.add_(torch.rand(1, N, 2, generator=gen) * 0.7)
+        model.rotation.copy_(torch.rand(1, N, generator=gen) * 2 * math.pi)
+        model.color.copy_(torch.rand(1, N, 3, generator=gen))
+    start = {k: v.detach().clone().numpy() for k, v in model.named_parameters()}
+    model.to(dev)
+    xg, yg = model.grids((H, W))
+    x, y = _np(xg.expand(1, 1, H, W))[:, 0], _np(yg.expand(1, 1, H, W))[:, 0]
+    tgt = _sinusoid_target(torch.from_numpy(x[0]), torch.from_numpy(y[0]))
+    tgt_np, tgt_d = _np(tgt), tgt.to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    oracle_params = {k: v.copy() for k, v in start.items()}
+    oracle_adam = _NumpyAdam(oracle_params)
+    alphas = np.ones((1, N), np.float32)
+
+    def oracle_at(p):
+        scales = np.exp(p["log_scale"].astype(np.float64)) + fit.EPS
+        P = {"positions": p["position"], "colors": p["color"], "scales": scales, "rotations": p["rotation"],
+             "alphas": alphas}
+        loss, _, g = _oracle_loss_and_grads(P, x, y, tgt_np)
+        return loss, {"position": g["positions"], "color": g["colors"], "rotation": g["rotations"],
+                      "log_scale": g["scales"] * np.exp(p["log_scale"].astype(np.float64))}
+
+    for step in range(3):
+        here = {k: _np(v) for k, v in model.named_parameters()}
+        loss = fit._eager_step(model, opt, tgt_d)  # zero_grad, render, MSE, backward, Adam step
+        o_loss, o_grads = oracle_at(here)
+        assert abs(float(loss) - o_loss) <= 1e-5 * o_loss, (step, float(loss), o_loss)
+        _assert_grads({k: _np(v.grad) for k, v in model.named_parameters()}, o_grads, f"step {step}")
+        t_loss, t_grads = oracle_at(oracle_params)
+        assert abs(float(loss) - t_loss) <= 1e-4 * t_loss, (step, float(loss), t_loss)
+        oracle_adam.step(oracle_params, t_grads)
+    for k, v in model.named_parameters():
+        diff = np.abs(_np(v) - oracle_params[k])
+        assert float(np.percentile(diff, 99)) <= 1e-5, (k, float(np.percentile(diff, 99)), float(diff.max()))
+
+
+def test_cfg3_one_full_size_step_against_the_oracle_alone(dev):
+    """One step of the single-image fit at its full size (B=1, N=16384, 512x512): loss, image
+    and every gradient of every gaussian against the fp64 oracle's own forward and backward
+    (nothing taken from the device)."""
+    from igs_b200 import workloads
+    from igs_b200.gs2d import gaussian_splatting_2d
+    from tests._util import assert_close
+
+    cfg = workloads.CONFIGS["cfg3"]
+    d = workloads.draw(cfg, device="cpu", with_target=False)
+    tgt = _sinusoid_target(d["x"][0, 0], d["y"][0, 0])
+    params = [d[k].to(dev).clone().requires_grad_() for k in NAMES]
+    out = gaussian_splatting_2d(*params, d["x"].to(dev), d["y"].to(dev))
+    loss = torch.nn.functional.mse_loss(out, tgt.to(dev))
+    loss.backward()
+    o_loss, o_out, o_grads = _oracle_loss_and_grads({k: _np(d[k]) for k in NAMES}, _np(d["x"])[:, 0],
+                                                    _np(d["y"])[:, 0], _np(tgt))
+    assert abs(float(loss) - o_loss) <= 1e-5 * o_loss
+    assert_close(_np(out), o_out, 1e-5, "image")
+    _assert_grads({k: _np(p.grad) for k, p in zip(NAMES, params)}, o_grads, "cfg3")
 
 
 def test_cfg4_feature_map_regime_one_batch_element(dev):

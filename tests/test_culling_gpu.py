@@ -218,6 +218,19 @@ def test_processing_order_on_general_grid_and_wide_channels():
         assert torch.equal(got[k], want[k]), k
 
 
+def _grads_via_api(d, gout, x, y):
+    """Gradients through the public function (the autograd Functions are where the policy
+    lives); synchronises, so a status read queued by the call has landed afterwards."""
+    from igs_b200.gs2d import gaussian_splatting_2d
+
+    leaves = {k: v.clone().requires_grad_() for k, v in d.items()}
+    out = gaussian_splatting_2d(leaves["positions"], leaves["colors"], leaves["scales"], leaves["rotations"],
+                                leaves["alphas"], x, y)
+    out.backward(gout)
+    torch.cuda.synchronize()
+    return {k: v.grad for k, v in leaves.items()}
+
+
 def test_auto_policy_learns_that_gaussians_are_narrow(monkeypatch):
     """'auto' starts unsorted, reads the device's narrow count without blocking, and sorts
     from a later call on; from then on the gradients are the same bits call after call, and
@@ -229,29 +242,65 @@ def test_auto_policy_learns_that_gaussians_are_narrow(monkeypatch):
     d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.02, seed=31, dev=dev)
     monkeypatch.setattr(_lib, "AUTO_ORDER_MIN_EVALS", 0)  # small case: lift the size threshold of "auto"
     _lib.set_backward_sort("auto")  # forgets what earlier tests taught it
-    first = _backward_with(d, gout, x, y, None)
-    probe = _lib._probes[(dev.index, B, N, H, W)]
-    assert probe.calls == 1 and not probe.narrow
+    first = _grads_via_api(d, gout, x, y)
+    memo = _lib._shape_memos[(dev.index, B, N, H, W)]
+    assert memo.calls == 2 and memo.narrow is None  # forward + backward; no answer has been looked at yet
     for _ in range(3):
-        again = _backward_with(d, gout, x, y, None)  # each call synchronises, so the copy has landed
-    assert probe.narrow
-    once_more = _backward_with(d, gout, x, y, None)
+        again = _grads_via_api(d, gout, x, y)
+    assert memo.narrow is True
+    once_more = _grads_via_api(d, gout, x, y)
     for k in first:
         assert torch.equal(once_more[k], again[k]), k
         assert _rel(again[k], first[k]) < 2e-6, k
-    # wide gaussians never switch it on
+    # wide gaussians never switch it on, and are remembered as wide (later calls pass the hint)
     d2, gout2, x2, y2 = _case(B, N, 100, W, 3, 0.3, 0.6, seed=32, dev=dev)
-    for _ in range(4):
-        _backward_with(d2, gout2, x2, y2, None)
-    assert not _lib._probes[(dev.index, B, N, 100, W)].narrow
+    wide_first = _grads_via_api(d2, gout2, x2, y2)
+    for _ in range(3):
+        wide_again = _grads_via_api(d2, gout2, x2, y2)
+    assert _lib._shape_memos[(dev.index, B, N, 100, W)].narrow is False
+    for k in wide_first:  # with and without the hint: the same kernels do the work, the same bits
+        assert torch.equal(wide_again[k], wide_first[k]), k
     # below the size threshold "auto" still learns, but orders only inside a graph capture
     monkeypatch.setattr(_lib, "AUTO_ORDER_MIN_EVALS", 5e8)
     _lib.set_backward_sort("auto")
     for _ in range(4):
-        _backward_with(d, gout, x, y, None)
-    assert _lib._probes[(dev.index, B, N, H, W)].narrow
-    order, _ = _lib.order_by_policy(d["positions"], None, None, x[:, 0], y[:, 0])
-    assert order is None
+        _grads_via_api(d, gout, x, y)
+    memo = _lib._shape_memos[(dev.index, B, N, H, W)]
+    assert memo.narrow is True
+    assert _lib.order_by_policy(memo, d["positions"], None, None, x[:, 0], y[:, 0]) is None
+
+
+def test_materialised_grid_is_remembered_as_separable():
+    """A materialised xy_grid is checked on the device by the first call; later calls with the
+    very same (unmodified) tensors pass stride-0 views and skip the check -- same bits.  An
+    in-place change of the grid tensor makes the next call look again."""
+    from igs_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 2, 600, 40, 48
+    d, gout, x, y = _case(B, N, H, W, 3, 0.1, 0.4, seed=33, dev=dev)
+    _lib.forget_what_calls_learnt()
+    first = _grads_via_api(d, gout, x, y)
+    entry = _lib._grid_memos[(id(x), id(y))]
+    n0 = _lib.launch_count()
+    second = _grads_via_api(d, gout, x, y)   # the answer of the first call's check is picked up here
+    n1 = _lib.launch_count()
+    assert entry.kind == "separable"
+    third = _grads_via_api(d, gout, x, y)
+    assert _lib.launch_count() - n1 <= n1 - n0
+    for k in first:
+        assert torch.equal(second[k], first[k]) and torch.equal(third[k], first[k]), k
+    # a warped grid in the same storage: the version counter moved, so the entry no longer applies
+    x.add_(0.01 * torch.sin(7 * y))
+    _lib.set_backward_sort("off")
+    try:
+        warped = _grads_via_api(d, gout, x, y)  # checked on the device again: not separable
+        hinted = _grads_via_api(d, gout, x, y)  # picks the answer up: IGS_HINT_GENERAL_GRID
+        assert _lib._grid_memos[(id(x), id(y))].kind == "general"
+    finally:
+        _lib.set_backward_sort("auto")
+    for k in warped:
+        assert torch.equal(hinted[k], warped[k]), k
 
 
 @pytest.mark.parametrize("C", [1, 3, 4])

@@ -359,6 +359,29 @@ def test_headline_gradients_on_gaussian_subset(headline):
         assert err <= TOL, f"d_{k}: {err:.3e}"
 
 
+def test_headline_one_whole_batch_element_from_the_oracle_alone(headline):
+    """One of the 16 batch elements in full, with nothing borrowed from the device: the fp64
+    oracle renders all 8192 gaussians over the whole 256x256 image itself, forms the upstream
+    gradient from ITS image, and runs its own backward.  Image, weight sum and all five
+    gradients of every gaussian must agree."""
+    from igs_b200 import _lib
+    from oracle import splat_oracle as so
+
+    cfg, d, out, gout, grads = headline
+    b = 5
+    P = {k: _np(d[k])[b:b + 1] for k in ("positions", "colors", "scales", "rotations", "alphas")}
+    x, y, target = _np(d["x"])[b:b + 1, 0], _np(d["y"])[b:b + 1, 0], _np(d["target"])[b:b + 1]
+    o_out, o_wsum, o_grads = so.render_with_grads(P["positions"], P["colors"], P["scales"], P["rotations"], P["alphas"],
+                                                  x, y, lambda o: 2 * (o - target), 1e-6, dtype=np.float64)
+    assert_close(_np(out)[b:b + 1], o_out, 1e-5, "image of the batch element")
+    _, wsum = _lib.forward("sr", d["positions"][b:b + 1].contiguous(), d["scales"][b:b + 1].contiguous(),
+                           d["rotations"][b:b + 1].contiguous(), None, d["alphas"][b:b + 1].contiguous(),
+                           d["colors"][b:b + 1].contiguous(), d["x"][b:b + 1, 0], d["y"][b:b + 1, 0], 1e-6)
+    assert_close(_np(wsum), o_wsum, 1e-5, "weight sum of the batch element")
+    for k, w in o_grads.items():
+        assert_close(_np(grads[k])[b:b + 1], w, TOL, f"d_{k} of the whole batch element")
+
+
 def test_headline_identities(headline, dev):
     """Size-independent properties at full size:
     (a) sum_{n,c} colour * d_colour = sum_{pixels,c} gout * out  (both equal sum gn*R);
