@@ -214,13 +214,14 @@ class _ShapeMemo:
 
 
 class _GridMemo:
-    __slots__ = ("xref", "yref", "xv", "yv", "kind", "pending")
+    __slots__ = ("xref", "yref", "xv", "yv", "kind", "pending", "views")
 
     def __init__(self, x, y):
         self.xref, self.yref = weakref.ref(x), weakref.ref(y)
         self.xv, self.yv = x._version, y._version
         self.kind = None  # None = not known yet; "separable", "general", "unchecked"
         self.pending = False
+        self.views = None  # (B, x3, y3) handed out last time, for the kind that is known
 
     def matches(self, x, y):
         return self.xref() is x and self.yref() is y and self.xv == x._version and self.yv == y._version
@@ -312,25 +313,27 @@ def grid_for_call(x, y, B):
     if x.shape[0] not in (B, 1):
         raise ValueError(f"x/y batch {x.shape[0]} does not match the gaussians' batch {B}")
     H, W = x.shape[2], x.shape[3]
+    key = (id(x), id(y))
+    entry = _grid_memos.get(key)
+    if entry is not None and entry.matches(x, y) and entry.kind in ("separable", "general"):
+        v = entry.views
+        if v is None or v[0] != B:
+            v = entry.views = (B, *grid_views(x, y, B, entry.kind == "separable"))
+        return v[1], v[2], (HINT_GENERAL_GRID if entry.kind == "general" else 0), None
     x3, y3 = x[:, 0].expand(B, H, W), y[:, 0].expand(B, H, W)
     if H < 4 or W < 16 or ((x3.stride(1) == 0 or H == 1) and (y3.stride(2) == 0 or W == 1)):
         return x3, y3, 0, None  # tiny, or separable by construction: the library needs no help
-    key = (id(x), id(y))
-    entry = _grid_memos.get(key)
     if entry is None or not entry.matches(x, y):
         if torch.cuda.is_current_stream_capturing():
             return x3, y3, 0, None
         with _memo_lock:
-            if len(_grid_memos) > 64:  # forget grids that are gone (or everything, if none is)
-                dead = [k for k, e in _grid_memos.items() if e.xref() is None or e.yref() is None]
-                for k in dead or list(_grid_memos):
-                    del _grid_memos[k]
+            # forget grids that are gone (their entries hold views, i.e. device memory)
+            for k in [k for k, e in _grid_memos.items() if e.xref() is None or e.yref() is None]:
+                del _grid_memos[k]
+            if len(_grid_memos) > 64:
+                _grid_memos.clear()
             entry = _grid_memos[key] = _GridMemo(x, y)
         return x3, y3, 0, entry
-    if entry.kind == "separable":
-        return x3[:, :1].expand(B, H, W), y3[:, :, :1].expand(B, H, W), 0, None
-    if entry.kind == "general":
-        return x3, y3, HINT_GENERAL_GRID, None
     return x3, y3, 0, (entry if entry.kind is None else None)
 
 
@@ -344,9 +347,9 @@ def grid_views(x, y, B, as_separable=False):
 
 
 class CallInfo:
-    """What one forward decided, kept for its backward: the grid views (as_separable says
-    which kind), the hints, the processing order, and the memos that learn from the call."""
-    __slots__ = ("x3", "y3", "as_separable", "hints", "order", "shape", "grid")
+    """What one forward decided, kept for its backward: the grid views, the hints, the
+    processing order, and the memos that learn from the call."""
+    __slots__ = ("x3", "y3", "hints", "order", "shape", "grid")
 
 
 def prepare_call(x, y, pos, feat=None, pos_off=None):
@@ -357,7 +360,6 @@ def prepare_call(x, y, pos, feat=None, pos_off=None):
     B, N = (pos if pos is not None else feat).shape[:2]
     info = CallInfo()
     info.x3, info.y3, info.hints, info.grid = grid_for_call(x, y, B)
-    info.as_separable = info.x3.stride(1) == 0 and info.y3.stride(2) == 0
     _, H, W = info.x3.shape
     info.shape = _shape_memo(x.device, B, N, H, W) if B * N * H * W > 0 else None
     info.order = None

@@ -212,10 +212,15 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     p->npairs = (HW + 1) / 2;
     p->nrp = (H + 1) / 2;
     p->ncb = (W + 3) / 4;
-    p->sep_ok = (p->ch.n == 1 && backward_has_separable(ct)) ? 1 : 0;
+    p->rows = H;
+    p->cols = W;
+    p->row_kernel = (p->ch.n == 1 && backward_has_row_kernel(ct)) ? 1 : 0;
+    p->sep_ok = (p->ch.n == 1 && (backward_has_separable(ct) || p->row_kernel)) ? 1 : 0;
     const long long per_cta = (long long)p->threads * p->gauss_per_thread;
     const long long groups = ((long long)N + per_cta - 1) / per_cta;
     const long long base = groups * (B > 0 ? B : 1);
+    // (every separable kernel gives a CTA 256 gaussians)
+    const long long base_sep = (((long long)N + 255) / 256) * (B > 0 ? B : 1);
     // The slab count is chosen for the general kernel's occupancy; when the separable kernel
     // will run (it holds fewer CTAs per SM: more registers) and would get fewer than four
     // waves, a deeper count is taken.  The workspace covers both.
@@ -223,10 +228,11 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     const int ns_gen = pick_parts(base > 0 ? base : 1, slots_gen, p->npairs, 2LL * p->chunk_pairs, 256);
     int ns_sep = ns_gen;
     if (p->sep_ok) {
-        const int per_sm = backward_sep_ctas_per_sm(ct, device);
-        if (per_sm > 0)
-            ns_sep = pick_parts(base > 0 ? base : 1, slots_gen, p->npairs, 2LL * p->chunk_pairs, 256,
-                                (long long)sm_count(device) * per_sm);
+        const int per_sm = p->row_kernel ? backward_row_ctas_per_sm(ct, device) : backward_sep_ctas_per_sm(ct, device);
+        if (per_sm > 0) {
+            const long long slots_sep = (long long)sm_count(device) * per_sm;
+            ns_sep = pick_parts(base_sep > 0 ? base_sep : 1, slots_sep, p->npairs, 2LL * p->chunk_pairs, 256, slots_sep);
+        }
     }
     const int ns = (separable_grid && p->sep_ok) ? ns_sep : ns_gen;
     const int ns_other = (separable_grid && p->sep_ok) ? ns_gen : ns_sep;  // covered by the workspace size
@@ -281,17 +287,21 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
         p->off_prec[k] = off;
         size_t rec_bytes = (size_t)B * p->npairs * bwd_rec_floats(p->ch.ct[k]) * sizeof(float);
         if (p->sep_ok) {
-            const size_t sep_bytes = (size_t)B * p->nrp * p->ncb * bwd_sep_rec_floats(p->ch.ct[k]) * sizeof(float);
+            const size_t sep_bytes =
+                p->row_kernel ? (size_t)B * HW * backward_row_record_floats(p->ch.ct[k]) * sizeof(float)
+                              : (size_t)B * p->nrp * p->ncb * bwd_sep_rec_floats(p->ch.ct[k]) * sizeof(float);
             if (sep_bytes > rec_bytes) rec_bytes = sep_bytes;
         }
         off = align_up(off + rec_bytes, 256);
     }
+    p->off_axes = off;
+    if (p->row_kernel) off = align_up(off + (size_t)B * H * sizeof(float), 256);
     p->off_part = off;
     off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
     p->part_bytes = (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float);
     p->off_tasks = off;
     p->task_capacity = 0;
-    if (p->sep_ok) {
+    if (p->sep_ok && !p->row_kernel) {  // (the task-queue kernel exists for up to 4 channels)
         const long long groups32 = ((long long)N + 31) / 32;
         const long long cap = (long long)B * groups32 * n_slab_max;
         if (cap <= 0x7fffffffLL / 2) {
@@ -609,6 +619,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     ta.npairs = p.npairs;
     ta.nrp = p.nrp;
     ta.ncb = p.ncb;
+    ta.axes = p.row_kernel ? reinterpret_cast<float*>(ws + p.off_axes) : nullptr;
     ta.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
     ta.flags = grid_flag;
     ta.B = B; ta.H = H; ta.W = W; ta.C = C;
@@ -630,6 +641,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.colors = colors;
         ba.prec = ta.prec[k];
         ba.order = order;
+        ba.axes = ta.axes;
         ba.part = reinterpret_cast<float*>(ws + p.off_part);
         ba.status = reinterpret_cast<int*>(ws);
         ba.npairs = p.npairs;
@@ -814,7 +826,8 @@ int igs_describe_kernels(int C, int* forward_separable, int* backward_separable)
     int rc = make_chunks(C, &ch);
     if (rc) return rc;
     if (forward_separable) *forward_separable = forward_has_separable(ch.ct[0]) ? 1 : 0;
-    if (backward_separable) *backward_separable = (ch.n == 1 && backward_has_separable(ch.ct[0])) ? 1 : 0;
+    if (backward_separable)
+        *backward_separable = (ch.n == 1 && (backward_has_separable(ch.ct[0]) || backward_has_row_kernel(ch.ct[0]))) ? 1 : 0;
     return IGS_OK;
 }
 

@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) pixel_terms_kernel(PixelTermArgs a) {
 }
 
 cudaError_t launch_pixel_terms(const PixelTermArgs& a, bool separable, cudaStream_t s) {
-    if (separable) return launch_pixel_terms_sep(a, s);
+    if (separable) return a.axes ? launch_pixel_terms_row(a, s) : launch_pixel_terms_sep(a, s);
     const long long n = (long long)a.B * a.npairs;
     if (n <= 0) return cudaSuccess;
     {
@@ -302,7 +302,8 @@ static cudaError_t launch_one(const BwdArgs& a, const BwdPlan& p, cudaStream_t s
 
 cudaError_t launch_backward_chunk(int ct, bool separable, bool culling, const BwdArgs& a, const BwdPlan& p,
                                   cudaStream_t s) {
-    if (separable) return launch_backward_sep_chunk(ct, culling, a, p, s);
+    if (separable)
+        return p.row_kernel ? launch_backward_row_chunk(ct, culling, a, p, s) : launch_backward_sep_chunk(ct, culling, a, p, s);
     const bool two = p.gauss_per_thread >= 2;
     switch (ct) {
         case 1: return two ? launch_one<1, BWD_GPT>(a, p, s) : launch_one<1, 1>(a, p, s);

@@ -15,6 +15,8 @@ struct PixelTermArgs {
     const float* out;   // [B, C, HW]  (exact mode only)
     const float* gout;  // [B, C, HW]
     float* prec[MAX_CHUNKS];  // [B, npairs, bwd_rec_floats(ct)]  or, separable, [B, nrp*ncb, bwd_sep_rec_floats(ct)]
+                              // or, separable with 8 / 16 channels, [B, H, W, row-record floats] (backward_row.cu)
+    float* axes;              // row layout only: receives y[b, h], [B, H]
     const int* grid_sel;      // grid word (bit 0 = not a separable grid) picking the kernel; nullptr = run
     int* flags;               // grid word: receives UPSTREAM_NOT_FINITE (separable kernel), or nullptr
     Chunks ch;
@@ -29,6 +31,7 @@ struct BwdArgs {
     const float* geo;     // [B, N, 8]
     const float* colors;  // [B, N, C]
     const float* prec;    // records of this chunk
+    const float* axes;    // row-streaming kernel (backward_row.cu): y[b, h], [B, H]
     const int* order;     // [B, N] permutation: processing slot -> gaussian index, or nullptr
     float* part;          // [n_slab, B, planes, N]
     int* status;
@@ -96,6 +99,12 @@ bool backward_has_separable(int ct);
 cudaError_t launch_pixel_terms_sep(const PixelTermArgs& a, cudaStream_t s);
 cudaError_t launch_backward_sep_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, int sm_count, cudaStream_t s);
+// separable grids, chunks of 8 and 16 channels: two gaussians per f32x2, pixels stream row by row
+bool backward_has_row_kernel(int ct);
+int backward_row_ctas_per_sm(int ct, int device);
+int backward_row_record_floats(int ct);
+cudaError_t launch_pixel_terms_row(const PixelTermArgs& a, cudaStream_t s);
+cudaError_t launch_backward_row_chunk(int ct, bool culling, const BwdArgs& a, const BwdPlan& p, cudaStream_t s);
 cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s);
 cudaError_t launch_coord_grad(const CoordGradArgs& a, cudaStream_t s);
 

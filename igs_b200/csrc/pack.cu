@@ -5,10 +5,11 @@
 // Reach.  With the exponent q = A dx^2 + B2 dx dy + Cq dy^2 in log2 units, the weight
 // ex2.approx.ftz(q) is exactly zero once q < -126 (results below 2^-126 are flushed).  For a
 // negative-definite form the set q >= -CULL_T is an ellipse whose bounding box has the
-// half-widths hx = sqrt(4 T (-Cq) / D), hy = sqrt(4 T (-A) / D), D = 4 A Cq - B2^2; a
-// pixel outside that box receives exactly nothing from the gaussian, which is what lets
-// the splat kernels skip (gaussian, pixel tile) combinations without changing a bit of
-// the result.  An indefinite form has no such box: hx = hy = +inf.
+// half-widths hx = sqrt(r2 cov_xx), hy = sqrt(r2 cov_yy) with cov the covariance (the inverse
+// of cov_inv) and r2 = CULL_T / (0.5 log2 e); a pixel outside that box receives exactly
+// nothing from the gaussian, which is what lets the splat kernels skip (gaussian, pixel
+// tile) combinations without changing a bit of the result.  An indefinite form has no such
+// box: hx = hy = +inf.
 #include "pack.cuh"
 
 namespace igs {
@@ -28,6 +29,12 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             py += L.pos_off[2 * i + 1];
         }
         float c00, c01, c11;
+        float hx = INFINITY, hy = INFINITY;
+        // Reach: the ellipse d^T cov_inv d <= r2 (r2 = CULL_T / (0.5 log2 e)) has the bounding
+        // box half-widths sqrt(r2 * cov_xx), sqrt(r2 * cov_yy).  A little wider than exact
+        // (factor 1.001 on top of the 130-against-126 margin of CULL_T), so that fp32 rounding
+        // here can never cull a non-zero weight.
+        const float r2 = CULL_T / -EXP2_SCALE;
         if (a.kind == SHAPE_SCALE_ROT) {
             float sx = a.shape0[(long long)L.s0_s * i], sy = a.shape0[(long long)L.s0_s * i + 1];
             if (L.log_scale) {
@@ -38,22 +45,28 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
             c00 = ci.c00;
             c01 = ci.c01;
             c11 = ci.c11;
+            // the covariance itself is at hand (sums of squares: nothing cancels, however
+            // anisotropic or rotated the gaussian is)
+            hx = 1.001f * sqrtf(r2 * ci.a);
+            hy = 1.001f * sqrtf(r2 * ci.d);
         } else {
             c00 = a.shape0[i];
             c01 = a.shape1[i];
             c11 = a.shape2[i];
+            // cov = inverse of the caller's matrix: its determinant cancels for strongly
+            // anisotropic rotated gaussians, so it is formed in double, and a form that is
+            // not safely positive definite gets no box at all
+            const double d00 = c00, d01 = c01, d11 = c11;
+            const double det = d00 * d11 - d01 * d01;
+            if (d00 > 0.0 && d11 > 0.0 && det > 1e-6 * d00 * d11) {
+                hx = 1.001f * (float)sqrt((double)r2 * d11 / det);
+                hy = 1.001f * (float)sqrt((double)r2 * d00 / det);
+            }
         }
+        if (!(hx == hx) || !(hy == hy)) hx = hy = INFINITY;
         const float A = EXP2_SCALE * c00, B2 = 2.0f * EXP2_SCALE * c01, Cq = EXP2_SCALE * c11;
         const float al = a.alpha ? a.alpha[i] : 1.0f;
 
-        float hx = INFINITY, hy = INFINITY;
-        const float D = 4.0f * A * Cq - B2 * B2;
-        if (A < 0.f && Cq < 0.f && D > 0.f) {
-            // a little wider than exact, so that fp32 rounding here can never cull a non-zero weight
-            hx = 1.001f * sqrtf(4.0f * CULL_T * (-Cq) / D);
-            hy = 1.001f * sqrtf(4.0f * CULL_T * (-A) / D);
-            if (!(hx == hx) || !(hy == hy)) hx = hy = INFINITY;
-        }
         // 0 * NaN is NaN: a gaussian with a non-finite parameter must reach every pixel, as in
         // the reference (its weights, or their products with alpha and the colours, are NaN)
         bool finite = isfinite(px) && isfinite(py) && isfinite(A) && isfinite(B2) && isfinite(Cq) && isfinite(al);

@@ -46,10 +46,13 @@ struct BwdPlan {
     int stages;
     int planes;            // moment planes per (slab, batch): 6 per chunk + C
     int sep_ok;            // a separable instantiation exists for this shape
+    int row_kernel;        // ... and it is the row-streaming one (8 / 16 channels, backward_row.cu)
+    int rows, cols;        // image size
     int nrp, ncb;          // separable: row pairs (2 rows) and blocks (4 columns) per row pair
     int rp_per_slab;       // separable: row pairs per slab (same n_slab as the general kernel)
     size_t off_geo;
     size_t off_prec[MAX_CHUNKS];
+    size_t off_axes;       // row-streaming kernel: y per row, [B][H]
     size_t off_part;       // [n_slab][B][planes][N]
     size_t off_tasks;      // ordered skipping path: [task_capacity] int4, then [B][ceil(N/32)] int4
     int task_capacity;     // B * ceil(N/32) * (most slabs either partition has); 0 without separable kernels

@@ -99,18 +99,16 @@ def _save_call(ctx, info, x, y, *tensors):
     processing order) so that the backward runs the same kernels on the same views."""
     ctx.save_for_backward(x, y, *tensors, info.order if info.order is not None else x.new_empty(0))
     ctx.has_order = info.order is not None
-    ctx.as_separable = info.as_separable
     ctx.hints = info.hints
-    info.x3 = info.y3 = info.order = None  # only the memos stay on the context
+    ctx.grid_views = (info.x3, info.y3)  # views of the saved x, y (whose versions autograd checks)
+    info.x3 = info.y3 = info.order = None  # only the memos stay on the info object
     ctx.call_info = info
 
 
 def _saved_call(ctx):
     """-> (the saved tensors without the order, x3, y3, order or None)."""
     *tensors, order = ctx.saved_tensors
-    x, y = tensors[0], tensors[1]
-    B = tensors[2].shape[0]
-    x3, y3 = _lib.grid_views(x, y, B, ctx.as_separable)
+    x3, y3 = ctx.grid_views
     return tensors, x3, y3, (order if ctx.has_order else None)
 
 
@@ -313,12 +311,17 @@ class GaussianSplatting2D(nn.Module):
         side spans more than [-1,1] so that x_range * y_range = 1.  Returns two [1,H,W]
         tensors that are expanded (stride-0) views of one row / one column ON the target
         device: same values as the reference's, no H*W copy, and the splat kernels can see
-        from the strides alone that the grid is separable."""
+        from the strides alone that the grid is separable.  The row and the column are kept
+        and shared by every call with the same size and device: treat the returned views as
+        read-only (clone them before an in-place change)."""
         h, w = size
         aspect = h / w
         h_range = aspect ** 0.5
         w_range = 1 / aspect ** 0.5
-        xs, ys = _grid_axes(int(h), int(w), float(w_range), float(h_range), str(torch.device(device or "cpu")))
+        dev = torch.device(device or "cpu")
+        if dev.type == "cuda" and dev.index is None:  # "cuda" means the current device, whichever that is now
+            dev = torch.device("cuda", torch.cuda.current_device())
+        xs, ys = _grid_axes(int(h), int(w), float(w_range), float(h_range), str(dev))
         return xs.view(1, 1, w).expand(1, h, w), ys.view(1, h, 1).expand(1, h, w)
 
     @staticmethod

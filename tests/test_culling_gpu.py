@@ -100,6 +100,92 @@ def test_culling_with_reversed_axes_and_wide_gaussians_mixed():
         assert torch.equal(g_on[k], g_off[k]), k
 
 
+@pytest.mark.parametrize("level", ["scales", "cov_inv"])
+def test_culling_with_strongly_anisotropic_rotated_gaussians(level):
+    """Long thin gaussians at random angles (axis ratios 1000:1 and 2000:1): the zero-weight
+    box must come out conservative although the determinant of the inverse covariance cancels
+    almost completely in fp32.  Culling on and off: the same bits, from the scale / rotation
+    entry and from the inverse-covariance entry."""
+    from igs_b200 import _lib, gs2d
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 2048, 96, 128
+    d, gout, x, y = _case(B, N, H, W, 3, 0.004, 0.03, seed=13, dev=dev)
+    d["scales"][:, ::2, 0] = 0.4
+    d["scales"][:, ::2, 1] = 0.0004
+    d["scales"][:, 1::4, 0] = 0.0002
+    d["scales"][:, 1::4, 1] = 0.4
+    if level == "scales":
+        o_on, g_on = _run(d, gout, x, y, True)
+        o_off, g_off = _run(d, gout, x, y, False)
+    else:
+        c00, c01, c11 = gs2d._cov_inv_torch(d["scales"], d["rotations"], 1e-6)
+
+        def run(culling):
+            _lib.set_culling(culling)
+            _lib.set_backward_sort("off")
+            try:
+                leaves = [t.clone().requires_grad_() for t in (d["positions"], c00, c01, c11, d["alphas"], d["colors"])]
+                out = gs2d.GaussianSplatting2DKernel.apply(x, y, *leaves)
+                out.backward(gout)
+                torch.cuda.synchronize()
+                return out.detach(), {i: t.grad for i, t in enumerate(leaves)}
+            finally:
+                _lib.set_culling(True)
+                _lib.set_backward_sort("auto")
+
+        o_on, g_on = run(True)
+        o_off, g_off = run(False)
+    assert torch.equal(o_on, o_off)
+    for k in g_on:
+        assert torch.equal(g_on[k], g_off[k]), k
+
+
+@pytest.mark.parametrize("C", [8, 16, 17])
+def test_many_channels_culling_changes_no_bit_and_matches_the_oracle(C):
+    """8 and 16 channels run the row-streaming separable backward (two gaussians per packed
+    operand) and its skipping instantiation; 17 channels are a chunk of 16 plus one and take
+    the general kernels.  Odd image sizes, a ragged gaussian count, a few image-wide gaussians
+    among the narrow ones.  Culling on / off: the same bits; and the culled result against the
+    fp64 oracle."""
+    from oracle import splat_oracle as so
+
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 2, 1501, 71, 150
+    d, gout, x, y = _case(B, N, H, W, C, 0.004, 0.03, seed=50 + C, dev=dev)
+    d["scales"][:, ::131] = 0.7
+    assert _narrow_count(d, x, y) * 8 >= B * N
+    o_on, g_on = _run(d, gout, x, y, True)
+    o_off, g_off = _run(d, gout, x, y, False)
+    assert torch.equal(o_on, o_off)
+    for k in g_on:
+        assert torch.equal(g_on[k], g_off[k]), k
+    P = {k: v.cpu().numpy() for k, v in d.items()}
+    o_out, _, o_grads = so.render_with_grads(P["positions"], P["colors"], P["scales"], P["rotations"], P["alphas"],
+                                             x[:, 0].cpu().numpy(), y[:, 0].cpu().numpy(), lambda o: gout.cpu().numpy(),
+                                             1e-6, dtype=np.float64)
+    assert_close(o_on.cpu().numpy(), o_out, 1e-4, "image")
+    for k, v in g_on.items():
+        assert_close(v.cpu().numpy(), o_grads[k], 1e-4, f"d_{k}")
+
+
+@pytest.mark.parametrize("C", [8, 16])
+def test_many_channels_gradients_do_not_depend_on_the_processing_order(C):
+    """The row-streaming backward with an explicit order (wide and narrow gaussians): every
+    gaussian's sums run over the same pixels in the same sequence whichever thread owns it."""
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 1, 900, 64, 96
+    gen = torch.Generator().manual_seed(8)
+    for lo, hi in ((0.004, 0.03), (0.2, 0.5)):
+        d, gout, x, y = _case(B, N, H, W, C, lo, hi, seed=60 + C, dev=dev)
+        orders = [torch.randperm(N, generator=gen).to(torch.int32).to(dev)[None].contiguous() for _ in range(2)]
+        orders.append(torch.arange(N - 1, -1, -1, dtype=torch.int32, device=dev)[None].contiguous())
+        res = [_backward_with(d, gout, x, y, o) for o in orders]
+        for r in res[1:]:
+            for k in res[0]:
+                assert torch.equal(r[k], res[0][k]), (k, lo)
+
+
 def _backward_with(d, gout, x, y, order):
     """Gradients through the library call itself, with an explicit processing order."""
     from igs_b200 import _lib
