@@ -58,6 +58,9 @@ SIGNATURES = {
     "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
     "igs_read_narrow_count": (_i, [_vp, _i, _vp, _vp]),
     "igs_read_executed": (_i, [_vp, _i, _vp, ctypes.POINTER(ctypes.c_ulonglong)]),
+    "igs_render_mse_workspace_bytes": (_i, [_i] * 6 + [ctypes.POINTER(_sz)]),
+    "igs_render_mse_sr": (_i, [_vp] * 5 + [_i, _vp, _I64, _vp, _I64, _vp] + [_i] * 5 + [_f, _i] + [_vp] * 9
+                          + [_i, _vp, _sz, _i, _vp]),
     "igs_mse_loss": (_i, [_vp, _vp, ctypes.c_longlong, _vp, _vp, _sz, _i, _vp]),
     "igs_mse_grad": (_i, [_vp, _vp, ctypes.c_longlong, _vp, _vp, _i, _vp]),
     "igs_profile_enable": (_i, [_i]),
@@ -352,10 +355,11 @@ class CallInfo:
     __slots__ = ("x3", "y3", "hints", "order", "shape", "grid")
 
 
-def prepare_call(x, y, pos, feat=None, pos_off=None):
+def prepare_call(x, y, pos, feat=None, pos_off=None, scales=None, log_scales=False):
     """Everything a forward (and the backward after it) needs beyond the tensors: grid views,
     hints from what earlier calls learnt, and the processing order the set_backward_sort
-    policy wants, if any.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off)."""
+    policy wants, if any.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off); scales
+    [B,N,2] when the caller has them."""
     _drain_reads()
     B, N = (pos if pos is not None else feat).shape[:2]
     info = CallInfo()
@@ -366,7 +370,7 @@ def prepare_call(x, y, pos, feat=None, pos_off=None):
     if info.shape is not None:
         if info.shape.narrow is False and _BACKWARD_SORT != "on":
             info.hints |= HINT_WIDE_GAUSSIANS
-        info.order = order_by_policy(info.shape, pos, feat, pos_off, info.x3, info.y3)
+        info.order = order_by_policy(info.shape, pos, feat, pos_off, info.x3, info.y3, scales, log_scales)
     return info
 
 
@@ -488,10 +492,32 @@ def set_backward_sort(mode: str) -> None:
     forget_what_calls_learnt()
 
 
-def order_by_policy(shape, pos, feat, pos_off, x3, y3):
+# A gaussian's zero-weight box reaches at most this many of its larger scale to either side
+# of its centre (sqrt(130 / (0.5 log2 e)), see pack.cu).
+REACH_IN_SCALES = 13.43
+
+
+def _positions_for_ordering(pos, scales, x3, y3):
+    """Positions to sort by: the gaussians' own, except that every WIDE gaussian (box at least
+    three quarters of the sampled extent) is moved to one corner.  The stable sort then puts
+    all wide gaussians next to each other at one end of the order and the narrow ones in
+    spatial order behind them, so that a warp of the backward (a stage of the forward) holds
+    either gaussians that reach everything or neighbours that reach one small patch; a single
+    wide gaussian among narrow ones would make its whole warp visit every pixel.  Any
+    permutation gives the same gradients; this one lets the kernels skip the most."""
+    ex = (x3[:, 0, -1] - x3[:, 0, 0]).abs()
+    ey = (y3[:, -1, 0] - y3[:, 0, 0]).abs()
+    limit = 0.75 * torch.minimum(ex, ey) / (2 * REACH_IN_SCALES)   # [B]
+    wide = scales.abs().amax(-1) >= limit[:, None]                 # [B,N]
+    corner = torch.stack((x3[:, 0, 0], y3[:, 0, 0]), -1)           # [B,2]
+    return torch.where(wide[..., None], corner[:, None, :], pos)
+
+
+def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=False):
     """The processing order one forward + backward should use under the set_backward_sort
     policy, or None.  shape: the call's _ShapeMemo; pos [B,N,2], or None with feat
-    [B,N,6+C] (+ pos_off) to take the positions from."""
+    [B,N,6+C] (+ pos_off) to take the positions from; scales [B,N,2] if at hand (lets the
+    order keep wide and narrow gaussians apart)."""
     B, N = (pos if pos is not None else feat).shape[:2]
     _, H, W = x3.shape
     if B * N == 0 or _BACKWARD_SORT == "off":
@@ -505,6 +531,10 @@ def order_by_policy(shape, pos, feat, pos_off, x3, y3):
             return None
     if pos is None:
         pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off
+        scales = torch.exp(feat[..., 2:4])
+    if scales is not None:
+        scales = scales.detach()
+        pos = _positions_for_ordering(pos.detach(), torch.exp(scales) if log_scales else scales, x3, y3)
     return spatial_order(pos.contiguous(), x3, y3)
 
 
@@ -548,6 +578,42 @@ def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps
     if keep_workspace:
         res["_workspace"] = ws
     return res
+
+
+@functools.lru_cache(maxsize=256)
+def _render_mse_workspace_bytes(B, N, H, W, C, index):
+    n = _sz(0)
+    check("igs_render_mse_workspace_bytes", load().igs_render_mse_workspace_bytes(B, N, H, W, C, index, ctypes.byref(n)))
+    return int(n.value)
+
+
+def render_mse(pos, scales, rot, alphas, colors, x3, y3, target, eps, grad_mode, log_scales=False, upstream=None,
+               want_image=False, order=None, hints=0, info=None):
+    """Render + mean-squared-error loss + all gradients in one library call
+    (igs_render_mse_sr).  Returns (loss, gradients, image or None); gradients keyed
+    positions, scales (of the log-scales when log_scales), rotations, colors and, when alphas
+    is given, alphas.  alphas None = all ones."""
+    dev = pos.device
+    B, N, C = colors.shape
+    _, H, W = x3.shape
+    ws = _workspace(_render_mse_workspace_bytes(B, N, H, W, C, dev.index), dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    loss = torch.empty((), **f32)
+    image = torch.empty(B, C, H, W, **f32) if want_image else None
+    g = {"positions": torch.empty(B, N, 2, **f32), "scales": torch.empty(B, N, 2, **f32),
+         "rotations": torch.empty(B, N, **f32), "colors": torch.empty(B, N, C, **f32)}
+    if alphas is not None:
+        g["alphas"] = torch.empty(B, N, **f32)
+    check("igs_render_mse_sr",
+          load().igs_render_mse_sr(_ptr(pos), _ptr(scales), _ptr(rot), _ptr(alphas), _ptr(colors), int(bool(log_scales)),
+                                   _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), _ptr(target), B, N, H, W, C,
+                                   float(eps), int(grad_mode), _ptr(upstream), _ptr(loss), _ptr(image),
+                                   _ptr(g["positions"]), _ptr(g["scales"]), _ptr(g["rotations"]), _ptr(g.get("alphas")),
+                                   _ptr(g["colors"]), _ptr(order), int(hints), _ptr(ws), ws.numel(), dev.index,
+                                   _stream(dev)))
+    if info is not None:
+        _queue_read(ws, info.shape, info.grid)
+    return loss, g, image
 
 
 MSE_WORKSPACE_BYTES = 4096

@@ -8,6 +8,7 @@
 #include "backward.cuh"
 #include "forward.cuh"
 #include "grid.cuh"
+#include "loss.cuh"
 #include "pack.cuh"
 #include "plan.cuh"
 
@@ -374,11 +375,23 @@ static ParamLayout layout_or_default(const ParamLayout* layout, int kind, int C)
     return l;
 }
 
+// One-split override for ordered calls.  A caller that passes an order expects narrow
+// gaussians: a CTA then streams a few stages only, and splitting the gaussians over several
+// CTAs per tile would just add partial sums to write and add up.  (A function of the shape and
+// of whether an order was passed, like every other choice that affects the bits of the result.)
+static void single_split_for_ordered_calls(FwdPlan* p, int B, int N, const int* order, bool culling_on, int device) {
+    if (order && culling_on && p->tiles_sep > 0 && (long long)p->tiles_sep * B >= sm_count(device) &&
+        (N + p->chunk_g - 1) / p->chunk_g <= 8192 /* what a CTA can list */) {
+        p->n_split = 1;
+        p->per_split = (N + p->chunk_g - 1) / p->chunk_g * p->chunk_g;
+    }
+}
+
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
                  size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan, const ParamLayout* layout,
-                 const int* order, int hints) {
+                 const int* order, int hints, const FwdExtras* extras) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (hints & ~(IGS_HINT_WIDE_GAUSSIANS | IGS_HINT_GENERAL_GRID)) return IGS_ERR_ARG;
     if (!out || (normalize && !wsum)) return IGS_ERR_ARG;
@@ -415,15 +428,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     }
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     const bool culling_on = g_culling.load(std::memory_order_relaxed) && !(hints & IGS_HINT_WIDE_GAUSSIANS);
-    if (order && culling_on && !use_plan && p.tiles_sep > 0 && (long long)p.tiles_sep * B >= sm_count(device) &&
-        (N + p.chunk_g - 1) / p.chunk_g <= 8192 /* what a CTA can list */) {
-        // A caller that passes an order expects narrow gaussians: a CTA then streams a few
-        // stages only, and splitting the gaussians over several CTAs per tile would just add
-        // partial sums to write and add up.  (A function of the shape and of whether an order
-        // was passed, like every other choice that affects the bits of the result.)
-        p.n_split = 1;
-        p.per_split = (N + p.chunk_g - 1) / p.chunk_g * p.chunk_g;
-    }
+    if (!use_plan) single_split_for_ordered_calls(&p, B, N, order, culling_on, device);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     cudaError_t e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
     if (e != cudaSuccess) return (int)e;
@@ -443,7 +448,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
     pa.shape2 = s2;
     pa.alpha = alpha;
     pa.colors = colors;
-    pa.geo = nullptr;
+    pa.geo = extras ? extras->geo_out : nullptr;  // (a fused forward + backward packs once for both)
     pa.lay = layout_or_default(layout, kind, C);
     pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
     for (int k = 0; k < p.ch.n; ++k) pa.frec[k] = reinterpret_cast<float*>(ws + p.off_frec[k]);
@@ -475,7 +480,9 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
         fa.out = out;
         fa.wsum = wsum;
         // single split without normalisation: the "partial" array IS the caller's sums buffer
-        fa.partial = (!normalize && p.n_split == 1) ? out : reinterpret_cast<float*>(ws + p.off_partial);
+        // (unless the caller wants the per-split sums left where they are)
+        const bool leave = extras && extras->leave_partials;
+        fa.partial = (!normalize && p.n_split == 1 && !leave) ? out : reinterpret_cast<float*>(ws + p.off_partial);
         fa.status = reinterpret_cast<int*>(ws);
         fa.B = B; fa.N = N; fa.H = H; fa.W = W; fa.C = C;
         fa.c0 = p.ch.c0[k];
@@ -509,6 +516,7 @@ int forward_impl(int kind, const float* pos, const float* s0, const float* s1, c
             if (e != cudaSuccess) return (int)e;
         }
     }
+    if (extras && extras->leave_partials) return IGS_OK;  // the caller adds the splits up itself
     if (p.n_split > 1) {
         ReduceArgs ra;
         ra.partial = reinterpret_cast<const float*>(ws + p.off_partial);
@@ -529,7 +537,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
                          int H, int W, int C, float eps, int mode, float* d_pos, float* d_s0, float* d_s1,
                          float* d_s2, float* d_alpha, float* d_colors, float* d_x, float* d_y, const int* order,
                          int hints, void* workspace, size_t workspace_bytes, int device, void* stream,
-                         const ParamLayout* layout = nullptr) {
+                         const ParamLayout* layout = nullptr, const BwdPrepared* prepared = nullptr) {
     if (B < 0 || N < 0 || H < 0 || W < 0 || C < 1) return IGS_ERR_ARG;
     if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
     if (hints & ~(IGS_HINT_WIDE_GAUSSIANS | IGS_HINT_GENERAL_GRID)) return IGS_ERR_ARG;
@@ -537,7 +545,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     if ((d_x == nullptr) != (d_y == nullptr)) return IGS_ERR_ARG;
     const long long HW = (long long)H * W;
     if (B == 0) return IGS_OK;
-    if (HW > 0 && (!x || !y || !wsum || !gout || (mode == IGS_GRAD_EXACT && !out))) return IGS_ERR_ARG;
+    if (HW > 0 && !prepared && (!x || !y || !wsum || !gout || (mode == IGS_GRAD_EXACT && !out))) return IGS_ERR_ARG;
     if (N > 0 && (!pos || !s0 || !s1 || !colors || !d_pos || !d_s0 || !d_s1 || !d_colors ||
                   (!layout && (!alpha || !d_alpha)) || (kind == SHAPE_COV_INV && (!s2 || !d_s2))))
         return IGS_ERR_ARG;
@@ -577,14 +585,23 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     if (rc) return rc;
     if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
-    e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
-    if (e != cudaSuccess) return (int)e;
+    // Prepared mode (the fused render + loss + gradient entry): a forward on the same data has
+    // just filled a status area (narrow count, axis flags), packed the geometry records into
+    // this workspace and written the pixel records; the grid is separable by its strides.
+    // Nothing of that is redone: straight to the splat kernels.
+    unsigned char* sa = prepared ? prepared->status : ws;  // status area
+    if (!prepared) {
+        e = cudaMemsetAsync(ws, 0, 8 * sizeof(int), st);  // status word, flags, counters
+        if (e != cudaSuccess) return (int)e;
+    }
 
     // separable grid?  (same decision procedure as the forward)
-    int* grid_flag = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
-    GridKind grid_kind;
-    e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.sep_ok != 0, hints, &grid_kind, st);
-    if (e != cudaSuccess) return (int)e;
+    int* grid_flag = reinterpret_cast<int*>(sa) + GRID_FLAG_WORD;
+    GridKind grid_kind = GRID_SEPARABLE;
+    if (!prepared) {
+        e = prepare_grid(ws, x, y, sx, sy, B, H, W, p.sep_ok != 0, hints, &grid_kind, st);
+        if (e != cudaSuccess) return (int)e;
+    }
 
     PackArgs pa;
     std::memset(&pa, 0, sizeof(pa));
@@ -596,14 +613,16 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     pa.colors = colors;
     pa.geo = reinterpret_cast<float*>(ws + p.off_geo);
     pa.lay = layout_or_default(layout, kind, C);
-    pack_grid_args(&pa, ws, x, y, sx, sy, B, N, H, W);
+    pack_grid_args(&pa, sa, x, y, sx, sy, B, N, H, W);
     pa.ch = p.ch;
     pa.M = (long long)B * N;
     pa.C = C;
     pa.eps = eps;
     pa.kind = kind;
-    e = launch_pack(pa, st);
-    if (e != cudaSuccess) return (int)e;
+    if (!prepared) {
+        e = launch_pack(pa, st);
+        if (e != cudaSuccess) return (int)e;
+    }
 
     PixelTermArgs ta;
     std::memset(&ta, 0, sizeof(ta));
@@ -625,7 +644,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     ta.B = B; ta.H = H; ta.W = W; ta.C = C;
     ta.mode = mode;
     ta.eps = eps;
-    if (grid_kind != GRID_GENERAL) {
+    if (grid_kind != GRID_GENERAL && !prepared) {
         e = launch_pixel_terms(ta, true, st);
         if (e != cudaSuccess) return (int)e;
     }
@@ -643,7 +662,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.order = order;
         ba.axes = ta.axes;
         ba.part = reinterpret_cast<float*>(ws + p.off_part);
-        ba.status = reinterpret_cast<int*>(ws);
+        ba.status = reinterpret_cast<int*>(sa);
         ba.npairs = p.npairs;
         ba.nrp = p.nrp;
         ba.ncb = p.ncb;
@@ -651,7 +670,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.grid_sel = (grid_kind == GRID_CHECK_ON_DEVICE) ? grid_flag : nullptr;
         ba.grid_word = grid_flag;
         ba.cull_sel = (g_culling.load(std::memory_order_relaxed) && !(hints & IGS_HINT_WIDE_GAUSSIANS)) ? pa.narrow_count : nullptr;
-        ba.exec_count = reinterpret_cast<unsigned long long*>(ws) + EXEC_COUNT_WORD / 2;
+        ba.exec_count = reinterpret_cast<unsigned long long*>(sa) + EXEC_COUNT_WORD / 2;
         ba.pairs_per_slab = p.pairs_per_slab;
         ba.B = B; ba.N = N;
         ba.C = pa.lay.col_s;  // the kernels use it as the colours' row stride only
@@ -678,8 +697,8 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
                     ba.tasks = reinterpret_cast<int4*>(ws + p.off_tasks);
                     ba.group_rect = reinterpret_cast<int4*>(
                         ws + align_up(p.off_tasks + (size_t)p.task_capacity * sizeof(int4), 256));
-                    ba.task_count = reinterpret_cast<int*>(ws) + TASK_COUNT_WORD;
-                    ba.task_next = reinterpret_cast<int*>(ws) + TASK_NEXT_WORD;
+                    ba.task_count = reinterpret_cast<int*>(sa) + TASK_COUNT_WORD;
+                    ba.task_next = reinterpret_cast<int*>(sa) + TASK_NEXT_WORD;
                     ba.task_capacity = p.task_capacity;
                     e = launch_backward_warp_chunk(p.ch.ct[k], ba, p, sm_count(device), st);
                 } else {
@@ -761,6 +780,137 @@ static int normalize_impl(const float* sums, int B, int H, int W, int C, float e
     ra.B = B; ra.C = C; ra.n_split = 1; ra.normalize = 1;
     ra.eps = eps;
     return (int)launch_reduce_normalize(ra, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// render + mean-squared-error loss + gradients in one call (igs_render_mse_sr)
+// ---------------------------------------------------------------------------
+struct RenderMsePlan {
+    FwdPlan fp;
+    BwdPlan bp;
+    bool fused;          // separable grid by its strides, one channel chunk, a separable backward for it
+    size_t off_bwd;      // the backward's workspace
+    size_t off_loss;     // block partial sums of the loss
+    size_t off_image;    // unfused path: image [B,C,HW] + weight sums [B,HW]
+    size_t off_gout;     // unfused path: upstream gradient [B,C,HW]
+    size_t bytes;
+};
+
+static int plan_render_mse(int B, int N, int H, int W, int C, int device, bool separable_by_strides, bool ordered,
+                           bool culling_on, const int* order, RenderMsePlan* p) {
+    int rc = plan_forward(B, N, H, W, C, device, &p->fp);
+    if (rc) return rc;
+    rc = plan_backward(B, N, H, W, C, device, &p->bp, ordered, separable_by_strides);
+    if (rc) return rc;
+    p->fused = separable_by_strides && p->bp.sep_ok && !p->bp.row_kernel && p->fp.tiles_sep > 0;
+    if (p->fused) single_split_for_ordered_calls(&p->fp, B, N, order, culling_on, device);
+    const long long HW = (long long)H * W;
+    size_t off = align_up(p->fp.bytes, 256);
+    p->off_bwd = off;
+    off = align_up(off + p->bp.bytes, 256);
+    p->off_loss = off;
+    long long lb = loss_terms_blocks(B, p->bp.nrp, p->bp.ncb);
+    if (lb < 1024) lb = 1024;  // (the unfused path's loss kernel uses up to 1024 blocks)
+    off = align_up(off + (size_t)lb * sizeof(float), 256);
+    p->off_image = off;
+    off = align_up(off + (size_t)B * (C + 1) * HW * sizeof(float), 256);
+    p->off_gout = off;
+    off = align_up(off + (size_t)B * C * HW * sizeof(float), 256);
+    p->bytes = off;
+    return IGS_OK;
+}
+
+static int render_mse_impl(const float* pos, const float* scales, const float* rot, const float* alpha,
+                           const float* colors, int log_scales, const float* x, const int64_t* xs, const float* y,
+                           const int64_t* ys, const float* target, int B, int N, int H, int W, int C, float eps,
+                           int mode, const float* upstream, float* loss, float* out, float* d_pos, float* d_scales,
+                           float* d_rot, float* d_alpha, float* d_colors, const int* order, int hints, void* workspace,
+                           size_t workspace_bytes, int device, void* stream) {
+    if (B < 1 || N < 1 || H < 1 || W < 1 || C < 1) return IGS_ERR_ARG;
+    if (mode != IGS_GRAD_REFERENCE && mode != IGS_GRAD_EXACT) return IGS_ERR_ARG;
+    if (hints & ~(IGS_HINT_WIDE_GAUSSIANS | IGS_HINT_GENERAL_GRID)) return IGS_ERR_ARG;
+    if (!pos || !scales || !rot || !colors || !x || !y || !target || !loss || !d_pos || !d_scales || !d_rot || !d_colors)
+        return IGS_ERR_ARG;
+    if ((alpha == nullptr) != (d_alpha == nullptr)) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long HW = (long long)H * W;
+    const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
+    const bool culling_on = g_culling.load(std::memory_order_relaxed) && !(hints & IGS_HINT_WIDE_GAUSSIANS);
+    const bool by_strides =
+        !(hints & IGS_HINT_GENERAL_GRID) && classify_grid(sx.h, sy.w, H, W, true) == GRID_SEPARABLE;
+    RenderMsePlan p;
+    rc = plan_render_mse(B, N, H, W, C, device, by_strides, order != nullptr, culling_on, order, &p);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < p.bytes) return IGS_ERR_WORKSPACE;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+
+    // the parameter tensors as the caller holds them: separate arrays, scales possibly as logs,
+    // opacities possibly absent (all ones)
+    ParamLayout lay;
+    std::memset(&lay, 0, sizeof(lay));
+    lay.pos_s = 2;
+    lay.s0_s = 2;
+    lay.s1_s = 1;
+    lay.col_s = C;
+    lay.log_scale = log_scales ? 1 : 0;
+
+    if (p.fused) {
+        // forward: un-normalised sums per gaussian split, left in the forward's workspace; its
+        // prologue also packs the backward's geometry records
+        FwdExtras ex;
+        ex.geo_out = reinterpret_cast<float*>(ws + p.off_bwd + p.bp.off_geo);
+        ex.leave_partials = 1;
+        float* partial = reinterpret_cast<float*>(ws + p.fp.off_partial);
+        rc = forward_impl(SHAPE_SCALE_ROT, pos, scales, rot, nullptr, alpha, colors, x, xs, y, ys, B, N, H, W, C, eps, 0,
+                          partial, nullptr, ws, p.fp.bytes, device, stream, &p.fp, &lay, order, hints, &ex);
+        if (rc) return rc;
+        LossTermArgs la;
+        std::memset(&la, 0, sizeof(la));
+        la.partial = partial;
+        la.target = target;
+        la.x = x;
+        la.y = y;
+        la.xs_b = sx.b; la.xs_w = sx.w; la.ys_b = sy.b; la.ys_h = sy.h;
+        la.upstream = upstream;
+        la.out = out;
+        la.wsum = nullptr;
+        la.prec = reinterpret_cast<float*>(ws + p.off_bwd + p.bp.off_prec[0]);
+        la.loss_partial = reinterpret_cast<float*>(ws + p.off_loss);
+        la.flags = reinterpret_cast<int*>(ws) + GRID_FLAG_WORD;
+        la.n_total = (long long)B * C * HW;
+        la.n_split = p.fp.n_split;
+        la.B = B; la.H = H; la.W = W; la.C = C;
+        la.nrp = p.bp.nrp; la.ncb = p.bp.ncb; la.ct = p.bp.ch.ct[0];
+        la.mode = mode;
+        la.eps = eps;
+        cudaError_t e = launch_loss_terms_sep(la, loss, st);
+        if (e != cudaSuccess) return (int)e;
+        BwdPrepared prep;
+        prep.status = ws;
+        return backward_impl(SHAPE_SCALE_ROT, pos, scales, rot, nullptr, alpha, colors, x, xs, y, ys, nullptr, nullptr,
+                             nullptr, B, N, H, W, C, eps, mode, d_pos, d_scales, d_rot, nullptr, d_alpha, d_colors,
+                             nullptr, nullptr, order, hints, ws + p.off_bwd, p.bp.bytes, device, stream, &lay, &prep);
+    }
+
+    // any other grid or channel count: the same steps one after the other
+    float* image = out ? out : reinterpret_cast<float*>(ws + p.off_image);
+    float* wsum = reinterpret_cast<float*>(ws + p.off_image) + (size_t)B * C * HW;
+    float* gout = reinterpret_cast<float*>(ws + p.off_gout);
+    rc = forward_impl(SHAPE_SCALE_ROT, pos, scales, rot, nullptr, alpha, colors, x, xs, y, ys, B, N, H, W, C, eps, 1, image,
+                      wsum, ws, p.fp.bytes, device, stream, nullptr, &lay, order, hints, nullptr);
+    if (rc) return rc;
+    const long long n = (long long)B * C * HW;
+    rc = igs_mse_loss(image, target, n, loss, ws + p.off_loss, IGS_MSE_WORKSPACE_BYTES, device, stream);
+    if (rc) return rc;
+    rc = igs_mse_grad(image, target, n, upstream, gout, device, stream);
+    if (rc) return rc;
+    return backward_impl(SHAPE_SCALE_ROT, pos, scales, rot, nullptr, alpha, colors, x, xs, y, ys, wsum, image, gout, B, N,
+                         H, W, C, eps, mode, d_pos, d_scales, d_rot, nullptr, d_alpha, d_colors, nullptr, nullptr, order,
+                         hints, ws + p.off_bwd, p.bp.bytes, device, stream, &lay, nullptr);
 }
 
 }  // namespace igs
@@ -879,6 +1029,33 @@ int igs_backward_cov(const float* positions, const float* cov_inv_00, const floa
                          y_strides, wsum, out, gout, B, N, H, W, C, eps, grad_mode, d_positions, d_cov_inv_00,
                          d_cov_inv_01, d_cov_inv_11, d_alphas, d_colors, d_x, d_y, order, hints, workspace,
                          workspace_bytes, device, stream);
+}
+
+int igs_render_mse_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* bytes) {
+    if (!bytes) return IGS_ERR_ARG;
+    int rc = check_device(device);
+    if (rc) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return IGS_ERR_DEVICE;
+    // the largest of the layouts a call of this shape can choose (an order only shrinks the forward's)
+    RenderMsePlan a, b;
+    rc = plan_render_mse(B, N, H, W, C, device, true, true, false, nullptr, &a);
+    if (rc) return rc;
+    rc = plan_render_mse(B, N, H, W, C, device, false, false, false, nullptr, &b);
+    if (rc) return rc;
+    *bytes = a.bytes > b.bytes ? a.bytes : b.bytes;
+    return IGS_OK;
+}
+
+int igs_render_mse_sr(const float* positions, const float* scales, const float* rotations, const float* alphas,
+                      const float* colors, int log_scales, const float* x, const int64_t* x_strides, const float* y,
+                      const int64_t* y_strides, const float* target, int B, int N, int H, int W, int C, float eps,
+                      int grad_mode, const float* upstream, float* loss, float* out, float* d_positions,
+                      float* d_scales, float* d_rotations, float* d_alphas, float* d_colors, const int* order,
+                      int hints, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    return render_mse_impl(positions, scales, rotations, alphas, colors, log_scales, x, x_strides, y, y_strides, target,
+                           B, N, H, W, C, eps, grad_mode, upstream, loss, out, d_positions, d_scales, d_rotations,
+                           d_alphas, d_colors, order, hints, workspace, workspace_bytes, device, stream);
 }
 
 int igs_set_culling(int on) {

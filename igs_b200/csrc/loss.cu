@@ -6,7 +6,12 @@
 //   igs_mse_grad: gout = upstream * 2 (out - target) / n    (one launch)
 // No atomics: block partial sums are written to the workspace and added in a fixed order by
 // one block, so the loss is repeatable to the bit.
-#include "common.cuh"
+//
+// loss_terms_sep_kernel is the fused form for the per-image fit (igs_render_mse_sr): it
+// takes the forward's un-normalised sums and does, in one pass over the image, what
+// otherwise takes the normalisation, the two loss kernels, the loss-gradient kernel and the
+// backward's pixel-terms kernel -- without ever writing the upstream gradient to memory.
+#include "loss.cuh"
 
 namespace igs {
 
@@ -58,6 +63,122 @@ __global__ void __launch_bounds__(MSE_THREADS) mse_grad_kernel(const float* __re
     const long long stride = (long long)gridDim.x * MSE_THREADS;
     for (long long i = (long long)blockIdx.x * MSE_THREADS + threadIdx.x; i < n; i += stride)
         gout[i] = k * (out[i] - target[i]);
+}
+
+// One thread per 2-row x 4-column block of pixels (the unit of the separable backward's
+// records).  Per pixel: S and the numerators summed over the gaussian splits in split order,
+// out = R / (S + eps), d = out - target, the block's share of sum d^2, the upstream gradient
+// g = k * d with k = upstream * 2 / n, and from it the backward's terms gn = g / (S + eps),
+// gS = -sum_c g_c^2 / (S + eps)^2 (reference mode) or -sum_c gn_c * out_c (exact mode): the
+// same expressions, in the same order, as reduce_normalize_kernel, mse_grad_kernel and
+// pixel_terms_sep_kernel, so that the fused and the unfused path agree to the last bit in
+// everything but the order in which the loss is added up.
+__global__ void __launch_bounds__(LOSS_TERMS_THREADS) loss_terms_sep_kernel(LossTermArgs a) {
+    extern __shared__ __align__(16) float s_rec[];  // [blockDim.x][record floats], then 8 floats for the block sum
+    const int rs = bwd_sep_rec_floats(a.ct), pf = bwd_sep_pair_floats(a.ct);
+    const long long per_b = (long long)a.nrp * a.ncb;
+    const long long total = (long long)a.B * per_b;
+    const long long i_raw = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool in_range = i_raw < total;
+    const long long i = in_range ? i_raw : total - 1;
+    const long long b = i / per_b, blk = i - b * per_b;
+    const int rp = (int)(blk / a.ncb), cbk = (int)(blk - (long long)rp * a.ncb);
+    const long long HW = (long long)a.H * a.W;
+    const int h0 = rp * 2, w0 = cbk * 4;
+    const long long split_stride = (long long)a.B * (a.C + 1) * HW;
+    const float* part_b = a.partial + b * (a.C + 1) * HW;
+    const float k = (a.upstream ? *a.upstream : 1.f) * 2.f / (float)a.n_total;
+
+    float* rec = s_rec + (size_t)threadIdx.x * rs;
+    float xv[4], yv[2];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) xv[q] = a.x[b * a.xs_b + (long long)min(w0 + q, a.W - 1) * a.xs_w];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) yv[q] = a.y[b * a.ys_b + (long long)min(h0 + q, a.H - 1) * a.ys_h];
+    reinterpret_cast<float4*>(rec)[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
+    reinterpret_cast<float4*>(rec)[1] = make_float4(yv[0], yv[1], 0.f, 0.f);
+
+    bool bad = false;
+    float lsum = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bool valid = in_range && (h0 + r < a.H) && (w0 + q < a.W);
+            const long long pp = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + q, a.W - 1);
+            float S = 0.f;
+            for (int sp = 0; sp < a.n_split; ++sp) S += part_b[sp * split_stride + (long long)a.C * HW + pp];
+            const float Sp = S + a.eps;
+            float acc = 0.f;
+            // pixel (r, q) is lane q & 1 of pixel pair 2 * r + (q >> 1)
+            float* pr = rec + 8 + (r * 2 + (q >> 1)) * pf + (q & 1);
+            for (int c = 0; c < pf / 2 - 1; ++c) {
+                float gn = 0.f;
+                if (c < a.C) {
+                    float R = 0.f;
+                    for (int sp = 0; sp < a.n_split; ++sp) R += part_b[sp * split_stride + (long long)c * HW + pp];
+                    const float o = R / Sp;
+                    const float d = o - a.target[(b * a.C + c) * HW + pp];
+                    const float g = k * d;
+                    if (valid) {
+                        lsum = fmaf(d, d, lsum);
+                        if (a.out) a.out[(b * a.C + c) * HW + pp] = o;
+                    }
+                    acc += (a.mode == IGS_GRAD_REFERENCE) ? g * g : (g / Sp) * o;
+                    gn = valid ? g / Sp : 0.f;
+                    bad |= !isfinite(gn);
+                }
+                pr[2 + 2 * c] = gn;
+            }
+            const float gS = valid ? ((a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp * Sp) : -acc) : 0.f;
+            bad |= !isfinite(gS);
+            pr[0] = gS;
+            if (valid && a.wsum) a.wsum[b * HW + pp] = S;
+        }
+    }
+    __syncthreads();
+    {
+        // the CTA writes its records out in consecutive 16-byte pieces
+        const long long first = (long long)blockIdx.x * blockDim.x;
+        const long long n_here = total - first < (long long)blockDim.x ? total - first : (long long)blockDim.x;
+        float4* dst = reinterpret_cast<float4*>(a.prec + first * rs);
+        const float4* src4 = reinterpret_cast<const float4*>(s_rec);
+        for (long long j = threadIdx.x; j < n_here * (rs / 4); j += blockDim.x) dst[j] = src4[j];
+    }
+    if (bad && a.flags) atomicOr(a.flags, UPSTREAM_NOT_FINITE);
+    // this CTA's share of the loss (added up in a fixed order: repeatable to the bit)
+    float* s_warp = s_rec + (size_t)blockDim.x * rs;
+    __syncthreads();
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, d);
+    if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = lsum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < LOSS_TERMS_THREADS / 32; ++w) t += s_warp[w];
+        a.loss_partial[blockIdx.x] = t;
+    }
+}
+
+long long loss_terms_blocks(int B, int nrp, int ncb) {
+    return ((long long)B * nrp * ncb + LOSS_TERMS_THREADS - 1) / LOSS_TERMS_THREADS;
+}
+
+cudaError_t launch_loss_terms_sep(const LossTermArgs& a, float* loss, cudaStream_t s) {
+    const long long blocks = loss_terms_blocks(a.B, a.nrp, a.ncb);
+    if (blocks <= 0) return cudaSuccess;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)LOSS_TERMS_THREADS * bwd_sep_rec_floats(a.ct) * sizeof(float) + 8 * sizeof(float);
+    {
+        KernelTimer timer(K_PIXEL_TERMS, s);
+        loss_terms_sep_kernel<<<(unsigned)blocks, LOSS_TERMS_THREADS, smem, s>>>(a);
+    }
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    mse_finish_kernel<<<1, MSE_THREADS, 0, s>>>(a.loss_partial, (int)blocks, a.n_total, loss);
+    count_launch();
+    return cudaGetLastError();
 }
 
 static int mse_blocks(long long n) {

@@ -80,13 +80,25 @@ struct ParamLayout {
     float* d_unused;               // backward: a column (row stride pos_s) to fill with zeros, or nullptr
 };
 
+// Extras of a forward that is the first half of a fused forward + loss + backward call.
+struct FwdExtras {
+    float* geo_out;       // the prologue also writes the backward's geometry records here, or nullptr
+    int leave_partials;   // do not add the gaussian splits up: the caller reads [n_split][B][C+1][HW] itself
+};
+
+// What a backward may find already done by such a forward (see backward_impl).
+struct BwdPrepared {
+    unsigned char* status;  // the forward's status area: narrow count, axis flags
+};
+
 // Body of igs_forward_sr / igs_forward_cov (kind = ShapeKind).  use_plan, when given,
 // replaces the plan the call would compute itself.
 int forward_impl(int kind, const float* pos, const float* s0, const float* s1, const float* s2, const float* alpha,
                  const float* colors, const float* x, const int64_t* xs, const float* y, const int64_t* ys, int B, int N,
                  int H, int W, int C, float eps, int normalize, float* out, float* wsum, void* workspace,
                  size_t workspace_bytes, int device, void* stream, const FwdPlan* use_plan = nullptr,
-                 const ParamLayout* layout = nullptr, const int* order = nullptr, int hints = 0);
+                 const ParamLayout* layout = nullptr, const int* order = nullptr, int hints = 0,
+                 const FwdExtras* extras = nullptr);
 
 // occupancy (CTAs per SM) of the instantiation a plan selects; defined next to the kernels
 int forward_ctas_per_sm(int ct, int device);

@@ -77,6 +77,24 @@ class ImageFitter(nn.Module):
         return gaussian_splatting_2d(self.position, self.color, torch.exp(self.log_scale) + EPS, self.rotation,
                                      self.alphas, x_grid, y_grid)
 
+    def mse_loss_and_backward(self, target):
+        """mean((render - target)^2) with the gradients of all four parameter tensors written
+        to their ``.grad`` (replacing what was there), through ONE library call
+        (igs_render_mse_sr): what ``mse_loss(self(size), target).backward()`` computes, without
+        the image, the upstream gradient or the weight sums ever going to memory.  Returns the
+        loss as a device scalar."""
+        from . import gs2d
+
+        x_grid, y_grid = self.grids(target.shape[-2:])
+        pos, ls, rot, col = (p.detach() for p in (self.position, self.log_scale, self.rotation, self.color))
+        info = _lib.prepare_call(x_grid, y_grid, pos, scales=ls, log_scales=True)
+        loss, g, _ = _lib.render_mse(pos, ls, rot, None, col, info.x3, info.y3, target, EPS,
+                                     gs2d._GRAD_MODES[gs2d.get_grad_mode()], log_scales=True, order=info.order,
+                                     hints=info.hints, info=info)
+        self.position.grad, self.log_scale.grad = g["positions"], g["scales"]
+        self.rotation.grad, self.color.grad = g["rotations"], g["colors"]
+        return loss
+
 
 class _MSELoss(torch.autograd.Function):
     """F.mse_loss(out, target) for contiguous fp32 CUDA tensors through the library's two
@@ -102,7 +120,20 @@ def mse_loss(out, target):
     return F.mse_loss(out, target)
 
 
-def _eager_step(model, opt, target):
+def _fusable(model, target):
+    return (isinstance(model, ImageFitter) and target.is_cuda and target.dtype == torch.float32
+            and target.is_contiguous() and target.dim() == 4 and target.shape[0] == 1
+            and target.shape[1] == model.color.shape[-1])
+
+
+def _eager_step(model, opt, target, fused=True):
+    """One optimiser step on mean((render - target)^2).  fused: render, loss and gradients in
+    one library call where the model and the target allow it (same numbers as the autograd
+    route to fp32 rounding)."""
+    if fused and _fusable(model, target):
+        loss = model.mse_loss_and_backward(target)
+        opt.step()
+        return loss
     opt.zero_grad(set_to_none=False)
     loss = mse_loss(model(target.shape[-2:]), target)
     loss.backward()

@@ -315,6 +315,38 @@ int igs_mse_grad(const float* out, const float* target, long long n, const float
                  int device, void* stream);
 
 /*
+ * Render, mean-squared-error loss and all gradients in one call: what one step of the
+ * reference's per-image fit computes (scripts/2dgs_img_comp.py: the model's forward
+ * :107-126, `GaussianSplatting2D.render(position, color, exp(log_scale) + eps, rotation,
+ * ones, grids)`, the L2 term of its loss :132-143, `F.mse_loss(rendered_image,
+ * target_image)`, and autograd back through both).
+ *   loss  (device scalar)  = mean((image - target)^2) over B*C*H*W elements;
+ *   d_*                    = upstream * d loss / d parameter, by the backward of
+ *                            igs_backward_sr in `grad_mode`;
+ *   log_scales != 0: `scales` holds log-scales, scale = exp(v) + eps, and d_scales is the
+ *                    gradient with respect to the log-scales (the fit's parametrisation);
+ *   alphas == NULL (with d_alphas == NULL): all opacities are one, as the fit script has them;
+ *   upstream: device scalar d objective / d loss, or NULL for 1;
+ *   out: receives the image [B,C,H,W], or NULL if the caller does not need it.
+ * On a grid that is separable by its strides (x row stride 0, y column stride 0: what
+ * xy_grid makes) with at most 4 channels the steps are fused: the forward's prologue also
+ * packs the backward's records, and one kernel turns the forward's un-normalised sums into
+ * the image, the loss and the backward's per-pixel terms, so neither the upstream gradient
+ * nor the weight sums ever go to memory.  Any other input runs the same steps one after the
+ * other; the results are the same to fp32 rounding either way.  No atomics: loss and
+ * gradients are repeatable to the bit.  order, hints: as for igs_forward_sr.
+ */
+int igs_render_mse_workspace_bytes(int B, int N, int H, int W, int C, int device, size_t* bytes);
+int igs_render_mse_sr(const float* positions, const float* scales, const float* rotations,
+                      const float* alphas, const float* colors, int log_scales, const float* x,
+                      const int64_t* x_strides, const float* y, const int64_t* y_strides,
+                      const float* target, int B, int N, int H, int W, int C, float eps, int grad_mode,
+                      const float* upstream, float* loss, float* out, float* d_positions,
+                      float* d_scales, float* d_rotations, float* d_alphas, float* d_colors,
+                      const int* order, int hints, void* workspace, size_t workspace_bytes, int device,
+                      void* stream);
+
+/*
  * Per-kernel device timing for reports.  While enabled, every kernel launch of the
  * library is bracketed by CUDA events recorded on the launch's own stream;
  * igs_profile_read waits for the recorded events and returns the accumulated device

@@ -209,8 +209,10 @@ def test_fit_protocol_first_adam_steps_against_an_oracle_driven_adam(dev):
         assert float(np.percentile(diff, 99)) <= 1e-5, (k, float(np.percentile(diff, 99)), float(diff.max()))
 
 
-def test_image_fitter_steps_against_an_oracle_driven_adam(dev):
-    """igs_b200.fit: three steps of ImageFitter + Adam (the loop fit() runs, eager) against
+@pytest.mark.parametrize("fused", [True, False], ids=["fused-call", "autograd-route"])
+def test_image_fitter_steps_against_an_oracle_driven_adam(fused, dev):
+    """igs_b200.fit: three steps of ImageFitter + Adam (the loop fit() runs, eager; through
+    the fused render + MSE + gradient call and through autograd) against
     the oracle-driven Adam in the fitter's own parametrisation (scales = exp(log_scale) + eps,
     opacities one): per-step loss and the gradients of position, log-scale, rotation, colour."""
     from igs_b200 import fit
@@ -244,7 +246,7 @@ def test_image_fitter_steps_against_an_oracle_driven_adam(dev):
 
     for step in range(3):
         here = {k: _np(v) for k, v in model.named_parameters()}
-        loss = fit._eager_step(model, opt, tgt_d)  # zero_grad, render, MSE, backward, Adam step
+        loss = fit._eager_step(model, opt, tgt_d, fused=fused)  # render, MSE, backward, Adam step
         o_loss, o_grads = oracle_at(here)
         assert abs(float(loss) - o_loss) <= 1e-5 * o_loss, (step, float(loss), o_loss)
         _assert_grads({k: _np(v.grad) for k, v in model.named_parameters()}, o_grads, f"step {step}")

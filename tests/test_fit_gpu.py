@@ -43,6 +43,89 @@ def test_fit_reduces_loss_and_graph_matches_eager(sort):
     assert torch.allclose(eager, graphed, rtol=2e-3, atol=1e-7), (eager[-5:], graphed[-5:])
 
 
+@pytest.mark.parametrize("mode", ["reference", "exact"])
+@pytest.mark.parametrize("case", ["wide", "narrow_ordered", "narrow_unordered"])
+def test_fused_render_mse_step_equals_the_autograd_route(case, mode):
+    """igs_render_mse_sr (render + MSE + all gradients in one library call) against the same
+    step through autograd (render, library MSE, backward): loss and gradients to 1e-6, and at
+    least four library launches fewer per step.  Wide gaussians; narrow gaussians with the
+    ordered kernels (stage lists, task queue) and without an order (skipping per CTA)."""
+    from igs_b200 import _lib, fit, gs2d
+
+    dev = torch.device("cuda", 0)
+    N, H, W = 2500, 96, 136
+    tgt = _target(H, W, dev, seed=7)
+    gen = torch.Generator().manual_seed(11)
+    model = fit.ImageFitter(N, channels=3, init_log_scale=-1.5 if case == "wide" else -4.0)
+    with torch.no_grad():
+        model.position.add_(torch.randn(1, N, 2, generator=gen) * 0.03)
+        model.log_scale.add_(torch.rand(1, N, 2, generator=gen) * 0.6)
+        model.rotation.copy_(torch.rand(1, N, generator=gen) * 6.28)
+        model.color.copy_(torch.rand(1, N, 3, generator=gen))
+    model.to(dev)
+    _lib.set_backward_sort("on" if case == "narrow_ordered" else "off")
+    try:
+        with gs2d.grad_mode(mode):
+            results, launches = {}, {}
+            for fused in (False, True):
+                for p in model.parameters():
+                    p.grad = None
+                for rep in range(2):  # the second time the call layer has learnt about the data
+                    n0 = _lib.launch_count()
+                    if fused:
+                        loss = model.mse_loss_and_backward(tgt)
+                    else:
+                        for p in model.parameters():
+                            p.grad = None
+                        loss = fit.mse_loss(model((H, W)), tgt)
+                        loss.backward()
+                    torch.cuda.synchronize()
+                    launches[fused] = _lib.launch_count() - n0
+                results[fused] = (float(loss), {k: v.grad.clone() for k, v in model.named_parameters()})
+    finally:
+        _lib.set_backward_sort("auto")
+    (l0, g0), (l1, g1) = results[False], results[True]
+    assert abs(l1 - l0) <= 1e-6 * abs(l0), (l0, l1)
+    for k in g0:
+        scale = float(g0[k].abs().max())
+        assert float((g1[k] - g0[k]).abs().max()) <= 1e-6 * scale, (k, float((g1[k] - g0[k]).abs().max()), scale)
+    assert launches[True] <= launches[False] - 4, launches
+
+
+def test_fused_render_mse_falls_back_for_other_grids_and_channel_counts():
+    """What the fused kernel does not take (a warped grid, 8 channels) runs the same steps one
+    after the other inside the same call: same loss and gradients as the autograd route."""
+    from igs_b200 import _lib
+    from igs_b200.gs2d import GaussianSplatting2D, gaussian_splatting_2d
+
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(12)
+    for C, warp in ((3, True), (8, False)):
+        B, N, H, W = 2, 300, 40, 56
+        pos = (torch.rand(B, N, 2, generator=gen) * 2 - 1).to(dev)
+        ls = (torch.rand(B, N, 2, generator=gen) - 2.5).to(dev)
+        rot = (torch.rand(B, N, generator=gen) * 6.28).to(dev)
+        al = (torch.rand(B, N, generator=gen) * 0.9 + 0.1).to(dev)
+        col = torch.rand(B, N, C, generator=gen).to(dev)
+        tgt = torch.rand(B, C, H, W, generator=gen).to(dev)
+        xg, yg = GaussianSplatting2D.xy_grid((H, W), dev)
+        xg, yg = xg[None].expand(B, -1, -1, -1), yg[None].expand(B, -1, -1, -1)
+        if warp:
+            xg = (xg + 0.02 * torch.sin(5 * yg)).contiguous()
+            yg = yg.contiguous()
+        x3, y3 = xg[:, 0], yg[:, 0]
+        loss, g, image = _lib.render_mse(pos, ls, rot, al, col, x3, y3, tgt, 1e-6, 0, log_scales=True, want_image=True)
+        leaves = [t.clone().requires_grad_() for t in (pos, col, ls, rot, al)]
+        out = gaussian_splatting_2d(leaves[0], leaves[1], torch.exp(leaves[2]) + 1e-6, leaves[3], leaves[4], xg, yg)
+        ref = torch.nn.functional.mse_loss(out, tgt)
+        ref.backward()
+        assert abs(float(loss) - float(ref)) <= 1e-6 * float(ref)
+        assert float((image - out).abs().max()) <= 1e-6
+        for k, t in zip(("positions", "colors", "scales", "rotations", "alphas"), leaves):
+            scale = float(t.grad.abs().max())
+            assert float((g[k] - t.grad).abs().max()) <= 2e-6 * scale, (C, k)
+
+
 def test_fit_resolution_schedule():
     from igs_b200 import fit
 
