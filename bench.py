@@ -673,7 +673,12 @@ def culling_report(args, wl, on_dev, _lib, torch):
     if culling["active"]:
         # one backward through the library call, with the order the policy would pass, to read
         # how many (gaussian, pixel) evaluations the culling kernels really did
-        order = _lib.spatial_order(on_dev["positions"], x3, y3) if args.backward_sort != "off" else None
+        order = None
+        if args.backward_sort != "off":  # the order the call layer would pass
+            order = _lib.order_by_policy(_lib._shape_memo(x3.device, wl.B_local, wl.N_local, wl.cfg.H, wl.cfg.W),
+                                         on_dev["positions"], None, None, x3, y3, on_dev["scales"])
+            if order is None:
+                order = _lib.spatial_order(on_dev["positions"], x3, y3)
         probe_bwd = _lib.backward("sr", on_dev["positions"], on_dev["scales"], on_dev["rotations"], None,
                                   on_dev["alphas"], on_dev["colors"], x3, y3, probe_fwd[1], probe_fwd[0],
                                   torch.ones_like(probe_fwd[0]), 1e-6, 0, False, keep_workspace=True, order=order)

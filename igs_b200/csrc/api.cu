@@ -121,35 +121,37 @@ int make_chunks(int C, Chunks* out) {
     return IGS_OK;
 }
 
-// Picks the count (1..max_parts) of equal parts along the streamed axis that wastes the
-// fewest CTA slots in the last wave (ties go to the smaller count).  `run_slots` are the CTA
-// slots of the kernel that will actually run: if the choice gives it fewer than four waves,
-// a deeper one (eight to sixteen waves) is taken instead -- CTAs do not finish in lockstep,
-// so with one or two waves the slowest SM sets the time (measured on B=1, N=16384, 512 x 512,
-// backward: 2.47 / 2.45 / 2.29 / 2.24 / 2.23 ms at 1 / 2 / 3 / 4 / 8 waves; at seven waves and
-// more the count no longer matters: 4.39-4.44 ms for 8 to 32 slabs on B=16, N=8192, 256 x 256).
-static int pick_parts(long long base_ctas, long long slots, long long axis_len, long long min_len, int max_parts,
-                      long long run_slots = 0) {
-    if (run_slots <= 0) run_slots = slots;
-    int best = 1, best_deep = 0;
-    double best_eff = -1.0, best_deep_eff = -1.0;
-    for (int s = 1; s <= max_parts; ++s) {
-        if (s > 1 && axis_len / s < min_len) break;
-        const long long ctas = base_ctas * s;
-        const long long waves = (ctas + slots - 1) / slots;
-        const double eff = (double)ctas / (double)(waves * slots);
-        if (eff > best_eff + 0.02) {
-            best_eff = eff;
-            best = s;
-        }
-        const long long run_waves = (ctas + run_slots - 1) / run_slots;
-        const double run_eff = (double)ctas / (double)(run_waves * run_slots);
-        if (run_waves >= 8 && run_waves <= 16 && run_eff > best_deep_eff + 0.02) {
-            best_deep_eff = run_eff;
-            best_deep = s;
+// How the streamed axis (gaussians in the forward, pixels in the backward) is cut into parts,
+// one CTA per (part, everything else).  The axis comes in indivisible units (stages of 128
+// gaussians, row pairs, chunks of pixel pairs); a part is `per` consecutive units.  The model:
+// CTAs run in waves of `slots`, every CTA of a wave takes per + overhead (its prologue and
+// epilogue, in units), so the kernel takes waves * (per + overhead); the partition with the
+// least modelled time wins, a deeper one only if it is at least half a percent better (more
+// parts mean more partial sums to write and add up).  CTAs do not finish in lockstep, so with
+// one or two waves the slowest SM sets the time (measured on B=1, N=16384, 512 x 512, backward:
+// 2.47 / 2.45 / 2.29 / 2.24 / 2.23 ms at 1 / 2 / 3 / 4 / 8 waves): fewer than three waves are
+// charged 8 % extra.
+struct Parts {
+    long long per;  // units per part
+    int n;          // parts
+};
+static Parts pick_parts(long long base_ctas, long long slots, long long units, double overhead, int max_parts,
+                        long long min_units) {
+    if (units < 1) units = 1;
+    if (base_ctas < 1) base_ctas = 1;
+    Parts best{units, 1};
+    double best_t = -1.0;
+    for (long long per = units; per >= 1; --per) {
+        const long long n = (units + per - 1) / per;
+        if (n > max_parts || (n > 1 && per < min_units)) break;
+        if (per < units && (units + per) / (per + 1) == n) continue;  // a larger `per` gives the same count
+        const long long waves = (base_ctas * n + slots - 1) / slots;
+        const double t = (double)waves * ((double)per + overhead) * (waves < 3 ? 1.08 : 1.0);
+        if (best_t < 0.0 || t < best_t * 0.995) {
+            best_t = t;
+            best = Parts{per, (int)n};
         }
     }
-    if (best_deep && base_ctas * best < 4 * run_slots) return best_deep;
     return best;
 }
 
@@ -174,16 +176,12 @@ int plan_forward(int B, int N, int H, int W, int C, int device, FwdPlan* p) {
     p->stages = 2;
     const long long slots = (long long)sm_count(device) * forward_ctas_per_sm(ct, device);
     const long long base = tiles * (B > 0 ? B : 1);
-    int ns = pick_parts(base > 0 ? base : 1, slots, N, 2LL * p->chunk_g, 64);
-    if (ns > 65535) ns = 65535;
-    p->n_split = ns;
-    // splits start on a stage boundary so that every bulk copy is a whole number of records
-    long long per = (N + ns - 1) / ns;
-    per = (per + p->chunk_g - 1) / p->chunk_g * p->chunk_g;
-    if (per <= 0) per = p->chunk_g;
-    p->per_split = (int)per;
-    p->n_split = (int)((N + per - 1) / per);
-    if (p->n_split < 1) p->n_split = 1;
+    // splits are whole stages (every bulk copy is a whole number of records); a CTA's epilogue
+    // (its partial sums) costs about a third of a stage
+    const long long stages_n = ((long long)N + p->chunk_g - 1) / p->chunk_g;
+    const Parts split = pick_parts(base, slots, stages_n, 0.3, 64, 2);
+    p->per_split = (int)(split.per * p->chunk_g);
+    p->n_split = split.n;
 
     size_t off = STATUS_BYTES;
     const long long M = (long long)B * N;
@@ -225,18 +223,23 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     // The slab count is chosen for the general kernel's occupancy; when the separable kernel
     // will run (it holds fewer CTAs per SM: more registers) and would get fewer than four
     // waves, a deeper count is taken.  The workspace covers both.
+    // general kernel: units are stages of pixel pairs; separable kernels: row pairs.  A CTA's
+    // prologue and epilogue cost about what ten 2 x 4-pixel blocks cost.
     const long long slots_gen = (long long)sm_count(device) * backward_ctas_per_sm(ct, device);
-    const int ns_gen = pick_parts(base > 0 ? base : 1, slots_gen, p->npairs, 2LL * p->chunk_pairs, 256);
+    const long long chunks_n = (p->npairs + p->chunk_pairs - 1) / p->chunk_pairs;
+    const int ns_gen = pick_parts(base, slots_gen, chunks_n, 40.0 / p->chunk_pairs, 256, 2).n;
     int ns_sep = ns_gen;
+    long long rp_sep = 0;  // row pairs per slab the separable kernel's own partition takes
     if (p->sep_ok) {
         const int per_sm = p->row_kernel ? backward_row_ctas_per_sm(ct, device) : backward_sep_ctas_per_sm(ct, device);
         if (per_sm > 0) {
-            const long long slots_sep = (long long)sm_count(device) * per_sm;
-            ns_sep = pick_parts(base_sep > 0 ? base_sep : 1, slots_sep, p->npairs, 2LL * p->chunk_pairs, 256, slots_sep);
+            const Parts rows = pick_parts(base_sep, (long long)sm_count(device) * per_sm, p->nrp,
+                                          10.0 / (p->ncb > 0 ? p->ncb : 1), 256, 1);
+            ns_sep = rows.n;
+            rp_sep = rows.per;
         }
     }
     const int ns = (separable_grid && p->sep_ok) ? ns_sep : ns_gen;
-    const int ns_other = (separable_grid && p->sep_ok) ? ns_gen : ns_sep;  // covered by the workspace size
     // Fine partition: slabs of 8 row pairs, at most 96 of them, never fewer than the plain
     // partition has.  A function of the shape alone, like the plain one, so the result's bits
     // depend on whether an order was passed but not on the order or on the gaussians.
@@ -274,10 +277,14 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     // workspace size must not depend on that choice
     int n_slab_max = ns_gen > ns_sep ? ns_gen : ns_sep;
     if (ns_fine > n_slab_max) n_slab_max = ns_fine;
-    (void)ns_other;
     p->planes = N_MOMENTS * p->ch.n + C;
     // separable variant: same slab count, slabs are ranges of whole row pairs
-    p->rp_per_slab = (p->nrp + p->n_slab - 1) / p->n_slab;
+    if (!fine && separable_grid && p->sep_ok && rp_sep > 0) {
+        p->n_slab = ns_sep;
+        p->rp_per_slab = (int)rp_sep;
+    } else {
+        p->rp_per_slab = (p->nrp + p->n_slab - 1) / p->n_slab;
+    }
     if (p->rp_per_slab < 1) p->rp_per_slab = 1;
 
     size_t off = STATUS_BYTES;

@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(256) pack_kernel(PackArgs a) {
         }
 
         if (a.geo) {
-            float4* g = reinterpret_cast<float4*>(a.geo + slot * GEO_FLOATS);
+            // (indexed by the gaussian, not by the slot: the backward kernels follow the order themselves)
+            float4* g = reinterpret_cast<float4*>(a.geo + i * GEO_FLOATS);
             g[0] = make_float4(px, py, A, B2);
             g[1] = make_float4(Cq, al, hx, hy);
         }
