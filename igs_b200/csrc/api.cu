@@ -586,7 +586,8 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     // which kernel family will (probably) run is known from the strides, or assumed separable
     // when the data has to be checked on the device (a materialised xy_grid)
     const Strides sx = get_strides(xs, H, W), sy = get_strides(ys, H, W);
-    const bool likely_separable = !(hints & IGS_HINT_GENERAL_GRID) && classify_grid(sx.h, sy.w, H, W, true) != GRID_GENERAL;
+    // (not a matter of the hints: the partition, and with it the bits of the result, must be the same with and without them)
+    const bool likely_separable = classify_grid(sx.h, sy.w, H, W, true) != GRID_GENERAL;
     BwdPlan p;
     rc = plan_backward(B, N, H, W, C, device, &p, order != nullptr, likely_separable);
     if (rc) return rc;
