@@ -141,10 +141,10 @@ static Parts pick_parts(long long base_ctas, long long slots, long long units, d
     if (base_ctas < 1) base_ctas = 1;
     Parts best{units, 1};
     double best_t = -1.0;
-    for (long long per = units; per >= 1; --per) {
+    for (long long want = 1; want <= max_parts && want <= units; ++want) {
+        const long long per = (units + want - 1) / want;  // the shortest parts that give this count
+        if (want > 1 && per < min_units) break;
         const long long n = (units + per - 1) / per;
-        if (n > max_parts || (n > 1 && per < min_units)) break;
-        if (per < units && (units + per) / (per + 1) == n) continue;  // a larger `per` gives the same count
         const long long waves = (base_ctas * n + slots - 1) / slots;
         const double t = (double)waves * ((double)per + overhead) * (waves < 3 ? 1.08 : 1.0);
         if (best_t < 0.0 || t < best_t * 0.995) {
