@@ -43,7 +43,7 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
 
 METRIC = "gaussian_pixel_evals_per_s_fwd_bwd"
 UNIT = "evals/s"
-SPLAT_WORKLOADS = ["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_b8", "cfg4", "narrow", "narrow64k"]
+SPLAT_WORKLOADS = ["cfg0", "cfg2", "cfg2_small", "cfg3", "cfg4_small", "cfg4_b8", "cfg4", "narrow", "narrow64k"]
 NAMES = ("positions", "colors", "scales", "rotations", "alphas")
 
 
@@ -564,7 +564,10 @@ def run_b200(args):
         # so it can exceed 1; `executed_frac` is the pipe's utilisation.
         has_sep_f, has_sep_b = _lib.separable_kernels(C)
         sep_f, sep_b = wl.separable_grid and has_sep_f, wl.separable_grid and has_sep_b
-        executed = {"forward": (5 + C) if sep_f else (8 + C), "backward": (8 + 2 * C) if sep_b else (16 + 2 * C)}
+        # (separable backward: 7.5 + 2C in the pixel-packed kernels for up to 4 channels, which
+        # share dx^2 between the two rows of a block; 8 + 2C in the row-streaming 8 / 16-channel ones)
+        executed = {"forward": (5 + C) if sep_f else (8 + C),
+                    "backward": ((7.5 if C <= 4 else 8) + 2 * C) if sep_b else (16 + 2 * C)}
         instr = {"forward": 9 + C, "backward": 18 + 2 * C}
         sep = {"forward": sep_f, "backward": sep_b}
 

@@ -268,11 +268,12 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
                     cd[0] = pk(c0, c0);  cd[1] = pk(c1, c1);
                     hs[0] = hs[1] = hxs[0] = hxs[1] = 0ull;
                 }
-                f2 dxc[2], adx[2];
+                f2 dxc[2], adx[2], dxx[2];
 #pragma unroll
                 for (int cp = 0; cp < 2; ++cp) {
                     dxc[cp] = sub2(xcp[cp], px);
                     adx[cp] = mul2(A, dxc[cp]);
+                    dxx[cp] = mul2(dxc[cp], dxc[cp]);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {  // j = 2*row + column pair
@@ -292,9 +293,8 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
                     for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[c], G);
                     const f2 h = mul2(G, e);
                     hs[row] = add2(hs[row], h);
-                    const f2 hx = mul2(h, dx);
-                    hxs[row] = add2(hxs[row], hx);
-                    M[3] = fma2(hx, dx, M[3]);
+                    hxs[row] = fma2(h, dx, hxs[row]);
+                    M[3] = fma2(h, dxx[cp], M[3]);
 #pragma unroll
                     for (int c = 0; c < CT; ++c) E[c] = fma2(gterm[1 + c], e, E[c]);
                 }

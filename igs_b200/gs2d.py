@@ -341,13 +341,9 @@ class GaussianSplatting2D(nn.Module):
         per = 6 + self.output_dim
         gs_feature = self.proj(feature).unflatten(-1, (-1, per)).flatten(1, 2)
         b = gs_feature.shape[0]
-        positions, log_scales, rotations, logit_opacity, colors = gs_feature.split(
-            [2, 2, 1, 1, self.output_dim], dim=-1)
 
         if grid is None:
-            x_grid, y_grid = self.xy_grid(size, feature.device)
-            x_grid = x_grid[None].expand(b, -1, -1, -1)  # [B,1,H,W]; the kernels take strides
-            y_grid = y_grid[None].expand(b, -1, -1, -1)
+            x_grid, y_grid = _batched_grid(int(size[0]), int(size[1]), str(feature.device), b)  # [B,1,H,W], stride 0
         else:
             # [B,2,H,W] with the row coordinate first (reference :651-653)
             y_grid, x_grid = grid.split([1, 1], dim=1)
@@ -364,6 +360,8 @@ class GaussianSplatting2D(nn.Module):
             offset = pos_map if self.pos_map_offset else None
             return _SplatFromFeature.apply(gs_feature, offset, x_grid, y_grid, eps), gs_feature
 
+        positions, log_scales, rotations, logit_opacity, colors = gs_feature.split(
+            [2, 2, 1, 1, self.output_dim], dim=-1)
         if self.pos_map_offset:
             positions = positions + pos_map
         alphas = torch.ones_like(logit_opacity[..., 0])
@@ -371,6 +369,14 @@ class GaussianSplatting2D(nn.Module):
         rotations = rotations[..., 0]
         output = self.render(positions, colors, scales, rotations, alphas, x_grid, y_grid, eps, fused)
         return output, gs_feature
+
+
+@functools.lru_cache(maxsize=64)
+def _batched_grid(h, w, device, b):
+    """xy_grid(size) as the [B,1,H,W] stride-0 views the module's forward hands to the splat;
+    kept per (size, device, batch), so a training loop builds them once."""
+    x_grid, y_grid = GaussianSplatting2D.xy_grid((h, w), device)
+    return x_grid[None].expand(b, -1, -1, -1), y_grid[None].expand(b, -1, -1, -1)
 
 
 @functools.lru_cache(maxsize=64)

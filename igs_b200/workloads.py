@@ -48,6 +48,8 @@ CONFIGS = {
     # the image-compression regime at a larger gaussian count (reference: 2dgs_img_comp.py trains
     # tens of thousands of gaussians of scale ~e^-5.5 at 1024 px)
     "narrow64k": SplatConfig("narrow64k", 1, 65536, 1024, 1024, 3, 0.002, 0.006, seed=8),
+    # config 4 cut down (one batch element, a quarter of the gaussians) for profiler captures
+    "cfg4_small": SplatConfig("cfg4_small", 1, 16384, 512, 512, 16, 0.02, 0.20, normal_colors=True, seed=4),
     # one GPU's share of config 4 when its batch of 64 is spread over 8 GPUs
     "cfg4_b8": SplatConfig("cfg4_b8", 8, 65536, 512, 512, 16, 0.02, 0.20, normal_colors=True, seed=4),
 }
