@@ -36,7 +36,7 @@ if ROOT not in sys.path:
 # workloads (workload -> kernel -> bytes); None where no capture was taken
 NCU_DRAM_BYTES_PER_LAUNCH = {
     "cfg2": {"forward": 18.93e6 + 8.23e6, "backward": 31.38e6 + 8.05e6},
-    "cfg2_sep": {"forward": 6.90e6 + 8.56e6, "backward": 26.76e6 + 7.62e6},
+    "cfg2_sep": {"forward": 6.90e6 + 8.56e6, "backward": 26.76e6 + 1.99e6},
     "cfg2_small": {"forward": 3.46e6 + 0.01e6, "backward": 7.03e6},
     "cfg2_small_sep": {"forward": 0.98e6 + 0.02e6, "backward": 5.98e6},
 }
@@ -532,12 +532,26 @@ def run_b200(args):
     for _ in range(2):
         run_e2e(1)
     e2e_total = run_e2e(steps)
+    # how long one step's host->device copies take by themselves while every rank copies at
+    # once (they overlap the previous step's kernels unless they take longer than a step)
+    barrier()
+    ca, cb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for ev in free:
+        ev.record(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(copy_stream):
+        ca.record(copy_stream)
+    for i in range(4):
+        prefetch(i % 2)
+    with torch.cuda.stream(copy_stream):
+        cb.record(copy_stream)
+    barrier()
+    h2d_copy_ms = ca.elapsed_time(cb) / 4
 
     culling = None
     if isinstance(wl, SplatWorkload):
         culling = culling_report(args, wl, on_dev, _lib, torch)
 
-    total_ms = torch.tensor([sum(times), e2e_total, sum(times_plain)], dtype=torch.float64, device=dev)
+    total_ms = torch.tensor([sum(times), e2e_total, sum(times_plain), h2d_copy_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = total_ms.tolist()
@@ -624,6 +638,8 @@ def run_b200(args):
             "dtype": "f32", "data": "synthetic", "config": wl.config(world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": total_ms[1] / steps,
+                    "h2d_copy_ms_per_step": total_ms[3],
+                    "h2d_gbs_per_gpu": h2d / (total_ms[3] * 1e-3) / 1e9 if total_ms[3] > 0 else None,
                     "timing": "whole loop of `steps` steps incl. the first copy; the inputs of step k+1 are copied "
                               "on a second stream while step k computes"},
             "gpu_launches": launches,
