@@ -9,12 +9,14 @@
 //   Mxx = sum h*dx*dx               with  hs_r = sum_cols h,  hxs_r = sum_cols h*dx
 // so per pixel only hs, hxs and Mxx are updated, and the row-level products are formed
 // once per row pair.  The exponent shares its terms the same way as in the separable
-// forward (dx, A*dx, dx^2 per column pair; B2*dy, Cq*dy^2 per row).  Per gaussian x pixel that
-// is 12 FMA-pipe instructions + 1.5 per pixel of column terms instead of 22, at C = 3:
-//   s = A*dx + B2*dy; q = dx*s + Cq*dy^2              2      G = gS + sum_c gn_c*col_c   3
+// forward (dx, dx^2 per column pair; B2*dy, Cq*dy^2 per row).  Per gaussian x pixel that
+// is 12 FMA-pipe instructions + 1 per pixel of column terms instead of 22, at C = 3:
+//   s = A*dx + B2*dy; q = dx*s + Cq*dy^2  (two FMAs)  2      G = gS + sum_c gn_c*col_c   3
 //   h = G*e; hs += h; hxs += h*dx; Mxx += h*dx^2      4      E_c += gn_c*e               3
 // (dx^2 once per column pair and row pair costs half an instruction per pixel and saves one:
-// measured 4.41 -> 4.27 ms at B=16, N=8192, 256 x 256).
+// measured 4.41 -> 4.27 ms at B=16, N=8192, 256 x 256; forming A*dx + B2*dy as one FMA per pixel
+// instead of a shared A*dx plus an add per pixel saves another half and eight registers, at
+// the same time).
 #include "backward.cuh"
 
 namespace igs {
@@ -452,13 +454,12 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
                 --must;
                 ++visited;
             }
-            f2 dxc[GPT][2], adx[GPT][2], dxx[GPT][2];
+            f2 dxc[GPT][2], dxx[GPT][2];
 #pragma unroll
             for (int g = 0; g < GPT; ++g)
 #pragma unroll
                 for (int cp = 0; cp < 2; ++cp) {
                     dxc[g][cp] = sub2(xcp[cp], px[g]);
-                    adx[g][cp] = mul2(A[g], dxc[g][cp]);
                     dxx[g][cp] = mul2(dxc[g][cp], dxc[g][cp]);
                 }
 #pragma unroll
@@ -475,7 +476,7 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
 #pragma unroll
                 for (int g = 0; g < GPT; ++g) {
                     const f2 dx = dxc[g][cp];
-                    const f2 e = ex2_2(fma2(dx, add2(adx[g][cp], bd[g][row]), cd[g][row]));
+                    const f2 e = ex2_2(fma2(dx, fma2(A[g], dx, bd[g][row]), cd[g][row]));
                     f2 G = gterm[0];
 #pragma unroll
                     for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[g][c], G);

@@ -268,11 +268,10 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
                     cd[0] = pk(c0, c0);  cd[1] = pk(c1, c1);
                     hs[0] = hs[1] = hxs[0] = hxs[1] = 0ull;
                 }
-                f2 dxc[2], adx[2], dxx[2];
+                f2 dxc[2], dxx[2];
 #pragma unroll
                 for (int cp = 0; cp < 2; ++cp) {
                     dxc[cp] = sub2(xcp[cp], px);
-                    adx[cp] = mul2(A, dxc[cp]);
                     dxx[cp] = mul2(dxc[cp], dxc[cp]);
                 }
 #pragma unroll
@@ -287,7 +286,7 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
                     }
                     const int row = j >> 1, cp = j & 1;
                     const f2 dx = dxc[cp];
-                    const f2 e = ex2_2(fma2(dx, add2(adx[cp], bd[row]), cd[row]));
+                    const f2 e = ex2_2(fma2(dx, fma2(A, dx, bd[row]), cd[row]));
                     f2 G = gterm[0];
 #pragma unroll
                     for (int c = 0; c < CT; ++c) G = fma2(gterm[1 + c], col[c], G);
