@@ -699,7 +699,8 @@ def culling_report(args, wl, on_dev, _lib, torch):
         order = None
         if args.backward_sort != "off":  # the order the call layer would pass
             order = _lib.order_by_policy(_lib._shape_memo(x3.device, wl.B_local, wl.N_local, wl.cfg.H, wl.cfg.W),
-                                         on_dev["positions"], None, None, x3, y3, on_dev["scales"])
+                                         on_dev["positions"], None, None, x3, y3, on_dev["scales"], False,
+                                         on_dev["rotations"])
             if order is None:
                 order = _lib.spatial_order(on_dev["positions"], x3, y3)
         probe_bwd = _lib.backward("sr", on_dev["positions"], on_dev["scales"], on_dev["rotations"], None,

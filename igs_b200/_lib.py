@@ -355,11 +355,15 @@ class CallInfo:
     __slots__ = ("x3", "y3", "hints", "order", "shape", "grid")
 
 
-def prepare_call(x, y, pos, feat=None, pos_off=None, scales=None, log_scales=False):
+KEEP_ORDER = "keep"  # prepare_call(order=...): use the caller's order, or none at all, instead of the policy's
+
+
+def prepare_call(x, y, pos, feat=None, pos_off=None, scales=None, log_scales=False, rotations=None, order=None):
     """Everything a forward (and the backward after it) needs beyond the tensors: grid views,
     hints from what earlier calls learnt, and the processing order the set_backward_sort
     policy wants, if any.  pos [B,N,2], or None with feat [B,N,6+C] (+ pos_off); scales
-    [B,N,2] when the caller has them."""
+    [B,N,2] and rotations [B,N] when the caller has them.  order: None = by the policy; a
+    (KEEP_ORDER, tensor or None) pair = exactly that order, e.g. one kept from an earlier step."""
     _drain_reads()
     B, N = (pos if pos is not None else feat).shape[:2]
     info = CallInfo()
@@ -370,7 +374,11 @@ def prepare_call(x, y, pos, feat=None, pos_off=None, scales=None, log_scales=Fal
     if info.shape is not None:
         if info.shape.narrow is False and _BACKWARD_SORT != "on":
             info.hints |= HINT_WIDE_GAUSSIANS
-        info.order = order_by_policy(info.shape, pos, feat, pos_off, info.x3, info.y3, scales, log_scales)
+        if order is not None and order[0] == KEEP_ORDER:
+            info.order = order[1]
+        else:
+            info.order = order_by_policy(info.shape, pos, feat, pos_off, info.x3, info.y3, scales, log_scales,
+                                         rotations)
     return info
 
 
@@ -497,23 +505,38 @@ def set_backward_sort(mode: str) -> None:
 REACH_IN_SCALES = 13.43
 
 
-def _positions_for_ordering(pos, scales, x3, y3):
-    """Positions to sort by: the gaussians' own, except that every WIDE gaussian (box at least
-    three quarters of the sampled extent) is moved to one corner.  The stable sort then puts
-    all wide gaussians next to each other at one end of the order and the narrow ones in
-    spatial order behind them, so that a warp of the backward (a stage of the forward) holds
-    either gaussians that reach everything or neighbours that reach one small patch; a single
-    wide gaussian among narrow ones would make its whole warp visit every pixel.  Any
-    permutation gives the same gradients; this one lets the kernels skip the most."""
-    ex = (x3[:, 0, -1] - x3[:, 0, 0]).abs()
-    ey = (y3[:, -1, 0] - y3[:, 0, 0]).abs()
-    limit = 0.75 * torch.minimum(ex, ey) / (2 * REACH_IN_SCALES)   # [B]
-    wide = scales.abs().amax(-1) >= limit[:, None]                 # [B,N]
-    corner = torch.stack((x3[:, 0, 0], y3[:, 0, 0]), -1)           # [B,2]
-    return torch.where(wide[..., None], corner[:, None, :], pos)
+# From this many gaussian x pixel pairs per call on, the ordering looks at each axis by itself
+# (a dozen small tensor operations more, which only a long step hides).
+ORDER_PER_AXIS_MIN_EVALS = 2e10
 
 
-def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=False):
+def _positions_for_ordering(pos, scales, x3, y3, rotations=None):
+    """Positions to sort by: per axis, the centre of the gaussian's zero-weight box CLIPPED to
+    the sampled extent.  A narrow gaussian inside the image keeps its own centre; a box that
+    sticks out on one side is placed by how far it reaches in; a box that covers the whole
+    extent lands on the image's centre line, next to all others like it.  The stable sort along
+    the curve then gives a warp of the backward (a stage of the forward) gaussians whose
+    clipped boxes nearly coincide -- a patch, a vertical or horizontal strip, or everything --
+    where a single image-wide gaussian among narrow ones would make its whole warp visit
+    every pixel.  Any permutation gives the same gradients; this one lets the kernels skip
+    the most.  Without rotations (short steps) the larger scale stands in for both axes."""
+    x0, x1, y0, y1 = x3[:, 0, 0], x3[:, 0, -1], y3[:, 0, 0], y3[:, -1, 0]
+    xmin, xmax = torch.minimum(x0, x1)[:, None], torch.maximum(x0, x1)[:, None]
+    ymin, ymax = torch.minimum(y0, y1)[:, None], torch.maximum(y0, y1)[:, None]
+    sx2, sy2 = scales[..., 0] ** 2, scales[..., 1] ** 2
+    if rotations is not None:
+        c2 = torch.cos(rotations) ** 2
+        hx = REACH_IN_SCALES * torch.sqrt(c2 * sx2 + (1 - c2) * sy2)   # box half-widths (pack.cu)
+        hy = REACH_IN_SCALES * torch.sqrt((1 - c2) * sx2 + c2 * sy2)
+    else:
+        hx = hy = REACH_IN_SCALES * torch.sqrt(torch.maximum(sx2, sy2))
+    px, py = pos[..., 0], pos[..., 1]
+    ux = 0.5 * (torch.maximum(px - hx, xmin) + torch.minimum(px + hx, xmax))
+    uy = 0.5 * (torch.maximum(py - hy, ymin) + torch.minimum(py + hy, ymax))
+    return torch.stack((ux, uy), -1)
+
+
+def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=False, rotations=None):
     """The processing order one forward + backward should use under the set_backward_sort
     policy, or None.  shape: the call's _ShapeMemo; pos [B,N,2], or None with feat
     [B,N,6+C] (+ pos_off) to take the positions from; scales [B,N,2] if at hand (lets the
@@ -531,10 +554,13 @@ def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=F
             return None
     if pos is None:
         pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off
-        scales = torch.exp(feat[..., 2:4])
+        scales, log_scales, rotations = feat[..., 2:4], True, feat[..., 4]
     if scales is not None:
         scales = scales.detach()
-        pos = _positions_for_ordering(pos.detach(), torch.exp(scales) if log_scales else scales, x3, y3)
+        if rotations is not None and B * N * H * W < ORDER_PER_AXIS_MIN_EVALS:
+            rotations = None
+        pos = _positions_for_ordering(pos.detach(), torch.exp(scales) if log_scales else scales, x3, y3,
+                                      rotations.detach() if rotations is not None else None)
     return spatial_order(pos.contiguous(), x3, y3)
 
 

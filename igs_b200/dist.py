@@ -73,10 +73,10 @@ class CudaSplatBackend:
     `prepare` returned for the step: grid views, hints and the memos of the call layer."""
 
     @staticmethod
-    def prepare(x, y, pos, scales=None):
+    def prepare(x, y, pos, scales=None, rotations=None):
         from . import _lib
 
-        return _lib.prepare_call(x, y, pos, scales=scales)
+        return _lib.prepare_call(x, y, pos, scales=scales, rotations=rotations)
 
     @staticmethod
     def forward_sums(pos, col, sc, rot, al, x3, y3, eps, info=None):
@@ -112,7 +112,7 @@ class _ShardedSplat(torch.autograd.Function):
         pos, col, sc, rot, al = (t.contiguous() for t in (positions, colors, scales, rotations, alphas))
         check_consistent_once((B, col.shape[2], x.shape[2], x.shape[3]), group)
         if hasattr(backend, "prepare"):
-            info = backend.prepare(x, y, pos, sc)
+            info = backend.prepare(x, y, pos, sc, rot)
             sums = backend.forward_sums(pos, col, sc, rot, al, info.x3, info.y3, eps, info=info)
         else:
             info = None

@@ -62,6 +62,12 @@ class ImageFitter(nn.Module):
         self.color = nn.Parameter(color.contiguous())
         self.register_buffer("alphas", torch.ones(1, num_gaussians))
         self._grids = {}
+        # The spatial processing order of the gaussians (narrow gaussians only, see
+        # igs_b200.set_backward_sort) is kept for this many fused steps before it is computed
+        # again: the gaussians move a little per step, any permutation gives the same gradients,
+        # and an eager step is bound by host time that the ordering adds to.
+        self.order_every = 8
+        self._kept_order = None  # (steps since it was computed, (image size, policy), order or None)
 
     def grids(self, size):
         """[1,1,H,W] sample coordinates of ``xy_grid`` on the parameters' device, built once
@@ -87,7 +93,16 @@ class ImageFitter(nn.Module):
 
         x_grid, y_grid = self.grids(target.shape[-2:])
         pos, ls, rot, col = (p.detach() for p in (self.position, self.log_scale, self.rotation, self.color))
-        info = _lib.prepare_call(x_grid, y_grid, pos, scales=ls, log_scales=True)
+        size = (tuple(target.shape[-2:]), _lib._BACKWARD_SORT)  # (an order is only good for one image size and policy)
+        kept = self._kept_order
+        if (kept is not None and kept[1] == size and kept[0] < self.order_every
+                and not torch.cuda.is_current_stream_capturing()):
+            # (a captured graph computes the order in every replay: that costs no host time)
+            info = _lib.prepare_call(x_grid, y_grid, pos, order=(_lib.KEEP_ORDER, kept[2]))
+            self._kept_order = (kept[0] + 1, size, kept[2])
+        else:
+            info = _lib.prepare_call(x_grid, y_grid, pos, scales=ls, log_scales=True, rotations=rot)
+            self._kept_order = (1, size, info.order)
         loss, g, _ = _lib.render_mse(pos, ls, rot, None, col, info.x3, info.y3, target, EPS,
                                      gs2d._GRAD_MODES[gs2d.get_grad_mode()], log_scales=True, order=info.order,
                                      hints=info.hints, info=info)

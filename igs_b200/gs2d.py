@@ -207,7 +207,7 @@ class _SplatFromScaleRotation(torch.autograd.Function):
         pos, col, sc, rot, al = (t.contiguous() for t in (positions, colors, scales, rotations, alphas))
         # grid views, hints and one spatial order per step (if the policy wants one), shared by
         # forward and backward
-        info = _lib.prepare_call(x, y, pos, scales=sc)
+        info = _lib.prepare_call(x, y, pos, scales=sc, rotations=rot)
         out, wsum = _lib.forward("sr", pos, sc, rot, None, al, col, info.x3, info.y3, eps, order=info.order,
                                  hints=info.hints, info=info)
         _save_call(ctx, info, x, y, pos, col, sc, rot, al, wsum, out)
