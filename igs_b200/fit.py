@@ -102,7 +102,8 @@ class ImageFitter(nn.Module):
             self._kept_order = (kept[0] + 1, size, kept[2])
         else:
             info = _lib.prepare_call(x_grid, y_grid, pos, scales=ls, log_scales=True, rotations=rot)
-            self._kept_order = (1, size, info.order)
+            # (only an actual order is kept: while the policy wants none, asking again costs nothing)
+            self._kept_order = (1, size, info.order) if info.order is not None else None
         loss, g, _ = _lib.render_mse(pos, ls, rot, None, col, info.x3, info.y3, target, EPS,
                                      gs2d._GRAD_MODES[gs2d.get_grad_mode()], log_scales=True, order=info.order,
                                      hints=info.hints, info=info)
