@@ -673,8 +673,9 @@ def set_culling(on: bool) -> None:
     forget_what_calls_learnt()
 
 
-def profile_enable(on: bool) -> None:
-    check("igs_profile_enable", load().igs_profile_enable(int(bool(on))))
+def profile_enable(on) -> None:
+    """False / 0: off; True / 1: every kernel; 2: the forward and backward splat kernels only."""
+    check("igs_profile_enable", load().igs_profile_enable(int(on)))
 
 
 def profile_reset() -> None:

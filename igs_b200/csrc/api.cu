@@ -49,7 +49,8 @@ static cudaEvent_t take_event(int dev) {
 }
 
 KernelTimer::KernelTimer(int id_, cudaStream_t s) : id(id_), stream(s) {
-    if (!g_profile_on.load(std::memory_order_relaxed)) return;
+    const int mode = g_profile_on.load(std::memory_order_relaxed);
+    if (!mode || (mode == 2 && id_ != K_FORWARD && id_ != K_BACKWARD)) return;
     if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
     start = take_event(dev);
     stop = take_event(dev);
@@ -1072,7 +1073,7 @@ int igs_set_culling(int on) {
 }
 
 int igs_profile_enable(int on) {
-    g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+    g_profile_on.store(on == 2 ? 2 : (on ? 1 : 0), std::memory_order_relaxed);
     return IGS_OK;
 }
 
