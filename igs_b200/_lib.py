@@ -303,6 +303,7 @@ def forget_what_calls_learnt() -> None:
     with _memo_lock:
         _shape_memos.clear()
         _grid_memos.clear()
+        _extents.clear()
 
 
 def grid_for_call(x, y, B):
@@ -520,20 +521,35 @@ def _positions_for_ordering(pos, scales, x3, y3, rotations=None):
     where a single image-wide gaussian among narrow ones would make its whole warp visit
     every pixel.  Any permutation gives the same gradients; this one lets the kernels skip
     the most.  Without rotations (short steps) the larger scale stands in for both axes."""
-    x0, x1, y0, y1 = x3[:, 0, 0], x3[:, 0, -1], y3[:, 0, 0], y3[:, -1, 0]
-    xmin, xmax = torch.minimum(x0, x1)[:, None], torch.maximum(x0, x1)[:, None]
-    ymin, ymax = torch.minimum(y0, y1)[:, None], torch.maximum(y0, y1)[:, None]
-    sx2, sy2 = scales[..., 0] ** 2, scales[..., 1] ** 2
+    lo, hi = _sampled_extent(x3, y3)  # [B,1,2] each
     if rotations is not None:
-        c2 = torch.cos(rotations) ** 2
-        hx = REACH_IN_SCALES * torch.sqrt(c2 * sx2 + (1 - c2) * sy2)   # box half-widths (pack.cu)
-        hy = REACH_IN_SCALES * torch.sqrt((1 - c2) * sx2 + c2 * sy2)
+        c2 = (torch.cos(rotations) ** 2)[..., None]
+        var = scales * scales
+        cov = c2 * var + (1 - c2) * var.flip(-1)   # covariance along x and along y
+        half = REACH_IN_SCALES * torch.sqrt(cov)   # box half-widths (pack.cu)
     else:
-        hx = hy = REACH_IN_SCALES * torch.sqrt(torch.maximum(sx2, sy2))
-    px, py = pos[..., 0], pos[..., 1]
-    ux = 0.5 * (torch.maximum(px - hx, xmin) + torch.minimum(px + hx, xmax))
-    uy = 0.5 * (torch.maximum(py - hy, ymin) + torch.minimum(py + hy, ymax))
-    return torch.stack((ux, uy), -1)
+        half = REACH_IN_SCALES * scales.abs().amax(-1, keepdim=True)
+    return 0.5 * (torch.maximum(pos - half, lo) + torch.minimum(pos + half, hi))
+
+
+_extents = {}  # (x pointer, y pointer, strides, shape) -> (lo, hi); a wrong hit could only cost skipping
+
+
+def _sampled_extent(x3, y3):
+    """Lower and upper corner of the sampled extent per batch element, [B,1,2] each; kept per
+    grid so that a training loop computes them once."""
+    key = (x3.data_ptr(), y3.data_ptr(), x3.stride(), y3.stride(), tuple(x3.shape), x3._version, y3._version)
+    got = _extents.get(key)
+    if got is None or torch.cuda.is_current_stream_capturing():
+        xa, xb, ya, yb = x3[:, 0, 0], x3[:, 0, -1], y3[:, 0, 0], y3[:, -1, 0]
+        lo = torch.stack((torch.minimum(xa, xb), torch.minimum(ya, yb)), -1)[:, None, :]
+        hi = torch.stack((torch.maximum(xa, xb), torch.maximum(ya, yb)), -1)[:, None, :]
+        if torch.cuda.is_current_stream_capturing():
+            return lo, hi
+        if len(_extents) > 64:
+            _extents.clear()
+        got = _extents[key] = (lo, hi)
+    return got
 
 
 def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=False, rotations=None):
