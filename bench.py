@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--backward-sort", choices=["auto", "on", "off"], default="auto",
                     help="spatial processing order of the gaussians (results are the same bits)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--warped-grid", action="store_true",
+                    help="move one sample point off the pixel grid: the grid is then not separable and the "
+                         "general kernels (arbitrary sample points) run instead of the separable ones")
     ap.add_argument("--no-sharded-leg", action="store_true",
                     help="N > 1, default workload: skip the extra single-image gaussian-sharded leg")
     ap.add_argument("--sharded-steps", type=int, default=20)
@@ -433,6 +436,11 @@ def run_b200(args):
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
     wl = make_workload(args.workload, rank, world, dev, torch)
+    if args.warped_grid:
+        if "x" not in wl.host:
+            raise SystemExit("--warped-grid applies to the workloads that pass their own sample grid")
+        wl.host["x"][0, 0, 0, 0] += 1e-3
+        wl.separable_grid = False
     host = wl.host
     on_dev = {k: v.to(dev) for k, v in host.items()}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

@@ -141,11 +141,11 @@ def test_culling_with_strongly_anisotropic_rotated_gaussians(level):
         assert torch.equal(g_on[k], g_off[k]), k
 
 
-@pytest.mark.parametrize("C", [8, 16, 17])
+@pytest.mark.parametrize("C", [5, 8, 12, 16, 17])
 def test_many_channels_culling_changes_no_bit_and_matches_the_oracle(C):
-    """8 and 16 channels run the row-streaming separable backward (two gaussians per packed
-    operand) and its skipping instantiation; 17 channels are a chunk of 16 plus one and take
-    the general kernels.  Odd image sizes, a ragged gaussian count, a few image-wide gaussians
+    """5 to 8 and 9 to 16 channels run the row-streaming separable backward (two gaussians per
+    packed operand; instantiated for 8 and 16, zero-padded in between) and its skipping
+    instantiation; 17 channels are a chunk of 16 plus one and take the general kernels.  Odd image sizes, a ragged gaussian count, a few image-wide gaussians
     among the narrow ones.  Culling on / off: the same bits; and the culled result against the
     fp64 oracle."""
     from oracle import splat_oracle as so
