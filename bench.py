@@ -486,8 +486,12 @@ def run_b200(args):
                 staged[i][k].copy_(v, non_blocking=True)
             ready[i].record(copy_stream)
 
+    d2h_stream = torch.cuda.Stream(dev)
+
     def run_e2e(n):
-        """n pipelined steps; returns the device time of the whole loop in ms."""
+        """n pipelined steps; returns the device time of the whole loop in ms.  The gradients
+        and the loss of step k go back to pinned host memory on a third stream while step k+1
+        computes; the clock stops when the last of them has arrived."""
         main = torch.cuda.current_stream(dev)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -502,10 +506,18 @@ def run_b200(args):
             flush.zero_()
             main.wait_event(ready[i])
             loss, grads = wl.step(staged[i])
-            for h, g in zip(grads_host, grads):
-                h.copy_(g, non_blocking=True)
-            loss_host.copy_(loss.detach(), non_blocking=True)
+            computed = torch.cuda.Event()
+            computed.record(main)
             free[i].record(main)
+            with torch.cuda.stream(d2h_stream):
+                d2h_stream.wait_event(computed)
+                for h, g in zip(grads_host, grads):
+                    h.copy_(g, non_blocking=True)
+                    g.record_stream(d2h_stream)
+                loss_d = loss.detach()
+                loss_host.copy_(loss_d, non_blocking=True)
+                loss_d.record_stream(d2h_stream)
+        main.wait_stream(d2h_stream)
         end.record(main)
         barrier()
         return begin.elapsed_time(end)
@@ -663,8 +675,9 @@ def run_b200(args):
                     "ms_per_step": total_ms[1] / steps,
                     "h2d_copy_ms_per_step": total_ms[3],
                     "h2d_gbs_per_gpu": h2d / (total_ms[3] * 1e-3) / 1e9 if total_ms[3] > 0 else None,
-                    "timing": "whole loop of `steps` steps incl. the first copy; the inputs of step k+1 are copied "
-                              "on a second stream while step k computes"},
+                    "timing": "whole loop of `steps` steps incl. the first copy in and the last copy out; the inputs "
+                              "of step k+1 are copied on a second stream and the results of step k-1 on a third "
+                              "while step k computes"},
             "gpu_launches": launches,
             "launches_per_step": launches / steps,
             "ms_per_step_without_kernel_events": total_ms[2] / steps,
