@@ -647,6 +647,9 @@ def run_b200(args):
                     "executed_instr_per_eval": executed[name],
                     "executed_frac": ev_rank * share[name] * executed[name] / per_pass_s / fp32_peak,
                     "mix_ceiling_frac": None if sep[name] else mix_ceiling[name] / fp32_peak,
+                    # f32x2 FMAs with three distinct register operands (every accumulation is one)
+                    # issue at this fraction of the FFMA-only rate: the register file's limit
+                    "three_operand_ceiling_frac": probes["fp32_packed_3operand_lane_instr_per_s"] / fp32_peak,
                     "grid": "separable (xy_grid)" if sep[name] else "general",
                     "peak_source": "measured live: FFMA-only kernel, best of scalar and f32x2 (igs_b200.probes)",
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload + suffix, {}).get(name)

@@ -41,7 +41,8 @@ def build(force: bool = False) -> str:
 
 def rates(device_index: int) -> dict:
     """Measured rates on one device: lane-instructions per second of the FMA pipe (scalar,
-    packed, forward mix 11 FMA : 2 ex2, backward mix 22 : 2) and ex2 results per second."""
+    packed with shared operands, packed with three distinct register operands, forward mix
+    11 FMA : 2 ex2, backward mix 22 : 2) and ex2 results per second."""
     lib = ctypes.CDLL(build())
     dbl = ctypes.POINTER(ctypes.c_double)
     lib.igs_probe_fp32_rate.argtypes = [ctypes.c_int, ctypes.c_int, dbl]
@@ -58,6 +59,9 @@ def rates(device_index: int) -> dict:
     return {
         "fp32_scalar_lane_instr_per_s": call(lib.igs_probe_fp32_rate, device_index, 0),
         "fp32_packed_lane_instr_per_s": call(lib.igs_probe_fp32_rate, device_index, 1),
+        # f32x2 FMAs with three different register operands each (what an accumulation a*b + v
+        # is): the register file, not the pipe, sets this rate
+        "fp32_packed_3operand_lane_instr_per_s": call(lib.igs_probe_fp32_rate, device_index, 2),
         "ex2_results_per_s": call(lib.igs_probe_ex2_rate, device_index),
         "fp32_forward_mix_lane_instr_per_s": call(lib.igs_probe_mix_rate, device_index, 0),
         "fp32_backward_mix_lane_instr_per_s": call(lib.igs_probe_mix_rate, device_index, 1),

@@ -47,6 +47,32 @@ __global__ void __launch_bounds__(PROBE_THREADS) probe_ffma2_kernel(float* sink,
     if (sink && s == 123.456f) sink[0] = s;
 }
 
+// f32x2 FMAs whose three operands are three different register pairs (a*b + v with a, b, v
+// distinct per chain), as in the splat kernels' accumulations; probe_ffma2_kernel multiplies
+// by and adds the same two values in every instruction, which the operand reuse cache serves.
+__global__ void __launch_bounds__(PROBE_THREADS) probe_ffma2_3op_kernel(float* sink, float m, float c) {
+    f2 v[PROBE_CHAINS], a[PROBE_CHAINS], b[PROBE_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) {
+        v[k] = pk((float)(threadIdx.x + k), (float)k);
+        a[k] = pk(m + k * 1e-6f, m - k * 1e-6f);
+        b[k] = pk(c + k * 1e-6f, c - k * 1e-6f);
+    }
+#pragma unroll 8
+    for (int it = 0; it < PROBE_ITERS; ++it) {
+#pragma unroll
+        for (int k = 0; k < PROBE_CHAINS; ++k) v[k] = fma2(a[k], b[k], v[k]);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < PROBE_CHAINS; ++k) {
+        float lo, hi;
+        upk(v[k], lo, hi);
+        s += lo + hi;
+    }
+    if (sink && s == 123.456f) sink[0] = s;
+}
+
 __global__ void __launch_bounds__(PROBE_THREADS) probe_ex2_kernel(float* sink, float c) {
     float v[PROBE_CHAINS];
 #pragma unroll
@@ -142,7 +168,9 @@ int igs_probe_fp32_rate(int device, int packed, double* lane_instr_per_s) {
     cudaError_t err;
     const double t = best_time(
         [&] {
-            if (packed)
+            if (packed == 2)
+                probe_ffma2_3op_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
+            else if (packed)
                 probe_ffma2_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
             else
                 probe_ffma_kernel<<<blocks, PROBE_THREADS>>>(nullptr, 0.999f, 0.001f);
