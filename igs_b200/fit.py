@@ -112,6 +112,69 @@ class ImageFitter(nn.Module):
         return loss
 
 
+class ShardedImageFitter(ImageFitter):
+    """An ``ImageFitter`` whose gaussians are spread over the ranks of a process group: the
+    one-image case on several GPUs (one process per GPU).
+
+    Every rank builds the same initial gaussians and keeps the contiguous range
+    ``igs_b200.dist.gaussian_range`` gives it; ``forward`` renders through
+    ``sharded_gaussian_splatting_2d`` (one all-reduce of the [1,C+1,H,W] sums, every rank gets
+    the whole image), the loss is computed from the whole image on every rank, and backward
+    and the optimiser touch the rank's own gaussians only: no gradient or parameter ever
+    crosses ranks.  ``gathered()`` collects the parameters of all ranks, e.g. for saving.
+    ``backend``: the three device calls (default: the CUDA library).
+    """
+
+    def __init__(self, num_gaussians, channels=3, image=None, init_log_scale=-3.0, aspect=1.0, group=None,
+                 backend=None):
+        import torch.distributed as tdist
+
+        from .dist import gaussian_range
+
+        super().__init__(num_gaussians, channels, image, init_log_scale, aspect)
+        if not tdist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised (launch with torchrun)")
+        self.group, self.backend = group, backend
+        lo, hi = gaussian_range(self.num_gaussians, tdist.get_world_size(group), tdist.get_rank(group))
+        self.range = (lo, hi)
+        for name in ("position", "log_scale", "rotation", "color"):
+            setattr(self, name, nn.Parameter(getattr(self, name).detach()[:, lo:hi].clone()))
+        self.alphas = self.alphas[:, lo:hi].clone()
+
+    def forward(self, size):
+        from .dist import sharded_gaussian_splatting_2d
+
+        x_grid, y_grid = self.grids(size)
+        return sharded_gaussian_splatting_2d(self.position, self.color, torch.exp(self.log_scale) + EPS,
+                                             self.rotation, self.alphas, x_grid, y_grid, group=self.group,
+                                             backend=self.backend)
+
+    def mse_loss_and_backward(self, target):
+        raise NotImplementedError("the one-call step renders all gaussians on one GPU; the sharded fitter "
+                                  "goes through forward() and autograd")
+
+    @torch.no_grad()
+    def gathered(self):
+        """{name: [1,N,...]} of position, log_scale, rotation and color over all ranks (a
+        collective: every rank must call it)."""
+        import torch.distributed as tdist
+
+        from .dist import gaussian_range
+
+        world = tdist.get_world_size(self.group)
+        ranges = [gaussian_range(self.num_gaussians, world, r) for r in range(world)]
+        longest = max(hi - lo for lo, hi in ranges)
+        res = {}
+        for name in ("position", "log_scale", "rotation", "color"):
+            mine = getattr(self, name).detach()
+            padded = mine.new_zeros((1, longest) + tuple(mine.shape[2:]))  # ranges differ by at most one
+            padded[:, : mine.shape[1]] = mine
+            parts = [torch.empty_like(padded) for _ in range(world)]
+            tdist.all_gather(parts, padded, group=self.group)
+            res[name] = torch.cat([part[:, : hi - lo] for part, (lo, hi) in zip(parts, ranges)], 1)
+        return res
+
+
 class _MSELoss(torch.autograd.Function):
     """F.mse_loss(out, target) for contiguous fp32 CUDA tensors through the library's two
     loss kernels (three launches forward + backward where the torch ops take about eight)."""
@@ -137,7 +200,7 @@ def mse_loss(out, target):
 
 
 def _fusable(model, target):
-    return (isinstance(model, ImageFitter) and target.is_cuda and target.dtype == torch.float32
+    return (type(model) is ImageFitter and target.is_cuda and target.dtype == torch.float32
             and target.is_contiguous() and target.dim() == 4 and target.shape[0] == 1
             and target.shape[1] == model.color.shape[-1])
 
@@ -206,6 +269,8 @@ def fit(model, target, steps, lr=1e-2, graph=True, schedule=None, betas=(0.9, 0.
 
         with gs2d.grad_mode(grad_mode):
             return fit(model, target, steps, lr, graph, schedule, betas, None)
+    if isinstance(model, ShardedImageFitter):
+        graph = False  # (a step holds a collective: issued eagerly, never captured)
     schedule = schedule or [(1, steps)]
     opt = torch.optim.Adam(model.parameters(), lr=lr, betas=betas, capturable=bool(graph))
     for p in model.parameters():  # Adam must see gradients from the first (captured) step on

@@ -210,6 +210,102 @@ def test_dead_peer_gives_an_error_not_a_hang():
     assert res[1] == "RuntimeError" and res[0] != "no error", res
 
 
+def _fit_target(H, W):
+    yy, xx = torch.meshgrid(torch.linspace(-1, 1, H), torch.linspace(-1, 1, W), indexing="ij")
+    return torch.stack([0.5 + 0.4 * torch.sin(3 * xx + c) * torch.cos(2 * yy - c) for c in range(3)])[None]
+
+
+def _worker_sharded_fit(rank, world, port, backend, q):
+    """Three Adam steps of the gaussian-sharded per-image fit: the loss of every step and the
+    parameters of all ranks afterwards."""
+    from igs_b200 import fit
+
+    try:
+        _init(rank, world, port, backend)
+        dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+        tgt = _fit_target(18, 22).to(dev)
+        model = fit.ShardedImageFitter(53, channels=3, image=tgt.cpu(), init_log_scale=-1.5,
+                                       backend=None if backend == "nccl" else OracleBackend).to(dev)
+        opt = torch.optim.Adam(model.parameters(), lr=2e-2)
+        losses = []
+        for _ in range(3):
+            opt.zero_grad(set_to_none=True)
+            loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        full = {k: v.cpu().numpy() for k, v in model.gathered().items()}
+        q.put((rank, model.range, losses, full, None))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # noqa: BLE001 - reported to the parent
+        q.put((rank, None, None, None, repr(exc)))
+
+
+def _run_sharded_fit(world, backend):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_sharded_fit, args=(r, world, port, backend, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for r in res:
+        assert r[4] is None, f"rank {r[0]} failed: {r[4]}"
+    return sorted(res, key=lambda r: r[0])
+
+
+def _check_sharded_fit(two, one):
+    (_, rng1, losses1, full1, _), = one
+    assert rng1 == (0, 53) and [r[1] for r in two] == [(0, 27), (27, 53)]
+    for r in two:
+        assert np.allclose(r[2], losses1, rtol=1e-5, atol=0), (r[2], losses1)
+        for k, v in r[3].items():
+            assert v.shape == full1[k].shape
+            assert_close(v, full1[k], 1e-5, f"{k} after 3 steps, seen from rank {r[0]}")
+    assert losses1[2] < losses1[0]
+
+
+def test_sharded_image_fitter_two_ranks_equal_one_gloo():
+    """The fit over two ranks walks the same path as over one: per-step loss and, after three
+    Adam steps, every parameter (gathered) agree."""
+    _check_sharded_fit(_run_sharded_fit(2, "gloo"), _run_sharded_fit(1, "gloo"))
+
+
+@pytest.mark.gpu
+def test_sharded_image_fitter_on_one_gpu_follows_the_plain_fitter():
+    """A process group of one rank: the sharded fitter (sums, all-reduce, normalise) against
+    ImageFitter through autograd, same three Adam steps."""
+    from igs_b200 import fit
+
+    (_, rng, losses, full, _), = _run_sharded_fit(1, "nccl")
+    dev = torch.device("cuda", 0)
+    tgt = _fit_target(18, 22).to(dev)
+    model = fit.ImageFitter(53, channels=3, image=tgt.cpu(), init_log_scale=-1.5).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=2e-2)
+    plain = []
+    for _ in range(3):
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
+        loss.backward()
+        opt.step()
+        plain.append(float(loss))
+    assert rng == (0, 53)
+    assert np.allclose(losses, plain, rtol=1e-4, atol=0), (losses, plain)
+    for k, v in full.items():
+        assert_close(v, getattr(model, k).detach().cpu().numpy(), 1e-4, f"{k} after 3 steps")
+
+
+@pytest.mark.gpu
+def test_sharded_image_fitter_two_gpus_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    _check_sharded_fit(_run_sharded_fit(2, "nccl"), _run_sharded_fit(1, "nccl"))
+
+
 @pytest.mark.gpu
 def test_gaussian_sharded_two_gpus_nccl():
     if torch.cuda.device_count() < 2:
