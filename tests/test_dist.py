@@ -215,6 +215,16 @@ def _fit_target(H, W):
     return torch.stack([0.5 + 0.4 * torch.sin(3 * xx + c) * torch.cos(2 * yy - c) for c in range(3)])[None]
 
 
+def _spread(model):
+    """Makes the start anisotropic and rotated (a function of each gaussian's own position, so
+    every split of the gaussians gets the same values).  With the fitter's isotropic start the
+    rotation gradient is rounding noise, which Adam's normalisation would turn into steps of
+    the size of the learning rate with a sign that depends on the summation order."""
+    with torch.no_grad():
+        model.log_scale.add_(0.4 * torch.sin(5.0 * model.position))
+        model.rotation.add_(2.0 * model.position[..., 0] - model.position[..., 1])
+
+
 def _worker_sharded_fit(rank, world, port, backend, q):
     """Three Adam steps of the gaussian-sharded per-image fit: the loss of every step and the
     parameters of all ranks afterwards."""
@@ -226,6 +236,7 @@ def _worker_sharded_fit(rank, world, port, backend, q):
         tgt = _fit_target(18, 22).to(dev)
         model = fit.ShardedImageFitter(53, channels=3, image=tgt.cpu(), init_log_scale=-1.5,
                                        backend=None if backend == "nccl" else OracleBackend).to(dev)
+        _spread(model)
         opt = torch.optim.Adam(model.parameters(), lr=2e-2)
         losses = []
         for _ in range(3):
@@ -233,7 +244,7 @@ def _worker_sharded_fit(rank, world, port, backend, q):
             loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
             loss.backward()
             opt.step()
-            losses.append(float(loss))
+            losses.append(float(loss.detach()))
         full = {k: v.cpu().numpy() for k, v in model.gathered().items()}
         q.put((rank, model.range, losses, full, None))
         dist.barrier()
@@ -257,21 +268,21 @@ def _run_sharded_fit(world, backend):
     return sorted(res, key=lambda r: r[0])
 
 
-def _check_sharded_fit(two, one):
+def _check_sharded_fit(two, one, tol):
     (_, rng1, losses1, full1, _), = one
     assert rng1 == (0, 53) and [r[1] for r in two] == [(0, 27), (27, 53)]
     for r in two:
-        assert np.allclose(r[2], losses1, rtol=1e-5, atol=0), (r[2], losses1)
+        assert np.allclose(r[2], losses1, rtol=tol, atol=0), (r[2], losses1)
         for k, v in r[3].items():
             assert v.shape == full1[k].shape
-            assert_close(v, full1[k], 1e-5, f"{k} after 3 steps, seen from rank {r[0]}")
+            assert_close(v, full1[k], tol, f"{k} after 3 steps, seen from rank {r[0]}")
     assert losses1[2] < losses1[0]
 
 
 def test_sharded_image_fitter_two_ranks_equal_one_gloo():
     """The fit over two ranks walks the same path as over one: per-step loss and, after three
     Adam steps, every parameter (gathered) agree."""
-    _check_sharded_fit(_run_sharded_fit(2, "gloo"), _run_sharded_fit(1, "gloo"))
+    _check_sharded_fit(_run_sharded_fit(2, "gloo"), _run_sharded_fit(1, "gloo"), 1e-5)
 
 
 @pytest.mark.gpu
@@ -284,6 +295,7 @@ def test_sharded_image_fitter_on_one_gpu_follows_the_plain_fitter():
     dev = torch.device("cuda", 0)
     tgt = _fit_target(18, 22).to(dev)
     model = fit.ImageFitter(53, channels=3, image=tgt.cpu(), init_log_scale=-1.5).to(dev)
+    _spread(model)
     opt = torch.optim.Adam(model.parameters(), lr=2e-2)
     plain = []
     for _ in range(3):
@@ -291,7 +303,7 @@ def test_sharded_image_fitter_on_one_gpu_follows_the_plain_fitter():
         loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
         loss.backward()
         opt.step()
-        plain.append(float(loss))
+        plain.append(float(loss.detach()))
     assert rng == (0, 53)
     assert np.allclose(losses, plain, rtol=1e-4, atol=0), (losses, plain)
     for k, v in full.items():
@@ -303,7 +315,7 @@ def test_sharded_image_fitter_two_gpus_nccl():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    _check_sharded_fit(_run_sharded_fit(2, "nccl"), _run_sharded_fit(1, "nccl"))
+    _check_sharded_fit(_run_sharded_fit(2, "nccl"), _run_sharded_fit(1, "nccl"), 1e-4)
 
 
 @pytest.mark.gpu
