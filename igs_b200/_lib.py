@@ -30,7 +30,7 @@ _lib = None
 
 _F = ctypes.POINTER(ctypes.c_float)
 _I64 = ctypes.POINTER(ctypes.c_int64)
-_vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+_vp, _i, _f, _sz, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_int64
 
 # name -> (restype, argtypes); mirrors include/igs_b200.h one to one
 SIGNATURES = {
@@ -56,6 +56,8 @@ SIGNATURES = {
     "igs_set_culling": (_i, [_i]),
     "igs_spatial_order_workspace_bytes": (_sz, [_i, _i]),
     "igs_spatial_order": (_i, [_vp, _vp, _I64, _vp, _I64] + [_i] * 4 + [_vp, _vp, _sz, _i, _vp]),
+    "igs_spatial_order_boxes": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _vp, _i64, _vp, _I64, _vp, _I64] + [_i] * 4
+                                + [_vp, _vp, _sz, _i, _vp]),
     "igs_read_narrow_count": (_i, [_vp, _i, _vp, _vp]),
     "igs_read_executed": (_i, [_vp, _i, _vp, ctypes.POINTER(ctypes.c_ulonglong)]),
     "igs_render_mse_workspace_bytes": (_i, [_i] * 6 + [ctypes.POINTER(_sz)]),
@@ -303,7 +305,6 @@ def forget_what_calls_learnt() -> None:
     with _memo_lock:
         _shape_memos.clear()
         _grid_memos.clear()
-        _extents.clear()
 
 
 def grid_for_call(x, y, B):
@@ -482,10 +483,46 @@ def spatial_order(pos, x3, y3):
     return order
 
 
+def _rows(t, width):
+    """(tensor to keep alive, floats from one gaussian's entry to the next) for reading `width`
+    consecutive floats per gaussian where they lie: a slice t = full[..., a:a+width] (or
+    full[..., a]) of a contiguous [B,N,K] tensor is taken in place, anything else is made
+    contiguous first."""
+    B, N = t.shape[:2]
+    st = t.stride()
+    inner_ok = t.dim() == 2 or st[2] == 1
+    if inner_ok and (N <= 1 or st[1] >= width) and (B <= 1 or st[0] == N * st[1]):
+        return t, (st[1] if N > 1 else width)
+    return t.contiguous(), width
+
+
+def spatial_order_boxes(pos, x3, y3, scales=None, log_scales=False, rotations=None, pos_off=None):
+    """[B,N] int32 permutation along the Hilbert curve of, per gaussian, the centre of its
+    zero-weight box clipped to the sampled extent (igs_spatial_order_boxes): pos [B,N,2],
+    scales [B,N,2] (their logarithms with log_scales), rotations [B,N] or None (then the larger
+    scale stands in for both axes), pos_off [B,N,2] or None (added to pos).  The tensors may be
+    slices of one [B,N,K] tensor; they are read in place."""
+    dev = pos.device
+    B, N, _ = pos.shape
+    _, H, W = x3.shape
+    lib = load()
+    ws = _workspace(int(lib.igs_spatial_order_workspace_bytes(B, N)), dev)
+    order = torch.empty(B, N, dtype=torch.int32, device=dev)
+    pos, ps = _rows(pos.detach(), 2)
+    sc, ss = _rows(scales.detach(), 2) if scales is not None else (None, 2)
+    rot, rs = _rows(rotations.detach(), 1) if rotations is not None and scales is not None else (None, 1)
+    off = pos_off.detach().contiguous() if pos_off is not None else None
+    check("igs_spatial_order_boxes",
+          lib.igs_spatial_order_boxes(_ptr(pos), ps, _ptr(off), _ptr(sc), ss, 1 if log_scales else 0, _ptr(rot), rs,
+                                      _ptr(x3), _strides3(x3), _ptr(y3), _strides3(y3), B, N, H, W, _ptr(order),
+                                      _ptr(ws), ws.numel(), dev.index, _stream(dev)))
+    return order
+
+
 _BACKWARD_SORT = "auto"
-# Below this many gaussian x pixel pairs per call, "auto" does not order: the half dozen
-# extra launches cost an eager step more host time than the skipping saves on the device
-# (measured: 2.7e8 pairs, 4096 gaussians at 256x256: 0.61 ms ordered against 0.51 ms; 1.1e9
+# Below this many gaussian x pixel pairs per call, "auto" does not order: the four extra
+# launches cost an eager step more host time than the skipping saves on the device
+# (measured: 2.7e8 pairs, 4096 gaussians at 256x256: 0.50 ms ordered against 0.44 ms; 1.1e9
 # pairs, 4096 at 512x512: 0.42 against 0.88 ms).
 AUTO_ORDER_MIN_EVALS = 5e8
 
@@ -499,57 +536,6 @@ def set_backward_sort(mode: str) -> None:
         raise ValueError("mode must be 'auto', 'on' or 'off'")
     _BACKWARD_SORT = mode
     forget_what_calls_learnt()
-
-
-# A gaussian's zero-weight box reaches at most this many of its larger scale to either side
-# of its centre (sqrt(130 / (0.5 log2 e)), see pack.cu).
-REACH_IN_SCALES = 13.43
-
-
-# From this many gaussian x pixel pairs per call on, the ordering looks at each axis by itself
-# (a dozen small tensor operations more, which only a long step hides).
-ORDER_PER_AXIS_MIN_EVALS = 2e10
-
-
-def _positions_for_ordering(pos, scales, x3, y3, rotations=None):
-    """Positions to sort by: per axis, the centre of the gaussian's zero-weight box CLIPPED to
-    the sampled extent.  A narrow gaussian inside the image keeps its own centre; a box that
-    sticks out on one side is placed by how far it reaches in; a box that covers the whole
-    extent lands on the image's centre line, next to all others like it.  The stable sort along
-    the curve then gives a warp of the backward (a stage of the forward) gaussians whose
-    clipped boxes nearly coincide -- a patch, a vertical or horizontal strip, or everything --
-    where a single image-wide gaussian among narrow ones would make its whole warp visit
-    every pixel.  Any permutation gives the same gradients; this one lets the kernels skip
-    the most.  Without rotations (short steps) the larger scale stands in for both axes."""
-    lo, hi = _sampled_extent(x3, y3)  # [B,1,2] each
-    if rotations is not None:
-        c2 = (torch.cos(rotations) ** 2)[..., None]
-        var = scales * scales
-        cov = c2 * var + (1 - c2) * var.flip(-1)   # covariance along x and along y
-        half = REACH_IN_SCALES * torch.sqrt(cov)   # box half-widths (pack.cu)
-    else:
-        half = REACH_IN_SCALES * scales.abs().amax(-1, keepdim=True)
-    return 0.5 * (torch.maximum(pos - half, lo) + torch.minimum(pos + half, hi))
-
-
-_extents = {}  # (x pointer, y pointer, strides, shape) -> (lo, hi); a wrong hit could only cost skipping
-
-
-def _sampled_extent(x3, y3):
-    """Lower and upper corner of the sampled extent per batch element, [B,1,2] each; kept per
-    grid so that a training loop computes them once."""
-    key = (x3.data_ptr(), y3.data_ptr(), x3.stride(), y3.stride(), tuple(x3.shape), x3._version, y3._version)
-    got = _extents.get(key)
-    if got is None or torch.cuda.is_current_stream_capturing():
-        xa, xb, ya, yb = x3[:, 0, 0], x3[:, 0, -1], y3[:, 0, 0], y3[:, -1, 0]
-        lo = torch.stack((torch.minimum(xa, xb), torch.minimum(ya, yb)), -1)[:, None, :]
-        hi = torch.stack((torch.maximum(xa, xb), torch.maximum(ya, yb)), -1)[:, None, :]
-        if torch.cuda.is_current_stream_capturing():
-            return lo, hi
-        if len(_extents) > 64:
-            _extents.clear()
-        got = _extents[key] = (lo, hi)
-    return got
 
 
 def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=False, rotations=None):
@@ -569,15 +555,8 @@ def order_by_policy(shape, pos, feat, pos_off, x3, y3, scales=None, log_scales=F
         if B * N * H * W < AUTO_ORDER_MIN_EVALS and not torch.cuda.is_current_stream_capturing():
             return None
     if pos is None:
-        pos = feat[..., :2] if pos_off is None else feat[..., :2] + pos_off
-        scales, log_scales, rotations = feat[..., 2:4], True, feat[..., 4]
-    if scales is not None:
-        scales = scales.detach()
-        if rotations is not None and B * N * H * W < ORDER_PER_AXIS_MIN_EVALS:
-            rotations = None
-        pos = _positions_for_ordering(pos.detach(), torch.exp(scales) if log_scales else scales, x3, y3,
-                                      rotations.detach() if rotations is not None else None)
-    return spatial_order(pos.contiguous(), x3, y3)
+        return spatial_order_boxes(feat[..., :2], x3, y3, feat[..., 2:4], True, feat[..., 4], pos_off)
+    return spatial_order_boxes(pos, x3, y3, scales, log_scales, rotations if scales is not None else None)
 
 
 def backward(kind, pos, s0, s1, s2, alphas, colors, x3, y3, wsum, out, gout, eps, grad_mode, want_xy,

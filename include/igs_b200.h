@@ -280,6 +280,27 @@ int igs_spatial_order(const float* positions, const float* x, const int64_t* x_s
                       void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
+ * The same sort on another key: per axis the centre of the gaussian's zero-weight box
+ * clipped to the sampled extent.  A narrow gaussian inside the image keeps its own centre, a
+ * box that sticks out on one side is placed by how far it reaches in, and a box that covers
+ * the whole extent lands on the image's centre line next to all others like it, so that one
+ * image-wide gaussian does not sit in a warp of narrow ones and make it visit every pixel.
+ * The parameters are read where they lie, in the layout of the parameter-level or of the
+ * feature-level entry points: gaussian i (over B*N) has its centre at
+ * positions[i * position_stride .. +1] (plus position_offsets[2i .. +1] when that is not
+ * NULL), its scales (logarithms of them with log_scales = 1) at scales[i * scale_stride ..
+ * +1] and its angle at rotations[i * rotation_stride].  rotations = NULL: the larger scale
+ * stands in for both axes; scales = NULL: igs_spatial_order.  Same workspace, same
+ * determinism.  No counterpart in the reference.
+ */
+int igs_spatial_order_boxes(const float* positions, int64_t position_stride, const float* position_offsets,
+                            const float* scales, int64_t scale_stride, int log_scales,
+                            const float* rotations, int64_t rotation_stride, const float* x,
+                            const int64_t* x_strides, const float* y, const int64_t* y_strides, int B, int N,
+                            int H, int W, int* order, void* workspace, size_t workspace_bytes, int device,
+                            void* stream);
+
+/*
  * Asynchronous read of the narrow-gaussian count the last forward or backward on this
  * workspace left: the number of gaussians (over the whole batch) whose zero-weight box
  * covers less than three quarters of the sampled extent in x or y.  The copy is queued on

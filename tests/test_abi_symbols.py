@@ -61,7 +61,13 @@ def test_added_entry_points_validate_arguments_without_gpu():
     assert lib.igs_spatial_order(one, one, strides, one, strides, 1, 8, 4, 4, one, None, 0, 0, None) == -2
     assert lib.igs_spatial_order(one, one, strides, one, strides, 1, 8, 4, 4, one, one, 16, 0, None) == -2
     assert lib.igs_spatial_order(one, one, strides, one, strides, 0, 8, 4, 4, one, one, 16, 0, None) == 0  # nothing to do
-    assert lib.igs_spatial_order_workspace_bytes(2, 3000) >= 2 * 4096 * 4 + 2 * 3 * 4096 * 4 + 2 * 3000 * 2
+    assert lib.igs_spatial_order_workspace_bytes(2, 3000) >= 2 * 3 * 4096 * 4 + 2 * 3000 * 2
+    boxes = lambda *head: lib.igs_spatial_order_boxes(*head, one, strides, one, strides, 1, 8, 4, 4, one, one, 1 << 20,
+                                                      0, None)
+    assert boxes(one, 1, None, one, 2, 0, one, 1) == -1   # a centre is two floats
+    assert boxes(one, 2, None, one, 1, 0, one, 1) == -1   # so are the scales
+    assert boxes(one, 2, None, None, 2, 0, one, 1) == -1  # rotations without scales
+    assert boxes(None, 2, None, one, 2, 0, one, 1) == -1
     assert lib.igs_mse_loss(None, one, 10, one, one, 4096, 0, None) == -1
     assert lib.igs_mse_loss(one, one, 0, one, one, 4096, 0, None) == -1
     assert lib.igs_mse_loss(one, one, 10, one, one, 16, 0, None) == -2

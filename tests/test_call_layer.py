@@ -69,29 +69,6 @@ def test_grid_argument_errors(lib):
         lib.grid_for_call(x, y, 3)
 
 
-def test_ordering_key_is_the_clipped_box_centre(lib):
-    B, H, W = 1, 16, 16
-    x, y = _grid(B, H, W)
-    x3, y3 = x[:, 0], y[:, 0]
-    R = lib.REACH_IN_SCALES
-    pos = torch.tensor([[[0.3, -0.2], [0.3, -0.2], [-0.9, 0.0], [0.5, 0.5], [0.0, 0.9]]])
-    sc = torch.tensor([[[0.01, 0.01],     # narrow: keeps its centre
-                        [0.5, 0.5],       # covers the whole extent: the image's centre
-                        [0.04, 0.01],     # sticks out on the left: placed by how far it reaches in
-                        [0.01, 0.5],      # a vertical strip (rotation 0): x kept, y = centre line
-                        [0.01, 0.5]]])    # the same shape turned by 90 degrees: a horizontal strip
-    rot = torch.tensor([[0.0, 0.0, 0.0, 0.0, math.pi / 2]])
-    u = lib._positions_for_ordering(pos, sc, x3, y3, rot)[0]
-    assert torch.allclose(u[0], pos[0, 0])
-    assert torch.allclose(u[1], torch.zeros(2), atol=1e-6)
-    assert abs(float(u[2, 0]) - 0.5 * (-1.0 + (-0.9 + R * 0.04))) < 1e-5 and abs(float(u[2, 1])) < 1e-6
-    assert abs(float(u[3, 0]) - 0.5) < 1e-6 and abs(float(u[3, 1])) < 1e-6
-    assert abs(float(u[4, 0])) < 1e-5 and abs(float(u[4, 1]) - 0.5 * ((0.9 - R * 0.01) + 1.0)) < 1e-5
-    # without rotations the larger scale stands in for both axes
-    u2 = lib._positions_for_ordering(pos, sc, x3, y3)[0]
-    assert torch.allclose(u2[0], pos[0, 0]) and torch.allclose(u2[3], torch.zeros(2), atol=1e-6)
-
-
 def test_policy_decides_without_launching(lib):
     B, N, H, W = 1, 64, 16, 16
     x, y = _grid(B, H, W)

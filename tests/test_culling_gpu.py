@@ -199,6 +199,78 @@ def _backward_with(d, gout, x, y, order):
     return res
 
 
+def test_box_order_sorts_by_the_clipped_box_centre():
+    """igs_spatial_order_boxes against igs_spatial_order on the key it documents: per axis the
+    centre of the zero-weight box clipped to the sampled extent.  Hand-made gaussians whose
+    keys are known, then random ones with the key recomputed by torch (also from a
+    feature-layout tensor read in place, with logarithmic scales and a position offset)."""
+    import math
+
+    from igs_b200 import _lib
+    from igs_b200.gs2d import GaussianSplatting2D
+
+    dev = torch.device("cuda", 0)
+    R = 13.43  # box half-width in standard deviations of the axis
+    xg, yg = GaussianSplatting2D.xy_grid((16, 16), dev)
+    x3, y3 = xg, yg  # [1,16,16] views; the extent is [-1,1] x [-1,1]
+    pos = torch.tensor([[[0.3, -0.2], [0.3, -0.2], [-0.9, 0.1], [0.5, 0.5], [0.1, 0.9]]], device=dev)
+    sc = torch.tensor([[[0.01, 0.01],     # narrow: keeps its centre
+                        [0.5, 0.5],       # covers the whole extent: the image's centre
+                        [0.04, 0.01],     # sticks out on the left: placed by how far it reaches in
+                        [0.01, 0.5],      # a vertical strip (rotation 0): x kept, y = centre line
+                        [0.01, 0.5]]], device=dev)  # the same shape turned by 90 degrees: a horizontal strip
+    rot = torch.tensor([[0.0, 0.0, 0.0, 0.0, math.pi / 2]], device=dev)
+    key = torch.tensor([[[0.3, -0.2], [0.0, 0.0], [0.5 * (-1.0 + (-0.9 + R * 0.04)), 0.1], [0.5, 0.0],
+                         [0.0, 0.5 * ((0.9 - R * 0.01) + 1.0)]]], device=dev)
+    assert torch.equal(_lib.spatial_order_boxes(pos, x3, y3, sc, False, rot), _lib.spatial_order(key, x3, y3))
+    # without rotations the larger scale stands in for both axes: the strips become image-wide
+    key2 = key.clone()
+    key2[0, 3] = 0.0
+    key2[0, 4] = 0.0
+    assert torch.equal(_lib.spatial_order_boxes(pos, x3, y3, sc), _lib.spatial_order(key2, x3, y3))
+    # without scales: the centres
+    assert torch.equal(_lib.spatial_order_boxes(pos, x3, y3), _lib.spatial_order(pos, x3, y3))
+
+    # random gaussians; the lattice has 64 cells per axis, so keys are kept away from cell
+    # boundaries (where one rounding decides the cell) by drawing until they are
+    gen = torch.Generator().manual_seed(33)
+    B, N, K = 2, 3000, 9
+    xg, yg = GaussianSplatting2D.xy_grid((48, 80), dev)
+    x3, y3 = xg.expand(B, -1, -1), yg.expand(B, -1, -1)
+    feat = torch.zeros(B, N, K)
+    feat[..., :2] = torch.rand(B, N, 2, generator=gen) * 2.4 - 1.2
+    feat[..., 2:4] = torch.rand(B, N, 2, generator=gen) * 4.0 - 5.0  # log scales: e^-5 .. e^-1
+    feat[..., 4] = torch.rand(B, N, generator=gen) * 6.28
+    off = (torch.rand(B, N, 2, generator=gen) - 0.5) * 0.1
+    lo = torch.tensor([float(xg.min()), float(yg.min())])
+    hi = torch.tensor([float(xg.max()), float(yg.max())])
+
+    def keys(f):
+        p, s, r = f[..., :2].double() + off.double(), torch.exp(f[..., 2:4].double()), f[..., 4].double()
+        c2 = (torch.cos(r) ** 2)[..., None]
+        half = R * torch.sqrt(c2 * s * s + (1 - c2) * (s * s).flip(-1))
+        return 0.5 * (torch.maximum(p - half, lo.double()) + torch.minimum(p + half, hi.double()))
+
+    mid = 0.5 * (lo.double() + hi.double())
+    for _ in range(20):
+        k = keys(feat)
+        cell = (k - lo) / (hi - lo) * 64.0
+        # (a box that covers an axis sits exactly on the centre line in either computation)
+        near = (((cell - cell.round()).abs() < 1e-3) & (k != mid)).any(-1)
+        if not bool(near.any()):
+            break
+        feat[..., :2][near] += 0.01
+    assert not bool(near.any())
+    feat_d, off_d = feat.to(dev), off.to(dev)
+    want = _lib.spatial_order(keys(feat).float().to(dev), x3, y3)
+    got = _lib.spatial_order_boxes(feat_d[..., :2], x3, y3, feat_d[..., 2:4], True, feat_d[..., 4], off_d)
+    assert torch.equal(got, want)
+    # the same parameters as separate contiguous tensors with plain scales
+    got2 = _lib.spatial_order_boxes((feat_d[..., :2] + off_d).contiguous(), x3, y3,
+                                    torch.exp(feat_d[..., 2:4]).contiguous(), False, feat_d[..., 4].contiguous())
+    assert torch.equal(got2, want)
+
+
 def test_spatial_order_is_a_permutation_with_neighbours_adjacent():
     from igs_b200 import _lib
 
