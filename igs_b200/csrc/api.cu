@@ -307,9 +307,9 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
     if (p->row_kernel) off = align_up(off + (size_t)B * H * sizeof(float), 256);
     p->off_part = off;
     off = align_up(off + (size_t)n_slab_max * B * p->planes * (size_t)N * sizeof(float), 256);
-    p->part_bytes = (size_t)p->n_slab * B * p->planes * (size_t)N * sizeof(float);
     p->off_tasks = off;
     p->task_capacity = 0;
+    p->off_slab_range = 0;
     if (p->sep_ok && !p->row_kernel) {  // (the task-queue kernel exists for up to 4 channels)
         const long long groups32 = ((long long)N + 31) / 32;
         const long long cap = (long long)B * groups32 * n_slab_max;
@@ -317,6 +317,8 @@ int plan_backward(int B, int N, int H, int W, int C, int device, BwdPlan* p, boo
             p->task_capacity = (int)cap;
             off = align_up(off + (size_t)cap * sizeof(int4), 256);
             off = align_up(off + (size_t)B * groups32 * sizeof(int4), 256);
+            p->off_slab_range = off;  // [B, N] int: the slabs that hold sums of a slot
+            off = align_up(off + (size_t)B * N * sizeof(int), 256);
         }
     }
     p->bytes = off;
@@ -662,6 +664,7 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         if (e != cudaSuccess) return (int)e;
     }
 
+    const int* slab_range = nullptr;  // set by the ordered skipping path
     for (int k = 0; k < p.ch.n; ++k) {
         BwdArgs ba;
         std::memset(&ba, 0, sizeof(ba));
@@ -686,16 +689,17 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
         ba.c0 = p.ch.c0[k];
         ba.cr = p.ch.cr[k];
         ba.planes = p.planes;
+        ba.n_slab = p.n_slab;
         ba.moment_plane0 = N_MOMENTS * k;
         ba.color_plane0 = N_MOMENTS * p.ch.n;
         if (grid_kind != GRID_GENERAL) {
             const bool queued = order && p.task_capacity > 0 && ba.cull_sel;
             if (queued) {
                 // The ordered skipping path writes partial sums only for the (group, slab) pairs
-                // that have a task; the others are exact zeros.  Cleared before ANY of the
-                // kernels below runs: whichever one the device selects writes after this.
-                e = cudaMemsetAsync(ba.part, 0, p.part_bytes, st);
-                if (e != cudaSuccess) return (int)e;
+                // that have a task and leaves, per gaussian, the range of slabs to add up
+                // (all of them when the device selects another kernel).
+                ba.slab_range = reinterpret_cast<int*>(ws + p.off_slab_range);
+                slab_range = ba.slab_range;
             }
             e = launch_backward_chunk(p.ch.ct[k], true, false, ba, p, st);
             if (e != cudaSuccess) return (int)e;
@@ -725,6 +729,8 @@ static int backward_impl(int kind, const float* pos, const float* s0, const floa
     FinalizeArgs fa;
     std::memset(&fa, 0, sizeof(fa));
     fa.part = reinterpret_cast<const float*>(ws + p.off_part);
+    fa.slab_range = slab_range;
+    fa.order = order;
     fa.pos = pos;
     fa.shape0 = s0;
     fa.shape1 = s1;

@@ -261,7 +261,10 @@ __global__ void __launch_bounds__(BwdCfg<CT, GPT>::THREADS, BwdCfg<CT, GPT>::MIN
 #pragma unroll
     for (int g = 0; g < GPT; ++g) {
         if (n[g] >= a.N) continue;
-        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n[g];
+        // (the partial sums are laid out by slot, not by gaussian: recomputed here, not kept)
+        const int slot = a.order ? blockIdx.x * Cfg::GAUSS_PER_CTA + tid * GPT + g
+                                 : blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + slot;
 #pragma unroll
         for (int k = 0; k < N_MOMENTS; ++k) {
             float lo, hi;
@@ -363,20 +366,38 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_kernel(FinalizeArgs a) {
     extern __shared__ float s_sum[];  // [planes][FIN_G]
     const int lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
     const long long total = (long long)a.B * a.N;
-    const long long i_raw = (long long)blockIdx.x * FIN_G + lane;  // over B*N
-    const long long i = i_raw < total ? i_raw : total - 1;
-    const long long b = i / a.N, n = i - b * a.N;
+    // The partial sums are laid out by processing slot (coalesced for the kernels that wrote
+    // them and for the loads below); the order maps a slot to its gaussian.
+    const long long t_raw = (long long)blockIdx.x * FIN_G + lane;  // over B*N slots
+    const long long t = t_raw < total ? t_raw : total - 1;
+    const long long b = t / a.N, slot = t - b * a.N;
     const long long plane = a.N;
     const long long slab_stride = (long long)a.B * a.planes * plane;
-    for (int p = wq; p < a.planes; p += FIN_THREADS / 32) {
-        const float* src = a.part + (b * a.planes + p) * plane + n;
-        float acc = 0.f;
+    // the slabs that hold sums of this slot: all of them, or (ordered skipping path) the
+    // range its group had tasks for; the others were never written and stand for exact zeros
+    if (a.slab_range) {
+        const int r = a.slab_range[t];
+        const int s_lo = min(r & 0xffff, a.n_slab), s_hi = min(r >> 16, a.n_slab);
+        for (int p = wq; p < a.planes; p += FIN_THREADS / 32) {
+            const float* src = a.part + (b * a.planes + p) * plane + slot;
+            float acc = 0.f;
+#pragma unroll 4
+            for (int s = s_lo; s < s_hi; ++s) acc += src[(long long)s * slab_stride];
+            s_sum[p * FIN_G + lane] = acc;
+        }
+    } else {
+        for (int p = wq; p < a.planes; p += FIN_THREADS / 32) {
+            const float* src = a.part + (b * a.planes + p) * plane + slot;
+            float acc = 0.f;
 #pragma unroll 8
-        for (int s = 0; s < a.n_slab; ++s) acc += src[(long long)s * slab_stride];
-        s_sum[p * FIN_G + lane] = acc;
+            for (int s = 0; s < a.n_slab; ++s) acc += src[(long long)s * slab_stride];
+            s_sum[p * FIN_G + lane] = acc;
+        }
     }
     __syncthreads();
-    if (wq != 0 || i_raw >= total) return;
+    long long n = a.order ? (long long)a.order[t] : slot;
+    if (wq != 0 || t_raw >= total || n < 0 || n >= a.N) return;  // (an entry that is no index: nothing to write)
+    const long long i = b * a.N + n;
     float M[N_MOMENTS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int q = 0; q < a.n_chunks; ++q)
 #pragma unroll

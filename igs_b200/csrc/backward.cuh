@@ -33,7 +33,7 @@ struct BwdArgs {
     const float* prec;    // records of this chunk
     const float* axes;    // row-streaming kernel (backward_row.cu): y[b, h], [B, H]
     const int* order;     // [B, N] permutation: processing slot -> gaussian index, or nullptr
-    float* part;          // [n_slab, B, planes, N]
+    float* part;          // [n_slab, B, planes, N], N running over processing slots
     int* status;
     // Selection on the device (nullptr = run unconditionally): a kernel returns at once
     // unless the word picks it.
@@ -42,6 +42,7 @@ struct BwdArgs {
     // task list of the ordered skipping path (backward_warp.cu); nullptr elsewhere
     int4* tasks;        // [task_capacity]: {batch element, group of 32 slots, slab, -}
     int4* group_rect;   // [B, ceil(N/32)]: rows lo..hi and column blocks lo..hi the group's box meets
+    int* slab_range;    // [B, N]: first slab | (last slab + 1) << 16 that hold partial sums of the slot
     int* task_count;    // tasks on the list
     int* task_next;     // next task to hand out
     int task_capacity;
@@ -49,6 +50,7 @@ struct BwdArgs {
     const int* grid_word;  //   bit 1 of the grid word clear) -> skipping / plain separable kernel
     long long npairs, pairs_per_slab;
     int nrp, ncb, rp_per_slab;  // separable: row pairs, blocks per row pair, row pairs per slab
+    int n_slab;                 // slabs of the partition in use
     int B, N, C;
     int c0, cr;
     int planes;
@@ -59,6 +61,8 @@ struct BwdArgs {
 struct FinalizeArgs {
     ParamLayout lay;    // strides of the parameter arrays AND of their gradient arrays
     const float* part;  // [n_slab, B, planes, N]
+    const int* slab_range;  // nullptr: every slab holds partial sums; else per slot, as in BwdArgs
+    const int* order;       // nullptr, or [B, N]: the gaussian of every slot
     const float* pos;
     const float* shape0;  // scales | cov_inv_00
     const float* shape1;  // rotations | cov_inv_01

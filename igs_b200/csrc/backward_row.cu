@@ -132,10 +132,11 @@ __global__ void __launch_bounds__(BwdRowCfg<CT>::THREADS, BwdRowCfg<CT>::MIN_CTA
 
     // ---- this thread's two gaussians (lanes lo, hi of every f32x2) ----
     int n[2];
+    const int slot0 = blockIdx.x * Cfg::GAUSS_PER_CTA + tid * 2;  // the partial sums are laid out by slot
     float gv[2][8], cv[2][CT];
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
-        const int slot = blockIdx.x * Cfg::GAUSS_PER_CTA + tid * 2 + g;
+        const int slot = slot0 + g;
         n[g] = slot < a.N ? (a.order ? a.order[(long long)b * a.N + slot] : slot) : a.N;
         if ((unsigned)n[g] > (unsigned)a.N) n[g] = a.N;  // an entry that is no index: the slot stays empty
         const int nn = n[g] < a.N ? n[g] : a.N - 1;
@@ -401,16 +402,16 @@ __global__ void __launch_bounds__(BwdRowCfg<CT>::THREADS, BwdRowCfg<CT>::MIN_CTA
     for (int k = 0; k < N_MOMENTS; ++k) {
         float lo, hi;
         upk(M[k], lo, hi);
-        if (n[0] < a.N) dst[(long long)(a.moment_plane0 + k) * a.N + n[0]] = lo;
-        if (n[1] < a.N) dst[(long long)(a.moment_plane0 + k) * a.N + n[1]] = hi;
+        if (n[0] < a.N) dst[(long long)(a.moment_plane0 + k) * a.N + slot0] = lo;
+        if (n[1] < a.N) dst[(long long)(a.moment_plane0 + k) * a.N + slot0 + 1] = hi;
     }
 #pragma unroll
     for (int c = 0; c < CT; ++c) {
         if (c < a.cr) {
             float lo, hi;
             upk(E[c], lo, hi);
-            if (n[0] < a.N) dst[(long long)(a.color_plane0 + a.c0 + c) * a.N + n[0]] = lo;
-            if (n[1] < a.N) dst[(long long)(a.color_plane0 + a.c0 + c) * a.N + n[1]] = hi;
+            if (n[0] < a.N) dst[(long long)(a.color_plane0 + a.c0 + c) * a.N + slot0] = lo;
+            if (n[1] < a.N) dst[(long long)(a.color_plane0 + a.c0 + c) * a.N + slot0 + 1] = hi;
         }
     }
 }

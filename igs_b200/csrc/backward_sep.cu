@@ -506,7 +506,10 @@ __global__ void __launch_bounds__(BwdSepCfg<CT>::THREADS, BwdSepCfg<CT>::MIN_CTA
 #pragma unroll
     for (int g = 0; g < GPT; ++g) {
         if (n[g] >= a.N) continue;
-        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n[g];
+        // (the partial sums are laid out by slot, not by gaussian: recomputed here, not kept)
+        const int slot = a.order ? blockIdx.x * Cfg::GAUSS_PER_CTA + tid * GPT + g
+                                 : blockIdx.x * Cfg::GAUSS_PER_CTA + g * T + tid;
+        float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + slot;
 #pragma unroll
         for (int k = 0; k < N_MOMENTS; ++k) {
             float lo, hi;

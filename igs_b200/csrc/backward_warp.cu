@@ -16,8 +16,10 @@
 //                      off the list until it is empty: streams the task's rectangle through
 //                      two private stages with private mbarriers and writes the partial
 //                      sums of its 32 gaussians for that slab
-// (Group, slab) pairs that are not on the list contribute exact zeros: the partial sums are
-// cleared before the tasks run.
+// (Group, slab) pairs that are not on the list contribute exact zeros and their partial sums
+// are never written: warp_task_kernel leaves, per slot, the range of slabs its group has
+// tasks for, and finalize_kernel adds up those only (the sums that are left out are exact
+// zeros, so the result's bits do not change).
 //
 // Why a list: with one CTA per (group, slab) pair four fifths of the CTAs found nothing to
 // do, and an SM held 12.8 of its 20 possible warps on average; a warp that pulls tasks
@@ -64,7 +66,6 @@ __device__ __forceinline__ bool warp_path_selected(const BwdArgs& a) {
 // One warp per group: group g of batch element b holds the slots 32 g .. 32 g + 31.
 __global__ void __launch_bounds__(128) warp_task_kernel(BwdArgs a, int rs) {
     constexpr unsigned FULL = 0xffffffffu;
-    if (!warp_path_selected(a)) return;
     const int lane = threadIdx.x & 31;
     const int group = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), b = blockIdx.y;
     const int n_groups = (a.N + 31) / 32;
@@ -73,6 +74,11 @@ __global__ void __launch_bounds__(128) warp_task_kernel(BwdArgs a, int rs) {
     const int slot = group * 32 + lane;
     int n = slot < a.N ? (a.order ? a.order[(long long)b * a.N + slot] : slot) : a.N;
     if ((unsigned)n > (unsigned)a.N) n = a.N;
+    if (!warp_path_selected(a)) {
+        // another kernel does the work and fills every slab
+        if (slot < a.N) a.slab_range[(long long)b * a.N + slot] = a.n_slab << 16;
+        return;
+    }
     float u[4] = {INFINITY, -INFINITY, INFINITY, -INFINITY};  // x0, x1, y0, y1 of the group's box
     bool open_box = false;                                    // a NaN or infinite box: no restriction
     if (n < a.N) {
@@ -118,8 +124,12 @@ __global__ void __launch_bounds__(128) warp_task_kernel(BwdArgs a, int rs) {
             chi = max(chi, __shfl_xor_sync(FULL, chi, d));
         }
     }
-    if (hi < lo || chi < clo) return;  // the group reaches no pixel
+    if (hi < lo || chi < clo) {  // the group reaches no pixel: no task, no slab to add up
+        if (slot < a.N) a.slab_range[(long long)b * a.N + slot] = 0;
+        return;
+    }
     const int s0 = lo / a.rp_per_slab, s1 = hi / a.rp_per_slab;
+    if (slot < a.N) a.slab_range[(long long)b * a.N + slot] = s0 | ((s1 + 1) << 16);
     int base = 0;
     if (lane == 0) {
         a.group_rect[(long long)b * n_groups + group] = make_int4(lo, hi, clo, chi);
@@ -309,7 +319,7 @@ __global__ void __launch_bounds__(BwdWarpCfg<CT>::THREADS, BwdWarpCfg<CT>::MIN_C
         it += (unsigned)n_chunks;
 
         if (n < a.N) {
-            float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + n;
+            float* dst = a.part + ((long long)slab * a.B + b) * a.planes * (long long)a.N + slot;  // by slot
 #pragma unroll
             for (int k = 0; k < N_MOMENTS; ++k) {
                 float lo, hi;
@@ -350,9 +360,9 @@ static cudaError_t launch_queue_one(const BwdArgs& a, int n_ctas, cudaStream_t s
 }
 
 // The skipping backward for calls that pass a processing order (needs a.cull_sel, a.grid_word,
-// a.tasks, a.group_rect, a.task_count, a.task_next; the partial sums must have been cleared).
+// a.tasks, a.group_rect, a.task_count, a.task_next, a.slab_range).
 cudaError_t launch_backward_warp_chunk(int ct, const BwdArgs& a, const BwdPlan& p, int sm_count, cudaStream_t s) {
-    if (!a.cull_sel || !a.grid_word || !a.tasks || !a.group_rect || !a.task_count || !a.task_next)
+    if (!a.cull_sel || !a.grid_word || !a.tasks || !a.group_rect || !a.task_count || !a.task_next || !a.slab_range)
         return cudaErrorInvalidValue;
     (void)p;
     const int n_groups = (a.N + 31) / 32;

@@ -55,8 +55,8 @@ struct BwdPlan {
     size_t off_axes;       // row-streaming kernel: y per row, [B][H]
     size_t off_part;       // [n_slab][B][planes][N]
     size_t off_tasks;      // ordered skipping path: [task_capacity] int4, then [B][ceil(N/32)] int4
+    size_t off_slab_range; //   and [B][N] int (valid when task_capacity > 0)
     int task_capacity;     // B * ceil(N/32) * (most slabs either partition has); 0 without separable kernels
-    size_t part_bytes;     // size of the partial sums of the partition in use
     size_t bytes;
 };
 
