@@ -73,8 +73,12 @@ __global__ void __launch_bounds__(MSE_THREADS) mse_grad_kernel(const float* __re
 // same expressions, in the same order, as reduce_normalize_kernel, mse_grad_kernel and
 // pixel_terms_sep_kernel, so that the fused and the unfused path agree to the last bit in
 // everything but the order in which the loss is added up.
+// VEC: the image width is a multiple of four and every plane starts on a 16-byte boundary, so a
+// thread's four pixels of a row are one 16-byte load or store per plane.
+template <bool VEC>
 __global__ void __launch_bounds__(LOSS_TERMS_THREADS) loss_terms_sep_kernel(LossTermArgs a) {
     extern __shared__ __align__(16) float s_rec[];  // [blockDim.x][record floats], then 8 floats for the block sum
+    constexpr int CMAX = 4;  // channels of a chunk the separable backward takes
     const int rs = bwd_sep_rec_floats(a.ct), pf = bwd_sep_pair_floats(a.ct);
     const long long per_b = (long long)a.nrp * a.ncb;
     const long long total = (long long)a.B * per_b;
@@ -98,32 +102,94 @@ __global__ void __launch_bounds__(LOSS_TERMS_THREADS) loss_terms_sep_kernel(Loss
     reinterpret_cast<float4*>(rec)[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
     reinterpret_cast<float4*>(rec)[1] = make_float4(yv[0], yv[1], 0.f, 0.f);
 
+    // four pixels of one row of one plane (columns past the end repeat the last one)
+    auto load4 = [&](const float* plane, long long row_off, float (&v)[4]) {
+        if constexpr (VEC) {
+            const float4 t = *reinterpret_cast<const float4*>(plane + row_off + w0);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] = plane[row_off + min(w0 + q, a.W - 1)];
+        }
+    };
+    auto store4 = [&](float* plane, long long row_off, const float (&v)[4]) {
+        if constexpr (VEC) {
+            *reinterpret_cast<float4*>(plane + row_off + w0) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (w0 + q < a.W) plane[row_off + w0 + q] = v[q];
+        }
+    };
+
+    // The sums over the gaussian splits, in split order, for both rows at once: the loads of
+    // one split (two rows x (C + 1) planes) are independent of each other and all in flight
+    // together; the kernel is bound by their latency, not by bandwidth.
+    long long row_off2[2];
+    float S2[2][4], R2[2][CMAX][4], T2[2][CMAX][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        row_off2[r] = (long long)min(h0 + r, a.H - 1) * a.W;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) S2[r][q] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CMAX; ++c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) R2[r][c][q] = T2[r][c][q] = 0.f;
+            if (c < a.C) load4(a.target + (b * a.C + c) * HW, row_off2[r], T2[r][c]);
+        }
+    }
+    for (int sp = 0; sp < a.n_split; ++sp) {
+        const float* ps = part_b + sp * split_stride;
+        float tS[2][4], tR[2][CMAX][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            load4(ps + (long long)a.C * HW, row_off2[r], tS[r]);
+#pragma unroll
+            for (int c = 0; c < CMAX; ++c)
+                if (c < a.C) load4(ps + (long long)c * HW, row_off2[r], tR[r][c]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) S2[r][q] += tS[r][q];
+#pragma unroll
+            for (int c = 0; c < CMAX; ++c)
+                if (c < a.C) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) R2[r][c][q] += tR[r][c][q];
+                }
+        }
+    }
+
     bool bad = false;
     float lsum = 0.f;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
+        const bool row_valid = in_range && (h0 + r < a.H);
+        const long long row_off = row_off2[r];
+        float (&S)[4] = S2[r];
+        float (&R)[CMAX][4] = R2[r];
+        float (&T)[CMAX][4] = T2[r];
+        float O[CMAX][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const bool valid = in_range && (h0 + r < a.H) && (w0 + q < a.W);
-            const long long pp = (long long)min(h0 + r, a.H - 1) * a.W + min(w0 + q, a.W - 1);
-            float S = 0.f;
-            for (int sp = 0; sp < a.n_split; ++sp) S += part_b[sp * split_stride + (long long)a.C * HW + pp];
-            const float Sp = S + a.eps;
+            const bool valid = row_valid && (w0 + q < a.W);
+            const float Sp = S[q] + a.eps;
             float acc = 0.f;
             // pixel (r, q) is lane q & 1 of pixel pair 2 * r + (q >> 1)
             float* pr = rec + 8 + (r * 2 + (q >> 1)) * pf + (q & 1);
-            for (int c = 0; c < pf / 2 - 1; ++c) {
+#pragma unroll
+            for (int c = 0; c < CMAX; ++c) {
+                O[c][q] = 0.f;
+                if (c >= pf / 2 - 1) continue;
                 float gn = 0.f;
                 if (c < a.C) {
-                    float R = 0.f;
-                    for (int sp = 0; sp < a.n_split; ++sp) R += part_b[sp * split_stride + (long long)c * HW + pp];
-                    const float o = R / Sp;
-                    const float d = o - a.target[(b * a.C + c) * HW + pp];
+                    const float o = R[c][q] / Sp;
+                    const float d = o - T[c][q];
                     const float g = k * d;
-                    if (valid) {
-                        lsum = fmaf(d, d, lsum);
-                        if (a.out) a.out[(b * a.C + c) * HW + pp] = o;
-                    }
+                    O[c][q] = o;
+                    if (valid) lsum = fmaf(d, d, lsum);
                     acc += (a.mode == IGS_GRAD_REFERENCE) ? g * g : (g / Sp) * o;
                     gn = valid ? g / Sp : 0.f;
                     bad |= !isfinite(gn);
@@ -133,7 +199,14 @@ __global__ void __launch_bounds__(LOSS_TERMS_THREADS) loss_terms_sep_kernel(Loss
             const float gS = valid ? ((a.mode == IGS_GRAD_REFERENCE) ? -acc / (Sp * Sp) : -acc) : 0.f;
             bad |= !isfinite(gS);
             pr[0] = gS;
-            if (valid && a.wsum) a.wsum[b * HW + pp] = S;
+        }
+        if (row_valid) {
+            if (a.out) {
+#pragma unroll
+                for (int c = 0; c < CMAX; ++c)
+                    if (c < a.C) store4(a.out + (b * a.C + c) * HW, row_off, O[c]);
+            }
+            if (a.wsum) store4(a.wsum + b * HW, row_off, S);
         }
     }
     __syncthreads();
@@ -168,10 +241,16 @@ cudaError_t launch_loss_terms_sep(const LossTermArgs& a, float* loss, cudaStream
     const long long blocks = loss_terms_blocks(a.B, a.nrp, a.ncb);
     if (blocks <= 0) return cudaSuccess;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (a.C > 4) return cudaErrorInvalidValue;  // (a chunk of the separable backward has at most four channels)
     const size_t smem = (size_t)LOSS_TERMS_THREADS * bwd_sep_rec_floats(a.ct) * sizeof(float) + 8 * sizeof(float);
+    auto aligned16 = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = a.W % 4 == 0 && aligned16(a.partial) && aligned16(a.target) && aligned16(a.out) && aligned16(a.wsum);
     {
         KernelTimer timer(K_PIXEL_TERMS, s);
-        loss_terms_sep_kernel<<<(unsigned)blocks, LOSS_TERMS_THREADS, smem, s>>>(a);
+        if (vec)
+            loss_terms_sep_kernel<true><<<(unsigned)blocks, LOSS_TERMS_THREADS, smem, s>>>(a);
+        else
+            loss_terms_sep_kernel<false><<<(unsigned)blocks, LOSS_TERMS_THREADS, smem, s>>>(a);
     }
     count_launch();
     cudaError_t e = cudaGetLastError();
