@@ -16,22 +16,37 @@ two settings its CPU path needs:
   (:471-476), which needs a GPU.
 
     python -m oracle.ref_copy [/path/to/reference]     # make the copy
+
+Without an argument the reference tree is looked up under the ``reference_path`` that
+``BASELINE.json`` at the repository root names.
 """
 from __future__ import annotations
 
 import importlib
+import json
 import os
 import shutil
 import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(_HERE, "_ref")
-DEFAULT_REFERENCE = "/root/reference"
 
 
-def make(reference_root: str = DEFAULT_REFERENCE) -> str | None:
+def default_reference() -> str | None:
+    """Where the reference tree lives according to BASELINE.json beside the package, or None."""
+    try:
+        with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as f:
+            return json.load(f).get("reference_path")
+    except (OSError, ValueError):
+        return None
+
+
+def make(reference_root: str | None = None) -> str | None:
     """Copies <reference_root>/src/igs to oracle/_ref/igs; returns the copy's path, or None
     when the reference tree is not there (then an existing copy is left as it is)."""
+    reference_root = reference_root or default_reference()
+    if not reference_root:
+        return None
     src = os.path.join(reference_root, "src", "igs")
     if not os.path.isdir(src):
         return None
@@ -74,5 +89,5 @@ def render_fwd_bwd(mod, positions, colors, scales, rotations, alphas, x, y, gout
 
 
 if __name__ == "__main__":
-    path = make(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE)
+    path = make(sys.argv[1] if len(sys.argv) > 1 else None)
     print(path or "reference tree not found; nothing copied")
