@@ -25,6 +25,7 @@ NVCC_FLAGS = [
     "-O3", "-lineinfo", "-std=c++17",
     "-Xptxas=-v",
     "-Xcompiler", "-fPIC", "-shared",
+    "-Xlinker", "--no-undefined",  # a function that lost its definition fails the build, not the first load
     "--threads", "0",
 ]
 

@@ -378,28 +378,59 @@ __global__ void __launch_bounds__(FwdCfg<CT, PX_>::THREADS, FwdCfg<CT, PX_>::MIN
 }
 
 // Adds the per-split partial sums in split order and either divides (normalize) or
-// hands back the raw sums [B, C+1, HW].
+// hands back the raw sums [B, C+1, HW].  V = pixels per thread: 4 (one 16-byte load or store
+// per plane; the planes must be a multiple of four pixels and start on 16-byte boundaries) or 1.
+template <int V>
 __global__ void __launch_bounds__(256) reduce_normalize_kernel(ReduceArgs a) {
     const long long HW = a.HW;
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*HW
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;  // over B*HW
     if (i >= (long long)a.B * HW) return;
     const long long b = i / HW, p = i - b * HW;
     const long long plane = (long long)(a.C + 1) * HW;
-    float s = 0.f;
-    for (int k = 0; k < a.n_split; ++k) s += a.partial[((long long)k * a.B + b) * plane + (long long)a.C * HW + p];
-    if (a.normalize) {
-        a.wsum[b * HW + p] = s;
-    } else {
-        a.out[b * plane + (long long)a.C * HW + p] = s;
-    }
-    const float den = s + a.eps;
-    for (int c = 0; c < a.C; ++c) {
-        float v = 0.f;
-        for (int k = 0; k < a.n_split; ++k) v += a.partial[((long long)k * a.B + b) * plane + (long long)c * HW + p];
-        if (a.normalize)
-            a.out[(b * a.C + c) * HW + p] = v / den;
+    const long long split_stride = (long long)a.B * plane;
+    auto load = [&](const float* src, float (&v)[V]) {
+        if constexpr (V == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(src);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+            v[0] = *src;
+        }
+    };
+    auto store = [&](float* dst, const float (&v)[V]) {
+        if constexpr (V == 4)
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
         else
-            a.out[b * plane + (long long)c * HW + p] = v;
+            *dst = v[0];
+    };
+    // one plane of this thread's pixels summed over the splits (the loads of four splits are in
+    // flight together; the additions keep the split order)
+    auto sum_plane = [&](int c, float (&acc)[V]) {
+        const float* src = a.partial + b * plane + (long long)c * HW + p;
+#pragma unroll
+        for (int q = 0; q < V; ++q) acc[q] = 0.f;
+#pragma unroll 4
+        for (int k = 0; k < a.n_split; ++k) {
+            float t[V];
+            load(src + (long long)k * split_stride, t);
+#pragma unroll
+            for (int q = 0; q < V; ++q) acc[q] += t[q];
+        }
+    };
+    float s[V], den[V];
+    sum_plane(a.C, s);
+    store(a.normalize ? a.wsum + b * HW + p : a.out + b * plane + (long long)a.C * HW + p, s);
+#pragma unroll
+    for (int q = 0; q < V; ++q) den[q] = s[q] + a.eps;
+    for (int c = 0; c < a.C; ++c) {
+        float v[V];
+        sum_plane(c, v);
+        if (a.normalize) {
+#pragma unroll
+            for (int q = 0; q < V; ++q) v[q] = v[q] / den[q];
+            store(a.out + (b * a.C + c) * HW + p, v);
+        } else {
+            store(a.out + b * plane + (long long)c * HW + p, v);
+        }
     }
 }
 
@@ -470,9 +501,14 @@ cudaError_t launch_forward_chunk(int ct, bool separable, bool culling, const Fwd
 cudaError_t launch_reduce_normalize(const ReduceArgs& a, cudaStream_t s) {
     const long long n = (long long)a.B * a.HW;
     if (n <= 0) return cudaSuccess;
+    auto aligned16 = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = a.HW % 4 == 0 && aligned16(a.partial) && aligned16(a.out) && aligned16(a.wsum);
     {
         KernelTimer timer(K_REDUCE, s);
-        reduce_normalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
+        if (vec)
+            reduce_normalize_kernel<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(a);
+        else
+            reduce_normalize_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
