@@ -362,6 +362,9 @@ int backward_chunk_pairs(int ct) { return ct <= 4 ? 256 : 128; }
 // warp turns the sums into gradients, one gaussian per lane.
 constexpr int FIN_G = 32, FIN_THREADS = 256;
 
+// RANGED: per-slot slab ranges (a.slab_range); ORDERED: a.order maps slots to gaussians.  Separate
+// instantiations: with both decided at run time the plain case ran 10 us longer.
+template <bool RANGED, bool ORDERED>
 __global__ void __launch_bounds__(FIN_THREADS) finalize_kernel(FinalizeArgs a) {
     extern __shared__ float s_sum[];  // [planes][FIN_G]
     const int lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
@@ -375,7 +378,7 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_kernel(FinalizeArgs a) {
     const long long slab_stride = (long long)a.B * a.planes * plane;
     // the slabs that hold sums of this slot: all of them, or (ordered skipping path) the
     // range its group had tasks for; the others were never written and stand for exact zeros
-    if (a.slab_range) {
+    if constexpr (RANGED) {
         const int r = a.slab_range[t];
         const int s_lo = min(r & 0xffff, a.n_slab), s_hi = min(r >> 16, a.n_slab);
         for (int p = wq; p < a.planes; p += FIN_THREADS / 32) {
@@ -395,7 +398,8 @@ __global__ void __launch_bounds__(FIN_THREADS) finalize_kernel(FinalizeArgs a) {
         }
     }
     __syncthreads();
-    long long n = a.order ? (long long)a.order[t] : slot;
+    long long n = slot;
+    if constexpr (ORDERED) n = a.order[t];
     if (wq != 0 || t_raw >= total || n < 0 || n >= a.N) return;  // (an entry that is no index: nothing to write)
     const long long i = b * a.N + n;
     float M[N_MOMENTS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -455,7 +459,16 @@ cudaError_t launch_finalize(const FinalizeArgs& a, cudaStream_t s) {
     {
         KernelTimer timer(K_FINALIZE, s);
         // (planes <= 6 * 16 + 256: at most 45 KB, within the default dynamic limit)
-        finalize_kernel<<<(unsigned)((n + FIN_G - 1) / FIN_G), FIN_THREADS, (size_t)a.planes * FIN_G * sizeof(float), s>>>(a);
+        const unsigned blocks = (unsigned)((n + FIN_G - 1) / FIN_G);
+        const size_t smem = (size_t)a.planes * FIN_G * sizeof(float);
+        if (a.slab_range && a.order)
+            finalize_kernel<true, true><<<blocks, FIN_THREADS, smem, s>>>(a);
+        else if (a.slab_range)
+            finalize_kernel<true, false><<<blocks, FIN_THREADS, smem, s>>>(a);
+        else if (a.order)
+            finalize_kernel<false, true><<<blocks, FIN_THREADS, smem, s>>>(a);
+        else
+            finalize_kernel<false, false><<<blocks, FIN_THREADS, smem, s>>>(a);
     }
     count_launch();
     return cudaGetLastError();
