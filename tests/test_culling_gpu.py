@@ -186,6 +186,29 @@ def test_many_channels_gradients_do_not_depend_on_the_processing_order(C):
                 assert torch.equal(r[k], res[0][k]), (k, lo)
 
 
+@pytest.mark.parametrize("C,warp", [(3, True), (17, False), (17, True)])
+def test_general_kernels_take_an_order_too(C, warp):
+    """The general backward (sample points off a grid; more than 16 channels in two chunks)
+    with an explicit order: the partial sums are laid out by processing slot and mapped back
+    through the order, so every permutation gives the same bits, and the result agrees with
+    an order-less call to rounding."""
+    dev = torch.device("cuda", 0)
+    B, N, H, W = 2, 777, 40, 72
+    gen = torch.Generator().manual_seed(90 + C)
+    d, gout, x, y = _case(B, N, H, W, C, 0.02, 0.3, seed=80 + C, dev=dev)
+    if warp:
+        x = (x + 0.03 * torch.sin(4 * y)).contiguous()
+    orders = [torch.stack([torch.randperm(N, generator=gen) for _ in range(B)]).to(torch.int32).to(dev).contiguous()
+              for _ in range(2)]
+    orders.append(torch.arange(N - 1, -1, -1, dtype=torch.int32, device=dev).expand(B, N).contiguous())
+    res = [_backward_with(d, gout, x, y, o) for o in orders]
+    plain = _backward_with(d, gout, x, y, None)
+    for k in plain:
+        for r in res[1:]:
+            assert torch.equal(r[k], res[0][k]), k
+        assert _rel(res[0][k], plain[k]) < 2e-5, (k, _rel(res[0][k], plain[k]))
+
+
 def _backward_with(d, gout, x, y, order):
     """Gradients through the library call itself, with an explicit processing order."""
     from igs_b200 import _lib
