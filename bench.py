@@ -379,7 +379,7 @@ class FitWorkload:
         with torch.no_grad():
             self.model.position.copy_(self.model.position[:, perm])
         self.model.to(dev)
-        self.opt = torch.optim.Adam(self.model.parameters(), lr=1e-2)
+        self.opt = torch.optim.Adam(self.model.parameters(), lr=1e-2, fused=True)
         self.host = {"target": torch.rand(1, 3, FIT_SIZE, FIT_SIZE, generator=gen).pin_memory()}
         self.cfg = cpu_config("fit")
         self.C, self.B_local, self.N_local = 3, 1, FIT_N

@@ -272,7 +272,9 @@ def fit(model, target, steps, lr=1e-2, graph=True, schedule=None, betas=(0.9, 0.
     if isinstance(model, ShardedImageFitter):
         graph = False  # (a step holds a collective: issued eagerly, never captured)
     schedule = schedule or [(1, steps)]
-    opt = torch.optim.Adam(model.parameters(), lr=lr, betas=betas, capturable=bool(graph))
+    # (torch's single-kernel Adam: the default one issues a dozen small launches per step, which
+    # a host-bound eager step pays for in full)
+    opt = torch.optim.Adam(model.parameters(), lr=lr, betas=betas, capturable=bool(graph), fused=True)
     for p in model.parameters():  # Adam must see gradients from the first (captured) step on
         p.grad = torch.zeros_like(p)
     history = torch.zeros(sum(n for _, n in schedule), device=target.device)
@@ -321,7 +323,7 @@ def fit_progressive(model, target, steps, lr=1e-4, chunk=4, ratios=(1 / 16, 1 / 
     if not target.is_cuda:
         raise RuntimeError("fit_progressive() runs on CUDA tensors only")
     gen = torch.Generator().manual_seed(seed)
-    opt = torch.optim.AdamW(model.parameters(), lr=lr, eps=EPS)
+    opt = torch.optim.AdamW(model.parameters(), lr=lr, eps=EPS, fused=True)
     size = target.shape[-2:]
     n = model.num_features
     history = torch.zeros(steps, device=target.device)
