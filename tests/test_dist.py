@@ -237,14 +237,18 @@ def _worker_sharded_fit(rank, world, port, backend, q):
         model = fit.ShardedImageFitter(53, channels=3, image=tgt.cpu(), init_log_scale=-1.5,
                                        backend=None if backend == "nccl" else OracleBackend).to(dev)
         _spread(model)
-        opt = torch.optim.Adam(model.parameters(), lr=2e-2)
-        losses = []
-        for _ in range(3):
-            opt.zero_grad(set_to_none=True)
-            loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
-            loss.backward()
-            opt.step()
-            losses.append(float(loss.detach()))
+        if backend == "nccl":
+            # through the package's own loop (which keeps a sharded model out of graph capture)
+            losses = fit.fit(model, tgt, steps=3, lr=2e-2, graph=True).tolist()
+        else:
+            opt = torch.optim.Adam(model.parameters(), lr=2e-2)
+            losses = []
+            for _ in range(3):
+                opt.zero_grad(set_to_none=True)
+                loss = torch.nn.functional.mse_loss(model((18, 22)), tgt)
+                loss.backward()
+                opt.step()
+                losses.append(float(loss.detach()))
         full = {k: v.cpu().numpy() for k, v in model.gathered().items()}
         q.put((rank, model.range, losses, full, None))
         dist.barrier()
