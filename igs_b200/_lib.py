@@ -192,9 +192,10 @@ def read_executed(ws: torch.Tensor) -> int:
 # Without help the library decides on the device which kernel instantiations the data calls
 # for (separable grid or not, narrow gaussians or not) and launches all candidates; those
 # not chosen return at once.  The facts end up in the workspace's status words.  Here they
-# are read back WITHOUT ever blocking (a 32-byte copy into pinned memory plus an event,
-# picked up by a later call once the event has completed) and remembered, so that later
-# calls pass hints and launch only what will run:
+# are read back without blocking (a 32-byte copy into pinned memory plus an event, picked up
+# by a later call once the event has completed; only the very first call on a device and
+# gaussian count nothing is known about waits for its own answer, see _queue_read) and
+# remembered, so that later calls pass hints and launch only what will run:
 #   * per (device, B, N, H, W): whether at least one gaussian in eight is narrow -- looked at
 #     during the first calls and every 32nd after that; "not narrow" becomes
 #     HINT_WIDE_GAUSSIANS, "narrow" lets the set_backward_sort policy order the gaussians.
@@ -208,6 +209,7 @@ _memo_lock = threading.Lock()
 _pending = []       # reads in flight: _PendingRead
 _free_hosts = []    # pinned int32[STATUS_WORDS] buffers to reuse
 _shape_memos = {}   # (device index, B, N, H, W) -> _ShapeMemo
+_family_narrow = {}  # (device index, B, N) -> the latest answer any image size gave
 _grid_memos = {}    # (id(x), id(y)) -> _GridMemo
 GRID_CHECKED_BIT = 8
 GRID_NOT_SEPARABLE_BIT = 1
@@ -216,13 +218,14 @@ GRID_NOT_SEPARABLE_BIT = 1
 class _ShapeMemo:
     EVERY = 32  # after the first few calls, look again every this many
 
-    __slots__ = ("total", "narrow", "calls", "pending")
+    __slots__ = ("total", "narrow", "calls", "pending", "family")
 
-    def __init__(self, total):
+    def __init__(self, total, family=None):
         self.total = total
         self.narrow = None  # unknown until the first read has come back
         self.calls = 0
         self.pending = False
+        self.family = family  # (device index, B, N): the same gaussians at any image size
 
 
 class _GridMemo:
@@ -260,6 +263,8 @@ def _drain_reads():
             if r.shape is not None:
                 r.shape.pending = False
                 r.shape.narrow = words[2] * 8 >= r.shape.total
+                if r.shape.family is not None:
+                    _family_narrow[r.shape.family] = r.shape.narrow
             if r.grid is not None:
                 r.grid.pending = False
                 if r.grid.kind is None:
@@ -295,6 +300,16 @@ def _queue_read(ws, shape, grid):
         if want_grid:
             grid.pending = True
         _pending.append(r)
+        first_look = want_shape and shape.narrow is None
+    if first_look:
+        # The very first call on gaussians nothing is known about: wait for its answer (the one
+        # place the call layer blocks, once per device and gaussian count).  A loop issues steps
+        # far faster than the device runs the unordered kernels on narrow gaussians, so without
+        # the wait dozens of such steps are queued before the answer to the first one arrives:
+        # measured, 16384 narrow gaussians at 1024 x 1024, the first 27 steps at 8 ms each
+        # instead of 0.5 ms.
+        r.event.synchronize()
+        _drain_reads()
 
 
 def _shape_memo(dev, B, N, H, W):
@@ -303,7 +318,14 @@ def _shape_memo(dev, B, N, H, W):
     if m is None:
         if len(_shape_memos) > 256:
             _shape_memos.clear()
-        m = _shape_memos[key] = _ShapeMemo(B * N)
+        # Whether gaussians are narrow is judged against the sampled extent, not against the
+        # pixel count, so a new image size starts from what the same number of gaussians showed
+        # at the last one (a fit that moves up its resolution schedule keeps its ordered kernels
+        # instead of running the first steps of every size without an order).  A guess: the
+        # first reads of the new shape confirm or correct it, and it only ever costs time.
+        family = (dev.index, B, N)
+        m = _shape_memos[key] = _ShapeMemo(B * N, family)
+        m.narrow = _family_narrow.get(family)
     return m
 
 
@@ -311,6 +333,7 @@ def forget_what_calls_learnt() -> None:
     """Drops every remembered fact (tests; after changing the culling switch)."""
     with _memo_lock:
         _shape_memos.clear()
+        _family_narrow.clear()
         _grid_memos.clear()
 
 

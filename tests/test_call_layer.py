@@ -69,6 +69,24 @@ def test_grid_argument_errors(lib):
         lib.grid_for_call(x, y, 3)
 
 
+def test_a_new_image_size_starts_from_what_the_same_gaussians_showed(lib):
+    """Narrow or wide is judged against the sampled extent, so the answer carries over to another
+    image size of the same (device, B, N) as a first guess; other gaussian counts start unknown."""
+    dev = torch.device("cuda", 0)
+    lib.forget_what_calls_learnt()
+    small = lib._shape_memo(dev, 1, 500, 64, 64)
+    assert small.narrow is None
+    small.narrow = True
+    lib._family_narrow[small.family] = True  # (what folding a completed read into the memo does)
+    big = lib._shape_memo(dev, 1, 500, 128, 128)
+    assert big is not small and big.narrow is True and big.calls == 0 and not big.pending
+    assert lib._shape_memo(dev, 1, 501, 128, 128).narrow is None
+    assert lib._shape_memo(dev, 2, 500, 128, 128).narrow is None
+    lib.forget_what_calls_learnt()
+    assert lib._shape_memo(dev, 1, 500, 256, 256).narrow is None
+    lib.forget_what_calls_learnt()
+
+
 def test_policy_decides_without_launching(lib):
     B, N, H, W = 1, 64, 16, 16
     x, y = _grid(B, H, W)
