@@ -53,9 +53,19 @@ def make(reference_root: str | None = None) -> str | None:
     dst = os.path.join(REF_DIR, "igs")
     os.makedirs(REF_DIR, exist_ok=True)
     if os.path.isdir(dst):
+        _make_writable(dst)
         shutil.rmtree(dst)
     shutil.copytree(src, dst, ignore=shutil.ignore_patterns("__pycache__"))
+    _make_writable(dst)  # (a read-only reference tree hands its modes to the copy)
     return dst
+
+
+def _make_writable(root: str) -> None:
+    for base, dirs, files in os.walk(root):
+        for name in dirs + files:
+            path = os.path.join(base, name)
+            os.chmod(path, os.stat(path).st_mode | 0o200)
+    os.chmod(root, os.stat(root).st_mode | 0o200)
 
 
 def available() -> bool:
